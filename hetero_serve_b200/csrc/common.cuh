@@ -1,0 +1,80 @@
+// Shared helpers for the sm_100a kernels of hetero_serve_b200.
+//
+// Conventions used by every entry point in this directory:
+//  * entry points are extern "C", take raw device pointers, sizes and the CUDA stream,
+//    allocate nothing and return 0 or a negative HS_ERR_* code (sizes refused) or a
+//    positive cudaError_t (launch failed);
+//  * `dtype` arguments: 0 = float32, 1 = bfloat16;
+//  * the residual stream, normalisation statistics, softmax state, accumulators, biases
+//    and norm parameters are float32 in both precisions;
+//  * `status` is one device int the engine owns.  A kernel that meets an index outside
+//    its table (token id, position, page) skips the access and ORs a bit into it; the
+//    host reads it with the step's results.  Nothing traps.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define HS_OK 0
+#define HS_ERR_UNSUPPORTED (-1)   // a size or option this kernel does not take
+#define HS_ERR_ARGUMENT (-2)      // null pointer / inconsistent arguments
+
+#define HS_STATUS_BAD_TOKEN 1
+#define HS_STATUS_BAD_POSITION 2
+#define HS_STATUS_BAD_PAGE 4
+#define HS_STATUS_PIPELINE_TIMEOUT 8
+
+#define HS_DT_F32 0
+#define HS_DT_BF16 1
+
+#define HS_ACT_NONE 0
+#define HS_ACT_GELU_TANH 1
+#define HS_ACT_GELU_ERF 2
+
+#define HS_EXPORT extern "C" __attribute__((visibility("default")))
+
+#define HS_LAUNCH_CHECK()                      \
+  do {                                         \
+    cudaError_t e__ = cudaGetLastError();      \
+    if (e__ != cudaSuccess) return (int)e__;   \
+  } while (0)
+
+namespace hs {
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// 0.5*u*(1+tanh(sqrt(2/pi)*(u+0.044715 u^3))) and 0.5*u*(1+erf(u/sqrt(2))), both with the
+// accurate libm-grade device functions (this library is never built with fast-math).
+__device__ __forceinline__ float gelu_tanh(float u) {
+  const float k = 0.7978845608028654f;
+  float inner = k * (u + 0.044715f * u * u * u);
+  return 0.5f * u * (1.0f + tanhf(inner));
+}
+__device__ __forceinline__ float gelu_erf(float u) {
+  return 0.5f * u * (1.0f + erff(u * 0.70710678118654752440f));
+}
+__device__ __forceinline__ float apply_act(float u, int act) {
+  if (act == HS_ACT_GELU_TANH) return gelu_tanh(u);
+  if (act == HS_ACT_GELU_ERF) return gelu_erf(u);
+  return u;
+}
+
+}  // namespace hs

@@ -1,0 +1,138 @@
+// Embedding gather (token table + optional learned position table) and LayerNorm.
+//
+// Reference formulas: x[t] = wte[ids[t]] + wpe[pos[t]] (heteroserve/model/torch_engine.py:89-90);
+// mu = mean(x), var = mean((x-mu)^2), y = (x-mu)/sqrt(var+eps)*g + b
+// (heteroserve/model/numpy_engine.py:26-30).  The sum and the statistics are float32.
+#include "common.cuh"
+
+namespace hs {
+
+template <typename T>
+__global__ void embed_kernel(float* __restrict__ x, const int* __restrict__ ids,
+                             const int* __restrict__ pos, const int* __restrict__ req,
+                             const T* __restrict__ wte, const T* __restrict__ wpe, int width,
+                             int vocab, int n_pos, int* status) {
+  const int t = blockIdx.x;
+  float* row = x + (size_t)t * width;
+  const int r = req[t];
+  const int id = ids[t];
+  const int p = pos[t];
+  bool ok = r >= 0;
+  if (ok && (id < 0 || id >= vocab)) {
+    if (threadIdx.x == 0) atomicOr(status, HS_STATUS_BAD_TOKEN);
+    ok = false;
+  }
+  if (ok && wpe != nullptr && (p < 0 || p >= n_pos)) {
+    if (threadIdx.x == 0) atomicOr(status, HS_STATUS_BAD_POSITION);
+    ok = false;
+  }
+  if (!ok) {  // padding rows of a bucket, or a refused index: a defined, finite row
+    for (int e = threadIdx.x; e < width; e += blockDim.x) row[e] = 0.f;
+    return;
+  }
+  const T* a = wte + (size_t)id * width;
+  if (wpe != nullptr) {
+    const T* b = wpe + (size_t)p * width;
+    for (int e = threadIdx.x; e < width; e += blockDim.x) row[e] = to_f(a[e]) + to_f(b[e]);
+  } else {
+    for (int e = threadIdx.x; e < width; e += blockDim.x) row[e] = to_f(a[e]);
+  }
+}
+
+// One block per output row.  The row is staged in shared memory as float32; the mean and
+// the centred variance are two block reductions whose tree depends on `width` and the
+// block size only, so a row's result never depends on the batch around it.
+template <typename TO, int THREADS>
+__global__ void layernorm_kernel(TO* __restrict__ out, const float* __restrict__ x,
+                                 const float* __restrict__ gamma, const float* __restrict__ beta,
+                                 const int* __restrict__ rows, int width, float eps) {
+  extern __shared__ float srow[];
+  __shared__ float red[THREADS / 32];
+  __shared__ float bcast;
+  const int o = blockIdx.x;
+  const int src = rows ? rows[o] : o;
+  const float* xr = x + (size_t)src * width;
+  float s = 0.f;
+  for (int e = threadIdx.x; e < width; e += THREADS) {
+    float v = xr[e];
+    srow[e] = v;
+    s += v;
+  }
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < THREADS / 32; ++i) t += red[i];
+    bcast = t / (float)width;
+  }
+  __syncthreads();
+  const float mu = bcast;
+  float q = 0.f;
+  for (int e = threadIdx.x; e < width; e += THREADS) {
+    float c = srow[e] - mu;
+    q += c * c;
+  }
+  q = warp_sum(q);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = q;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < THREADS / 32; ++i) t += red[i];
+    bcast = 1.0f / sqrtf(t / (float)width + eps);
+  }
+  __syncthreads();
+  const float rstd = bcast;
+  TO* orow = out + (size_t)o * width;
+  for (int e = threadIdx.x; e < width; e += THREADS)
+    orow[e] = from_f<TO>((srow[e] - mu) * rstd * gamma[e] + beta[e]);
+}
+
+}  // namespace hs
+
+HS_EXPORT int hs_embed(float* x, const int* ids, const int* pos, const int* req, const void* wte,
+                       const void* wpe, int n_tokens, int width, int vocab, int n_pos,
+                       int table_dtype, int* status, void* stream) {
+  if (!x || !ids || !pos || !req || !wte || !status) return HS_ERR_ARGUMENT;
+  if (n_tokens <= 0) return HS_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  int threads = width >= 1024 ? 256 : 128;
+  if (table_dtype == HS_DT_F32)
+    hs::embed_kernel<float><<<n_tokens, threads, 0, st>>>(
+        x, ids, pos, req, (const float*)wte, (const float*)wpe, width, vocab, n_pos, status);
+  else if (table_dtype == HS_DT_BF16)
+    hs::embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, st>>>(
+        x, ids, pos, req, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, width, vocab,
+        n_pos, status);
+  else
+    return HS_ERR_UNSUPPORTED;
+  HS_LAUNCH_CHECK();
+  return HS_OK;
+}
+
+HS_EXPORT int hs_layernorm(void* out, const float* x, const float* gamma, const float* beta,
+                           const int* rows, int n_rows, int width, float eps, int out_dtype,
+                           void* stream) {
+  if (!out || !x || !gamma || !beta) return HS_ERR_ARGUMENT;
+  if (n_rows <= 0) return HS_OK;
+  constexpr int THREADS = 256;
+  size_t smem = (size_t)width * sizeof(float);
+  if (smem > 200 * 1024) return HS_ERR_UNSUPPORTED;  // a row must fit shared memory
+  cudaStream_t st = (cudaStream_t)stream;
+  if (out_dtype == HS_DT_F32) {
+    auto k = hs::layernorm_kernel<float, THREADS>;
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<n_rows, THREADS, smem, st>>>((float*)out, x, gamma, beta, rows, width, eps);
+  } else if (out_dtype == HS_DT_BF16) {
+    auto k = hs::layernorm_kernel<__nv_bfloat16, THREADS>;
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<n_rows, THREADS, smem, st>>>((__nv_bfloat16*)out, x, gamma, beta, rows, width, eps);
+  } else {
+    return HS_ERR_UNSUPPORTED;
+  }
+  HS_LAUNCH_CHECK();
+  return HS_OK;
+}

@@ -1,0 +1,424 @@
+"""The step function: one forward pass over a batch of (request, its next tokens).
+
+A batch is flat and ragged.  Each entry brings the next tokens of one request — a
+portion of its prompt, cut anywhere, or a single decoded token — and the places among
+them whose logits are wanted.  :meth:`Runner.step` runs exactly these tokens, as one
+batch, against the pages earlier steps left in the cache, and returns the logits at
+the wanted places (and, on request, tokens sampled from them on the device).
+
+The reference has four entry points instead (``prefill``, ``decode_batch``,
+``prefill_paged``, ``decode_batch_paged``, heteroserve/model/torch_engine.py:94-321) and
+never mixes a prompt portion with decoded tokens in one pass
+(heteroserve/worker/worker.py:580-591); the order inside a layer is the same
+(torch_engine.py:297-317).
+
+Host to device traffic per step is ONE copy of a packed int32 block (token ids,
+positions, the request of each token, block tables, wanted rows, sampling
+parameters); device to host is one small copy of the sampled tokens and the status
+word, or nothing at all when the caller only wants device logits.  With
+``cuda_graphs`` the kernels of a step are captured once per size class and replayed.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Hashable, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, CacheStorage, GroupSpec
+from ..kernels.ops import KernelError
+
+STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a position outside the table",
+               4: "a page number outside the pool", 8: "a kernel pipeline timed out"}
+
+
+class StepError(RuntimeError):
+    pass
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request, and which of their logits are wanted."""
+
+    req_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+    # used only when the step samples on the device
+    temperature: float = 0.0
+    top_k: int = 0
+    seed: int = 0
+
+
+@dataclass
+class StepResult:
+    logits: torch.Tensor | None          # [n_wanted, vocab] float32 on the device
+    tokens: torch.Tensor | None          # [n_wanted] int32 on the device (if sampled)
+    rows: list[tuple[Hashable, int]]     # (request, index among its tokens) per wanted row
+    n_tokens: int = 0
+
+    def tokens_host(self) -> list[int]:
+        return [] if self.tokens is None else self.tokens.cpu().tolist()
+
+
+@dataclass
+class CacheView:
+    """What a mixer sees of the cache for one layer call."""
+
+    pool: torch.Tensor           # [pages, 2, kv_heads, page_size, head_dim]
+    table: torch.Tensor          # [requests, max_pages] int32: this batch's block tables
+    page_size: int
+    num_pages: int
+    writes: bool
+    group: int
+
+
+class Layout:
+    """Offsets of the sections of the packed int32 metadata block for one size class."""
+
+    def __init__(self, T: int, R: int, W: int, max_pages: Sequence[int], plan_ints: int):
+        self.T, self.R, self.W = T, R, W
+        self.max_pages = tuple(max_pages)
+        off = 0
+
+        def take(n):
+            nonlocal off
+            start = off
+            off += (n + 3) // 4 * 4          # keep every section 16-byte aligned
+            return start
+
+        self.tok_ids, self.tok_pos, self.tok_req = take(T), take(T), take(T)
+        self.req_start, self.req_len, self.req_ctx, self.req_slot = (take(R), take(R), take(R),
+                                                                     take(R))
+        self.logit_rows = take(W)
+        self.samp_temp, self.samp_topk = take(W), take(W)
+        self.samp_seed_lo, self.samp_seed_hi, self.samp_pos = take(W), take(W), take(W)
+        self.tables = [take(R * mp) for mp in self.max_pages]
+        self.plan = take(plan_ints)
+        self.plan_ints = plan_ints
+        self.total = off
+
+
+class StepContext:
+    """Everything a part may touch while a step runs."""
+
+    def __init__(self, runner: "Runner", layout: Layout, meta: torch.Tensor):
+        self.runner = runner
+        self.ops = runner.ops
+        self.dtype = runner.dtype
+        self.device = runner.device
+        self.status = runner.status
+        self.layout = layout
+        self.meta = meta
+        L = layout
+        self.n_rows, self.n_requests, self.n_logit_rows = L.T, L.R, L.W
+        self.tok_ids = meta[L.tok_ids:L.tok_ids + L.T]
+        self.tok_pos = meta[L.tok_pos:L.tok_pos + L.T]
+        self.tok_req = meta[L.tok_req:L.tok_req + L.T]
+        self.req_start = meta[L.req_start:L.req_start + L.R]
+        self.req_len = meta[L.req_len:L.req_len + L.R]
+        self.req_ctx = meta[L.req_ctx:L.req_ctx + L.R]
+        self.req_slot = meta[L.req_slot:L.req_slot + L.R]
+        self.logit_rows = meta[L.logit_rows:L.logit_rows + L.W]
+        self.samp_temp = meta[L.samp_temp:L.samp_temp + L.W].view(torch.float32)
+        self.samp_topk = meta[L.samp_topk:L.samp_topk + L.W]
+        self.samp_seed_lo = meta[L.samp_seed_lo:L.samp_seed_lo + L.W]
+        self.samp_seed_hi = meta[L.samp_seed_hi:L.samp_seed_hi + L.W]
+        self.samp_pos = meta[L.samp_pos:L.samp_pos + L.W]
+        self.tables = [meta[o:o + L.R * mp].view(L.R, mp)
+                       for o, mp in zip(L.tables, L.max_pages)]
+        self.plan = AttentionPlan(meta[L.plan:L.plan + L.plan_ints], L.T, L.R)
+        self.call_index: int | None = None
+        # host-side view of the batch for parts written in plain PyTorch
+        self.host: list[tuple[Hashable, int, int, int]] = []   # (req, slot, start, n)
+
+    def buffer(self, name: str, shape, dtype) -> torch.Tensor:
+        """A temporary tensor that lives until the next step (never allocated twice for the
+        same use and size class)."""
+        return self.runner.workspace.get(name, shape, dtype)
+
+    def cache_view(self, call) -> CacheView:
+        model, rn = self.runner.model, self.runner
+        gi, k = model.entry_location[call.cache]
+        pool = rn.storage.entry_pool(gi, k)
+        return CacheView(pool=pool, table=self.tables[gi], page_size=rn.manager.page_size,
+                         num_pages=pool.shape[0], writes=call.writes_cache, group=gi)
+
+    def state(self) -> torch.Tensor:
+        """State tensor ``[slots, ...]`` of the mixer running now; rows are indexed with
+        ``req_slot``."""
+        return self.runner.storage.states[self.call_index]
+
+
+@dataclass
+class AttentionPlan:
+    """Work lists a specialised attention kernel reads (filled by ``ops.plan_attention``)."""
+
+    data: torch.Tensor
+    n_rows: int
+    n_requests: int
+    info: dict = field(default_factory=dict)
+
+
+class Workspace:
+    """Temporary buffers by (name, dtype): one flat allocation each, grown when a larger
+    shape is asked for.  Outgrown allocations are kept, since captured graphs may still
+    point into them."""
+
+    def __init__(self, device):
+        self.device = device
+        self._flat: dict[tuple[str, torch.dtype], torch.Tensor] = {}
+        self._retired: list[torch.Tensor] = []
+
+    def get(self, name, shape, dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (name, dtype)
+        flat = self._flat.get(key)
+        if flat is None or flat.numel() < n:
+            if flat is not None:
+                self._retired.append(flat)
+            flat = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
+            self._flat[key] = flat
+        return flat[:n].view(*shape)
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self._flat.values())
+
+
+def _bucket(n: int, lo: int) -> int:
+    b = lo
+    while b < n:
+        b *= 2
+    return b
+
+
+class Runner:
+    """Owns the model, the cache and the kernels, and runs steps."""
+
+    def __init__(self, model, *, num_pages: int, page_size: int, max_requests: int,
+                 dtype: torch.dtype, device, ops=None, prefix_cache: bool = False,
+                 cuda_graphs: bool = False):
+        if ops is None:
+            from ..kernels.ops import CudaOps
+            ops = CudaOps()
+        self.ops = ops
+        self.model = model
+        self.dtype = dtype
+        self.device = torch.device(device)
+        if model.dtype != dtype:
+            raise StepError("the model was bound with another dtype than the runner's")
+        self.manager = CacheManager(
+            [GroupSpec(window=g.window) for g in model.cache_groups], num_pages, page_size,
+            max_requests, prefix_cache=prefix_cache, has_state=bool(model.state_shapes))
+        self.storage = CacheStorage(model, self.manager, dtype, self.device)
+        self.workspace = Workspace(self.device)
+        self.max_positions = model.spec.max_positions
+        self.max_pages = [self.manager.pages_for(self.max_positions) for _ in model.cache_groups]
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.cuda = self.device.type == "cuda"
+        self.use_graphs = bool(cuda_graphs and self.cuda)
+        self._graphs: dict[tuple, "_Captured"] = {}
+        self._host_meta: dict[int, torch.Tensor] = {}
+        self._dev_meta: dict[tuple, torch.Tensor] = {}
+        self._layouts: dict[tuple, Layout] = {}
+        self._copy_done = None
+        self.steps_run = 0
+
+    # -- requests ---------------------------------------------------------------
+    def open(self, req_id, token_ids=None):
+        """Start a request (state slot; prefix pages if ``token_ids`` is given and prefix
+        reuse is on).  Returns how many leading tokens are already cached."""
+        opened = self.manager.open(req_id, token_ids)
+        for st in self.storage.states.values():
+            st[opened.slot].zero_()
+        return opened.cached_tokens
+
+    def close(self, req_id) -> None:
+        self.manager.close(req_id)
+
+    # -- the step -----------------------------------------------------------------
+    def _layout(self, T, R, W) -> Layout:
+        key = (T, R, W)
+        lay = self._layouts.get(key)
+        if lay is None:
+            plan_ints = 0
+            if hasattr(self.ops, "attention_plan_ints"):
+                plan_ints = self.ops.attention_plan_ints(T, R)
+            lay = Layout(T, R, W, self.max_pages, plan_ints)
+            self._layouts[key] = lay
+        return lay
+
+    def _host_buffer(self, n: int) -> torch.Tensor:
+        size = _bucket(n, 1024)
+        buf = self._host_meta.get(size)
+        if buf is None:
+            buf = torch.zeros(size, dtype=torch.int32)
+            if self.cuda:
+                buf = buf.pin_memory()
+            self._host_meta[size] = buf
+        return buf
+
+    def step(self, entries: Sequence[StepEntry], sample: bool = False,
+             check_status: bool = True) -> StepResult:
+        if not entries:
+            return StepResult(None, None, [], 0)
+        mgr = self.manager
+        # ---- host side: validate, reserve pages, lay the batch out ----------------
+        seen = set()
+        starts = []
+        n_tok = n_want = 0
+        for e in entries:
+            if e.req_id in seen:
+                raise StepError(f"request {e.req_id!r} appears twice in one step")
+            seen.add(e.req_id)
+            if e.req_id not in mgr:
+                self.open(e.req_id)
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.req_id!r} brings no tokens")
+            start = mgr.length(e.req_id)
+            if start + n > self.max_positions:
+                raise StepError(f"request {e.req_id!r}: {start + n} positions exceed the "
+                                f"model's {self.max_positions}")
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise StepError(f"request {e.req_id!r}: wanted place {w} outside its "
+                                    f"{n} tokens")
+            starts.append(start)
+            n_tok += n
+            n_want += len(e.want)
+        for e, start in zip(entries, starts):
+            mgr.reserve(e.req_id, start + len(e.tokens))      # OutOfPages: nothing ran
+
+        if self.use_graphs:
+            T, R = _bucket(n_tok, 16), _bucket(len(entries), 1)
+            W = _bucket(n_want, 1) if n_want else 0
+        else:
+            T, R, W = n_tok, len(entries), n_want
+        lay = self._layout(T, R, W)
+        host = self._host_buffer(lay.total)
+        if self._copy_done is not None:
+            self._copy_done.synchronize()     # the previous step's upload has left the buffer
+        hm = host.numpy()
+        vocab = self.model.spec.vocab_size
+        hm[lay.tok_req:lay.tok_req + T] = -1
+        hm[lay.tok_ids:lay.tok_ids + T] = 0
+        hm[lay.tok_pos:lay.tok_pos + T] = 0
+        if W:
+            hm[lay.logit_rows:lay.logit_rows + W] = 0
+            hm[lay.samp_temp:lay.samp_temp + W] = 0
+            hm[lay.samp_topk:lay.samp_topk + W] = 0
+            hm[lay.samp_pos:lay.samp_pos + W] = 0
+        for gi, mp in enumerate(lay.max_pages):
+            hm[lay.tables[gi]:lay.tables[gi] + R * mp] = -1
+        hm[lay.req_len:lay.req_len + R] = 0
+        hm[lay.req_ctx:lay.req_ctx + R] = 0
+        hm[lay.req_start:lay.req_start + R] = 0
+        hm[lay.req_slot:lay.req_slot + R] = 0
+        temps = hm[lay.samp_temp:lay.samp_temp + W].view(np.float32) if W else None
+        rows: list[tuple[Hashable, int]] = []
+        host_batch = []
+        t = w_i = 0
+        for r, (e, start) in enumerate(zip(entries, starts)):
+            n = len(e.tokens)
+            toks = np.asarray(e.tokens, dtype=np.int64)
+            if toks.min() < 0 or toks.max() >= vocab:
+                raise StepError(f"request {e.req_id!r}: token id outside [0, {vocab})")
+            hm[lay.tok_ids + t:lay.tok_ids + t + n] = toks
+            hm[lay.tok_pos + t:lay.tok_pos + t + n] = np.arange(start, start + n)
+            hm[lay.tok_req + t:lay.tok_req + t + n] = r
+            hm[lay.req_start + r] = t
+            hm[lay.req_len + r] = n
+            hm[lay.req_ctx + r] = start + n
+            slot = mgr.slot(e.req_id)
+            hm[lay.req_slot + r] = slot
+            for gi, mp in enumerate(lay.max_pages):
+                tab = mgr.table(e.req_id, gi)
+                o = lay.tables[gi] + r * mp
+                hm[o:o + len(tab)] = tab
+            for w in e.want:
+                hm[lay.logit_rows + w_i] = t + w
+                temps[w_i] = e.temperature
+                hm[lay.samp_topk + w_i] = e.top_k
+                seed = int(e.seed) & 0xFFFFFFFFFFFFFFFF
+                hm[lay.samp_seed_lo + w_i] = np.array(seed & 0xFFFFFFFF, dtype=np.uint32).view(np.int32)
+                hm[lay.samp_seed_hi + w_i] = np.array(seed >> 32, dtype=np.uint32).view(np.int32)
+                hm[lay.samp_pos + w_i] = start + w + 1     # position the new token will take
+                rows.append((e.req_id, w))
+                w_i += 1
+            host_batch.append((e.req_id, slot, start, n))
+            t += n
+        if lay.plan_ints:
+            self.ops.plan_attention(hm[lay.plan:lay.plan + lay.plan_ints], host_batch, T, R,
+                                    mgr.page_size)
+
+        # ---- device side -------------------------------------------------------------
+        key = (T, R, W, bool(sample))
+        dev = self._dev_meta.get(key[:3])
+        if dev is None:
+            dev = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
+            self._dev_meta[key[:3]] = dev
+        dev.copy_(host[:lay.total], non_blocking=True)
+        if self.cuda:
+            if self._copy_done is None:
+                self._copy_done = torch.cuda.Event()
+            self._copy_done.record()
+
+        cap = self._graphs.get(key) if self.use_graphs else None
+        if cap is not None:
+            cap.ctx.host = host_batch
+            cap.graph.replay()
+            logits, tokens = cap.logits, cap.tokens
+        else:
+            ctx = StepContext(self, lay, dev)
+            ctx.host = host_batch
+            if self.use_graphs and not self.model.state_shapes:
+                # run once eagerly (loads kernels, sizes buffers), then capture and replay
+                self._forward(ctx, sample)
+                torch.cuda.synchronize(self.device)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    logits, tokens = self._forward(ctx, sample)
+                self._graphs[key] = _Captured(graph, ctx, logits, tokens)
+                graph.replay()
+            else:
+                logits, tokens = self._forward(ctx, sample)
+
+        for e, start in zip(entries, starts):
+            mgr.commit(e.req_id, start + len(e.tokens))
+        self.steps_run += 1
+        if check_status and not sample:
+            self.check_status()
+        res = StepResult(
+            logits=None if logits is None else logits[:n_want],
+            tokens=None if tokens is None else tokens[:n_want],
+            rows=rows, n_tokens=n_tok)
+        return res
+
+    def _forward(self, ctx: StepContext, sample: bool):
+        logits = self.model.forward(ctx)
+        tokens = None
+        if sample and logits is not None:
+            tokens = ctx.buffer("sampled", (ctx.n_logit_rows,), torch.int32)
+            self.ops.sample(tokens, logits, ctx.samp_temp, ctx.samp_topk, ctx.samp_seed_lo,
+                            ctx.samp_seed_hi, ctx.samp_pos)
+        return logits, tokens
+
+    def check_status(self) -> None:
+        """Read the status word the kernels OR their refusals into (synchronises)."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            what = [msg for bit, msg in STATUS_BITS.items() if code & bit]
+            raise StepError("a kernel refused an index: " + "; ".join(what))
+
+
+@dataclass
+class _Captured:
+    graph: "torch.cuda.CUDAGraph"
+    ctx: StepContext
+    logits: torch.Tensor | None
+    tokens: torch.Tensor | None

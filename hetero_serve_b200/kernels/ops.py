@@ -1,0 +1,278 @@
+"""The kernel interface of the engine: thin, checked Python wrappers around the
+``extern "C"`` entry points of the CUDA library.
+
+Every operation writes into tensors the caller owns (nothing is allocated here),
+runs on the current CUDA stream and raises :class:`KernelError` for a size or
+type a kernel does not take.  There is no fallback: if the library cannot be
+built or loaded, constructing :class:`CudaOps` fails.
+
+``tests/plain_ops.py`` holds a plain PyTorch twin of each operation with the same
+signature; the kernel tests compare the two.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from dataclasses import dataclass
+
+import torch
+
+from . import build as _build
+
+ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "gelu_erf": 2}
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+@dataclass(frozen=True)
+class AttentionGeometry:
+    """Sizes an attention layer hands to the cache and attention kernels."""
+
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    page_size: int
+    num_pages: int
+    max_pages: int          # row length of the block table
+    q_off: int              # column of q / k / v in a row of the fused projection
+    k_off: int
+    v_off: int
+    qkv_stride: int
+    window: int = 0         # 0: every earlier key; w: the last w keys
+
+    def page_elems(self) -> int:
+        return 2 * self.n_kv_heads * self.page_size * self.head_dim
+
+
+_ERRORS = {-1: "unsupported size, type or option", -2: "bad argument"}
+
+_lib = None
+
+
+def load_library():
+    """Build if needed and open the CUDA library (once per process)."""
+    global _lib
+    if _lib is None:
+        path = _build.build()
+        try:
+            _lib = ctypes.CDLL(str(path))
+        except OSError as exc:
+            raise KernelError(f"cannot load {path}: {exc}") from None
+        _declare(_lib)
+    return _lib
+
+
+def _declare(lib) -> None:
+    P, I, F = c_void_p, c_int, c_float
+    sig = {
+        "hs_embed": [P, P, P, P, P, P, I, I, I, I, I, P, P],
+        "hs_layernorm": [P, P, P, P, P, I, I, F, I, P],
+        "hs_linear_simt": [P, P, P, P, P, I, I, I, I, I, I, P],
+        "hs_kv_append": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
+        "hs_attention_simt": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
+        "hs_argmax": [P, P, I, I, P],
+        "hs_sample": [P, P, P, P, P, P, P, I, I, P],
+    }
+    for name, argtypes in sig.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: {_ERRORS.get(code, code)}")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _want(t, name, dtype=None, dim=None, cuda=True):
+    if not isinstance(t, torch.Tensor):
+        raise KernelError(f"{name}: expected a tensor, got {type(t).__name__}")
+    if cuda and not t.is_cuda:
+        raise KernelError(f"{name}: must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: must be contiguous")
+    if dtype is not None:
+        ok = t.dtype in dtype if isinstance(dtype, (tuple, list, set)) else t.dtype == dtype
+        if not ok:
+            raise KernelError(f"{name}: dtype {t.dtype} not accepted (want {dtype})")
+    if dim is not None and t.dim() != dim:
+        raise KernelError(f"{name}: expected {dim} dimensions, got shape {tuple(t.shape)}")
+    return t
+
+
+_FLOATS = (torch.float32, torch.bfloat16)
+
+
+class CudaOps:
+    """The hand-written sm_100a kernels, one method per operation."""
+
+    name = "cuda"
+
+    def __init__(self):
+        if not torch.cuda.is_available():
+            raise KernelError("hetero_serve_b200 needs a CUDA device: its kernels have no CPU path")
+        self.lib = load_library()
+
+    @staticmethod
+    def _stream():
+        return torch.cuda.current_stream().cuda_stream
+
+    # -- embedding and norm -------------------------------------------------
+    def embed(self, x, ids, pos, req, wte, wpe, status):
+        """x[t] = wte[ids[t]] (+ wpe[pos[t]]); rows with req[t] < 0 become zero."""
+        _want(x, "x", torch.float32, 2)
+        _want(wte, "wte", _FLOATS, 2)
+        n, width = x.shape
+        for t, nm in ((ids, "ids"), (pos, "pos"), (req, "req")):
+            _want(t, nm, torch.int32, 1)
+            if t.shape[0] < n:
+                raise KernelError(f"{nm}: {t.shape[0]} entries for {n} rows")
+        if wte.shape[1] != width:
+            raise KernelError(f"wte width {wte.shape[1]} != x width {width}")
+        n_pos = 0
+        if wpe is not None:
+            _want(wpe, "wpe", wte.dtype, 2)
+            if wpe.shape[1] != width:
+                raise KernelError(f"wpe width {wpe.shape[1]} != x width {width}")
+            n_pos = wpe.shape[0]
+        _check(self.lib.hs_embed(_ptr(x), _ptr(ids), _ptr(pos), _ptr(req), _ptr(wte), _ptr(wpe),
+                                 n, width, wte.shape[0], n_pos, _DT[wte.dtype], _ptr(status),
+                                 self._stream()), "embed")
+
+    def layernorm(self, out, x, gamma, beta, eps, rows=None):
+        """out[i] = LayerNorm(x[rows[i]] if rows is given else x[i]) * gamma + beta."""
+        _want(out, "out", _FLOATS, 2)
+        _want(x, "x", torch.float32, 2)
+        _want(gamma, "gamma", torch.float32, 1)
+        _want(beta, "beta", torch.float32, 1)
+        n, width = out.shape
+        if x.shape[1] != width or gamma.shape[0] != width or beta.shape[0] != width:
+            raise KernelError("layernorm: widths of out, x, gamma, beta differ")
+        if rows is not None:
+            _want(rows, "rows", torch.int32, 1)
+            if rows.shape[0] < n:
+                raise KernelError("layernorm: fewer row indices than output rows")
+        elif x.shape[0] < n:
+            raise KernelError("layernorm: x has fewer rows than out")
+        _check(self.lib.hs_layernorm(_ptr(out), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(rows), n,
+                                     width, float(eps), _DT[out.dtype], self._stream()),
+               f"layernorm(width={width})")
+
+    # -- linear ---------------------------------------------------------------
+    def linear(self, out, a, w, bias=None, act="none", residual=None):
+        """out = act(a @ w.T + bias) (+ residual).  a [M,K], w [N,K], out [M,N].
+
+        ``residual`` is float32 [M,N] and may be ``out`` itself (accumulate in place)."""
+        _want(a, "a", _FLOATS, 2)
+        _want(w, "w", a.dtype, 2)
+        _want(out, "out", _FLOATS, 2)
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+            raise KernelError(f"linear: shapes a{tuple(a.shape)} w{tuple(w.shape)} "
+                              f"out{tuple(out.shape)} do not fit")
+        if a.dtype == torch.float32 and out.dtype != torch.float32:
+            raise KernelError("linear: float32 inputs give float32 outputs")
+        if bias is not None:
+            _want(bias, "bias", torch.float32, 1)
+            if bias.shape[0] != N:
+                raise KernelError("linear: bias length != N")
+        if residual is not None:
+            _want(residual, "residual", torch.float32, 2)
+            if tuple(residual.shape) != (M, N):
+                raise KernelError("linear: residual shape != out shape")
+        if act not in ACTIVATIONS:
+            raise KernelError(f"linear: unknown activation {act!r}")
+        self._linear(out, a, w, bias, ACTIVATIONS[act], residual, M, N, K)
+
+    def _linear(self, out, a, w, bias, act, residual, M, N, K):
+        _check(self.lib.hs_linear_simt(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual),
+                                       M, N, K, act, _DT[a.dtype], _DT[out.dtype],
+                                       self._stream()), f"linear(M={M},N={N},K={K})")
+
+    # -- cache and attention ------------------------------------------------------
+    def _attn_common(self, qkv, pool, table, tok_pos, tok_req, g, n):
+        _want(qkv, "qkv", _FLOATS, 2)
+        _want(pool, "pool", qkv.dtype)
+        _want(table, "table", torch.int32, 2)
+        _want(tok_pos, "tok_pos", torch.int32, 1)
+        _want(tok_req, "tok_req", torch.int32, 1)
+        if qkv.shape[0] < n or tok_pos.shape[0] < n or tok_req.shape[0] < n:
+            raise KernelError("attention: fewer rows than tokens")
+        if qkv.shape[1] != g.qkv_stride or table.shape[1] != g.max_pages:
+            raise KernelError("attention: geometry does not match the tensors")
+        if pool.numel() != g.num_pages * g.page_elems():
+            raise KernelError(f"attention: pool has {pool.numel()} elements, geometry wants "
+                              f"{g.num_pages * g.page_elems()}")
+        hd = g.head_dim
+        if (g.q_off + g.n_heads * hd > g.qkv_stride or g.k_off + g.n_kv_heads * hd > g.qkv_stride
+                or g.v_off + g.n_kv_heads * hd > g.qkv_stride):
+            raise KernelError("attention: q/k/v columns exceed the fused row")
+
+    def kv_append(self, pool, qkv, table, tok_pos, tok_req, g, status, n_tokens=None):
+        """Write each token's key and value rows into its page (rows with req < 0 are skipped)."""
+        n = qkv.shape[0] if n_tokens is None else n_tokens
+        self._attn_common(qkv, pool, table, tok_pos, tok_req, g, n)
+        _check(self.lib.hs_kv_append(_ptr(pool), _ptr(qkv), _ptr(table), _ptr(tok_pos),
+                                     _ptr(tok_req), n, g.n_heads, g.n_kv_heads, g.head_dim,
+                                     g.page_size, g.num_pages, g.max_pages, g.q_off, g.k_off,
+                                     g.v_off, g.qkv_stride, _DT[qkv.dtype], _ptr(status),
+                                     self._stream()),
+               f"kv_append(head_dim={g.head_dim})")
+
+    def attention(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan=None):
+        """out[t] = causal attention of token t's query over its request's pages.
+
+        ``plan`` may carry a batch's work lists for the specialised kernels; the general
+        kernel needs none."""
+        _want(out, "out", qkv.dtype, 2)
+        n = out.shape[0]
+        if out.shape[1] != g.n_heads * g.head_dim:
+            raise KernelError("attention: out width != n_heads * head_dim")
+        self._attn_common(qkv, pool, table, tok_pos, tok_req, g, n)
+        self._attention(out, qkv, pool, table, tok_pos, tok_req, g, float(scale), status, plan, n)
+
+    def _attention(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan, n):
+        _check(self.lib.hs_attention_simt(
+            _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req), n,
+            g.n_heads, g.n_kv_heads, g.head_dim, g.page_size, g.num_pages, g.max_pages, g.q_off,
+            g.k_off, g.v_off, g.qkv_stride, g.window, scale, _DT[qkv.dtype], _ptr(status),
+            self._stream()), f"attention(head_dim={g.head_dim}, heads={g.n_heads})")
+
+    # -- sampling ---------------------------------------------------------------
+    def argmax(self, out, logits):
+        _want(out, "out", torch.int32, 1)
+        _want(logits, "logits", torch.float32, 2)
+        rows, vocab = logits.shape
+        if out.shape[0] < rows:
+            raise KernelError("argmax: out shorter than the rows")
+        _check(self.lib.hs_argmax(_ptr(out), _ptr(logits), rows, vocab, self._stream()), "argmax")
+
+    def sample(self, out, logits, temperature, top_k, seed_lo, seed_hi, position):
+        """Per row: argmax if temperature <= 0, else a draw from softmax(logits/temperature)
+        restricted to the top_k largest when 0 < top_k < vocab."""
+        _want(out, "out", torch.int32, 1)
+        _want(logits, "logits", torch.float32, 2)
+        rows, vocab = logits.shape
+        _want(temperature, "temperature", torch.float32, 1)
+        for t, nm in ((top_k, "top_k"), (seed_lo, "seed_lo"), (seed_hi, "seed_hi"),
+                      (position, "position")):
+            _want(t, nm, torch.int32, 1)
+            if t.shape[0] < rows:
+                raise KernelError(f"sample: {nm} shorter than the rows")
+        if out.shape[0] < rows or temperature.shape[0] < rows:
+            raise KernelError("sample: out/temperature shorter than the rows")
+        _check(self.lib.hs_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(top_k),
+                                  _ptr(seed_lo), _ptr(seed_hi), _ptr(position), rows, vocab,
+                                  self._stream()), "sample")
