@@ -57,9 +57,19 @@ class StepResult:
     tokens: torch.Tensor | None          # [n_wanted] int32 on the device (if sampled)
     rows: list[tuple[Hashable, int]]     # (request, index among its tokens) per wanted row
     n_tokens: int = 0
+    _with_status: torch.Tensor | None = None
+    _runner: "Runner | None" = None
 
     def tokens_host(self) -> list[int]:
-        return [] if self.tokens is None else self.tokens.cpu().tolist()
+        """The sampled tokens as Python ints: one device-to-host copy that also brings the
+        kernels' status word, which is checked."""
+        if self._with_status is None:
+            return []
+        host = self._with_status.cpu().tolist()
+        n = self.tokens.shape[0]
+        if host[-1]:
+            self._runner.raise_status(host[-1])
+        return host[:n]
 
 
 @dataclass
@@ -392,28 +402,34 @@ class Runner:
         self.steps_run += 1
         if check_status and not sample:
             self.check_status()
-        res = StepResult(
+        return StepResult(
             logits=None if logits is None else logits[:n_want],
             tokens=None if tokens is None else tokens[:n_want],
-            rows=rows, n_tokens=n_tok)
-        return res
+            rows=rows, n_tokens=n_tok,
+            _with_status=None if tokens is None else tokens, _runner=self)
 
     def _forward(self, ctx: StepContext, sample: bool):
         logits = self.model.forward(ctx)
         tokens = None
         if sample and logits is not None:
-            tokens = ctx.buffer("sampled", (ctx.n_logit_rows,), torch.int32)
+            # one extra element carries the status word, so that one copy brings both back
+            W = ctx.n_logit_rows
+            tokens = ctx.buffer("sampled", (W + 1,), torch.int32)
             self.ops.sample(tokens, logits, ctx.samp_temp, ctx.samp_topk, ctx.samp_seed_lo,
                             ctx.samp_seed_hi, ctx.samp_pos)
+            tokens[W:].copy_(self.status)
         return logits, tokens
 
     def check_status(self) -> None:
         """Read the status word the kernels OR their refusals into (synchronises)."""
         code = int(self.status.item())
         if code:
-            self.status.zero_()
-            what = [msg for bit, msg in STATUS_BITS.items() if code & bit]
-            raise StepError("a kernel refused an index: " + "; ".join(what))
+            self.raise_status(code)
+
+    def raise_status(self, code: int) -> None:
+        self.status.zero_()
+        what = [msg for bit, msg in STATUS_BITS.items() if code & bit]
+        raise StepError("a kernel refused an index: " + "; ".join(what))
 
 
 @dataclass
