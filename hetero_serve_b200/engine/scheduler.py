@@ -25,7 +25,9 @@ What happens when pages run out — decided here:
    until pages for its whole prompt are obtainable; a prompt that could never fit the
    pool is refused when it is submitted;
 2. while decoding: preempt the newest running request and try again; a request that
-   preempts itself sits the step out.  A preempted request goes to the FRONT of the
+   preempts itself sits the step out.  A request that has outgrown the whole pool on its
+   own (nothing else is live and it still cannot be admitted) ends with the tokens it
+   has, ``finish_reason == "out_of_pages"``.  A preempted request goes to the FRONT of the
    waiting queue, keeps its sampled tokens, and is prefilled again over prompt + outputs
    (all but the last token, which decoding feeds).  Because the random draw of a token
    depends only on (seed, position), a preempted request continues exactly as it would
@@ -282,6 +284,14 @@ class Scheduler:
         if not planned:
             if self.waiting and not self.active:
                 head = self.waiting[0]
+                if head.output_ids:
+                    # it outgrew the whole pool while generating: end it with what it has
+                    self.waiting.popleft()
+                    head.state, head.finish_reason = SeqState.DONE, "out_of_pages"
+                    head.t_done = self.clock()
+                    self.finished.append(head)
+                    self.stats.finished += 1
+                    return [head]
                 raise RequestRefused(
                     f"request {head.req_id!r} cannot be admitted although nothing else is "
                     f"running: the pool is too small for it")

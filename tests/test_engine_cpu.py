@@ -1,0 +1,104 @@
+"""The step function, the cache and the replay driver without a GPU: the kernels are
+replaced by their plain PyTorch twins (tests/plain_ops.py) on CPU tensors, everything
+else — model assembly, metadata, pages, block tables — is the product's own code."""
+
+import pytest
+import torch
+
+import plain_ops
+import traces
+from hetero_serve_b200.engine.loading import load_model
+from hetero_serve_b200.engine.replay import replay
+from hetero_serve_b200.engine.step import Runner, StepEntry, StepError
+from hetero_serve_b200.cache import OutOfPages
+
+TOL = 2e-5
+
+
+def _requests(tiny):
+    lens = {"tiny_a": (5, 17, 33, 70), "tiny_b": (1, 16, 31, 70, 45)}[tiny.name]
+    return {f"r{i}": tiny.tokens(n, 100 + i) for i, n in enumerate(lens)}
+
+
+def _replay(tiny, steps, tmp_path, max_tokens):
+    out = tmp_path / "out"
+    out.mkdir(exist_ok=True)
+    import io
+    rep = io.StringIO()
+    assert replay(model_dir=tiny.dir, dtype="float32", out_dir=out, max_tokens=max_tokens,
+                  lines=traces.lines_of(steps), report=rep, device="cpu",
+                  ops=plain_ops.PlainOps()) == 0
+    assert rep.getvalue().split() == [w for s in steps for w in ("done", str(s["step"]))]
+    return out
+
+
+@pytest.mark.parametrize("driver", ["whole", "tail", "portions"])
+def test_cuts_agree_with_the_plain_model(tiny, tmp_path, driver):
+    reqs = _requests(tiny)
+    make = {"whole": traces.whole, "tail": traces.tail_one_by_one, "portions": traces.portions}
+    steps, index = make[driver](reqs)
+    out = _replay(tiny, steps, tmp_path, max_tokens=128)
+    got = traces.collect(out, index, tiny.config["vocab_size"])
+    err, where = traces.worst_error(got, {r: tiny.logits(t) for r, t in reqs.items()})
+    assert err < TOL, (err, where)
+
+
+def test_mixed_batches_with_page_reuse(tiny, tmp_path):
+    reqs = {f"r{i}": tiny.tokens(n, 200 + i) for i, n in
+            enumerate((40, 9, 64, 23, 70, 3, 55, 31))}
+    steps, index, peak = traces.mixed(reqs, seed=1)
+    assert peak <= 4 * 128
+    out = _replay(tiny, steps, tmp_path, max_tokens=peak)      # so few pages that they are reused
+    got = traces.collect(out, index, tiny.config["vocab_size"])
+    assert len(got) > 40
+    err, where = traces.worst_error(got, {r: tiny.logits(t) for r, t in reqs.items()})
+    assert err < TOL, (err, where)
+
+
+def _runner(tiny, pages=8, **kw):
+    model, _ = load_model(tiny.dir, "float32", "cpu")
+    return Runner(model, num_pages=pages, page_size=16, max_requests=4, dtype=torch.float32,
+                  device="cpu", ops=plain_ops.PlainOps(), **kw)
+
+
+def test_step_refuses_what_it_cannot_run(tiny_models):
+    tiny = tiny_models["tiny_a"]
+    rn = _runner(tiny, pages=2)
+    with pytest.raises(StepError, match="twice"):
+        rn.step([StepEntry("a", [1]), StepEntry("a", [2])])
+    with pytest.raises(StepError, match="outside"):
+        rn.step([StepEntry("a", [1, 2], want=[2])])
+    with pytest.raises(StepError, match="token id"):
+        rn.step([StepEntry("a", [512])])
+    with pytest.raises(StepError, match="no tokens"):
+        rn.step([StepEntry("a", [])])
+    with pytest.raises(OutOfPages):
+        rn.step([StepEntry("b", [1] * 33)])
+    rn2 = _runner(tiny, pages=16)
+    with pytest.raises(StepError, match="exceed"):
+        rn2.step([StepEntry("a", [1] * 129)])
+    rn.manager.check()
+
+
+def test_pages_are_reused_with_stale_contents(tiny_models):
+    """A page that held another request's keys must not leak into the next one."""
+    tiny = tiny_models["tiny_b"]
+    rn = _runner(tiny, pages=3)
+    a, b = tiny.tokens(40, 1), tiny.tokens(37, 2)
+    rn.step([StepEntry("a", a)])
+    rn.close("a")
+    res = rn.step([StepEntry("b", b, want=[36])])
+    assert (res.logits[0].double() - tiny.logits(b)[36]).abs().max() < TOL
+
+
+def test_sampling_through_the_step_matches_the_plain_sampler(tiny_models):
+    import plain_gpt2
+    tiny = tiny_models["tiny_b"]
+    rn = _runner(tiny)
+    toks = tiny.tokens(12, 9)
+    res = rn.step([StepEntry("a", toks, want=[11], temperature=0.8, top_k=40, seed=77),
+                   StepEntry("b", toks[:5], want=[4], temperature=0.0)], sample=True)
+    got = res.tokens_host()
+    u = plain_gpt2.uniform_for(77, 12)
+    assert got[0] == plain_gpt2.sample_token(tiny.logits(toks)[11], 0.8, 40, u)
+    assert got[1] == int(torch.argmax(tiny.logits(toks[:5])[4]))

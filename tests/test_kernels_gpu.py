@@ -1,0 +1,326 @@
+"""Each CUDA kernel alone against its plain PyTorch twin (tests/plain_ops.py, float64), at
+sizes other than the tiny models': widths and vocabularies that are no power of two, head
+sizes from 16 to 256, grouped heads, windows, pages of 16 and 32 tokens."""
+
+import pytest
+import torch
+
+import plain_ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from hetero_serve_b200.kernels import CudaOps
+    return CudaOps()
+
+
+@pytest.fixture(scope="module")
+def plain():
+    return plain_ops.PlainOps()
+
+
+def _status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def _i32(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+# ------------------------------------------------------------------ embedding, norm
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(ops, plain, dtype):
+    torch.manual_seed(0)
+    V, P, E, n = 777, 50, 200, 13
+    wte = torch.randn(V, E, device=DEV).to(dtype)
+    wpe = torch.randn(P, E, device=DEV).to(dtype)
+    ids = torch.randint(0, V, (n,), device=DEV, dtype=torch.int32)
+    pos = torch.randint(0, P, (n,), device=DEV, dtype=torch.int32)
+    req = _i32([0, 0, 1, -1, 2, 2, 2, -1, 3, 3, 3, 3, 0])
+    x = torch.full((n, E), 9.0, device=DEV)
+    ref = torch.empty(n, E, device=DEV, dtype=torch.float64)
+    st = _status()
+    ops.embed(x, ids, pos, req, wte, wpe, st)
+    plain.embed(ref, ids, pos, req, wte, wpe, st)
+    assert (x.double() - ref).abs().max() < 1e-6
+    assert x[3].abs().max() == 0 and st.item() == 0          # padding rows are zeroed
+    ops.embed(x, ids, pos, req, wte, None, st)                # no position table
+    plain.embed(ref, ids, pos, req, wte, None, st)
+    assert (x.double() - ref).abs().max() < 1e-6
+
+
+def test_embed_flags_bad_indices_instead_of_reading_them(ops):
+    wte = torch.randn(10, 32, device=DEV)
+    wpe = torch.randn(4, 32, device=DEV)
+    x = torch.empty(3, 32, device=DEV)
+    st = _status()
+    ops.embed(x, _i32([1, 10, 2]), _i32([0, 1, 4]), _i32([0, 0, 0]), wte, wpe, st)
+    assert st.item() == 1 | 2 and x[1].abs().max() == 0 and x[2].abs().max() == 0
+    assert torch.allclose(x[0], wte[1] + wpe[0])
+
+
+@pytest.mark.parametrize("width", [16, 100, 1600, 5000])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_layernorm(ops, plain, width, dtype):
+    torch.manual_seed(width)
+    x = torch.randn(19, width, device=DEV) * 7 + 3          # large mean: centring matters
+    g, b = torch.randn(width, device=DEV), torch.randn(width, device=DEV)
+    out = torch.empty(19, width, device=DEV, dtype=dtype)
+    ref = torch.empty(19, width, device=DEV, dtype=torch.float64)
+    ops.layernorm(out, x, g, b, 1e-6)
+    plain.layernorm(ref, x, g, b, 1e-6)
+    tol = 5e-6 if dtype == torch.float32 else 4e-2
+    assert (out.double() - ref).abs().max() < tol
+    rows = _i32([18, 0, 7])
+    out2 = torch.empty(3, width, device=DEV, dtype=dtype)
+    ops.layernorm(out2, x, g, b, 1e-6, rows)
+    assert torch.equal(out2, out[rows.long()])               # a row's result is its own
+
+
+def test_layernorm_refuses_rows_that_do_not_fit_shared_memory(ops):
+    from hetero_serve_b200.kernels import KernelError
+    w = 60000
+    x = torch.zeros(1, w, device=DEV)
+    with pytest.raises(KernelError, match="unsupported"):
+        ops.layernorm(torch.empty(1, w, device=DEV), x, torch.ones(w, device=DEV),
+                      torch.zeros(w, device=DEV), 1e-5)
+
+
+# ------------------------------------------------------------------ linear
+SHAPES = [(1, 50, 24), (7, 130, 100), (64, 192, 320), (200, 1000, 96), (33, 257, 515)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("act", ["none", "gelu_tanh", "gelu_erf"])
+def test_linear(ops, plain, M, N, K, dtype, act):
+    torch.manual_seed(M * N + K)
+    a = torch.randn(M, K, device=DEV).to(dtype)
+    w = (torch.randn(N, K, device=DEV) / K ** 0.5).to(dtype)
+    bias = torch.randn(N, device=DEV)
+    out = torch.empty(M, N, device=DEV, dtype=dtype)
+    ref = torch.empty(M, N, device=DEV, dtype=torch.float64)
+    ops.linear(out, a, w, bias, act=act)
+    plain.linear(ref, a, w, bias, act=act)
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    assert (out.double() - ref).abs().max() < tol
+    # accumulate into a float32 residual in place; no bias
+    res = torch.randn(M, N, device=DEV)
+    acc = res.clone()
+    ops.linear(acc, a, w, None, act=act, residual=acc)
+    plain.linear(ref, a, w, None, act=act, residual=res)
+    assert (acc.double() - ref).abs().max() < (2e-5 if dtype == torch.float32 else 2e-3 * K ** 0.5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_linear_rows_do_not_depend_on_the_batch(ops, dtype):
+    torch.manual_seed(5)
+    a = torch.randn(150, 96, device=DEV).to(dtype)
+    w = torch.randn(1000, 96, device=DEV).to(dtype)
+    full = torch.empty(150, 1000, device=DEV, dtype=dtype)
+    ops.linear(full, a, w)
+    for lo, hi in ((0, 1), (63, 66), (149, 150)):
+        part = torch.empty(hi - lo, 1000, device=DEV, dtype=dtype)
+        ops.linear(part, a[lo:hi].contiguous(), w)
+        assert torch.equal(part, full[lo:hi])
+
+
+def test_linear_checks_its_arguments(ops):
+    from hetero_serve_b200.kernels import KernelError
+    a = torch.randn(4, 8, device=DEV)
+    w = torch.randn(6, 8, device=DEV)
+    with pytest.raises(KernelError, match="do not fit"):
+        ops.linear(torch.empty(4, 5, device=DEV), a, w)
+    with pytest.raises(KernelError, match="dtype"):
+        ops.linear(torch.empty(4, 6, device=DEV), a, w.bfloat16())
+    with pytest.raises(KernelError, match="CUDA tensor"):
+        ops.linear(torch.empty(4, 6), a.cpu(), w.cpu())
+    with pytest.raises(KernelError, match="contiguous"):
+        ops.linear(torch.empty(4, 6, device=DEV), a, torch.randn(8, 6, device=DEV).t())
+
+
+# ------------------------------------------------------------------ cache and attention
+def _attention_case(H, HK, D, PS, lens, new, window=0, dtype=torch.float32, seed=0, scramble=True):
+    """Requests with ``lens[r]`` tokens after the step, of which the last ``new[r]`` are in
+    the batch.  Earlier keys/values are laid into pages directly."""
+    from hetero_serve_b200.kernels import AttentionGeometry
+    g_ = torch.Generator(device="cpu").manual_seed(seed)
+    R = len(lens)
+    max_pages = max(-(-n // PS) for n in lens) + 1
+    n_pages = sum(-(-n // PS) for n in lens) + 3
+    perm = torch.randperm(n_pages, generator=g_).tolist() if scramble else list(range(n_pages))
+    table = torch.full((R, max_pages), -1, dtype=torch.int32)
+    it = iter(perm)
+    for r, n in enumerate(lens):
+        for i in range(-(-n // PS)):
+            table[r, i] = next(it)
+    W = (H + 2 * HK) * D
+    geom = AttentionGeometry(H, HK, D, PS, n_pages, max_pages, 0, H * D, (H + HK) * D, W, window)
+    T = sum(new)
+    qkv = torch.randn(T, W, generator=g_).to(dtype)
+    pool = torch.full((n_pages, 2, HK, PS, D), float("nan")).to(dtype)   # unwritten slots poison
+    tok_pos, tok_req = [], []
+    for r, (n, k) in enumerate(zip(lens, new)):
+        past = torch.randn(n - k, 2, HK, D, generator=g_).to(dtype)
+        for p in range(n - k):
+            pool[table[r, p // PS], :, :, p % PS, :] = past[p]
+        tok_pos += list(range(n - k, n))
+        tok_req += [r] * k
+    return (geom, qkv.to(DEV), pool.to(DEV), table.to(DEV), _i32(tok_pos), _i32(tok_req))
+
+
+CASES = [
+    # H, HK, D,  PS, lens,            new,           window
+    (4, 4, 16, 16, [5, 17, 33], [5, 17, 33], 0),            # whole prompts
+    (3, 3, 32, 16, [40, 16, 70, 1], [1, 1, 1, 1], 0),       # decode, a page edge (16), one token
+    (6, 2, 64, 16, [50, 23], [7, 23], 0),                   # grouped heads, portion + prompt
+    (2, 1, 128, 32, [100, 64], [3, 1], 0),                  # pages of 32
+    (1, 1, 256, 16, [35], [2], 0),                          # the largest head
+    (5, 5, 48, 16, [90, 31], [30, 1], 0),                   # head size 48, five heads
+    (4, 2, 32, 16, [80, 40, 20], [10, 1, 20], 24),          # a window of 24
+    (2, 2, 16, 16, [48], [48], 16),                         # window == page
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=[f"H{c[0]}k{c[1]}D{c[2]}P{c[3]}w{c[6]}" for c in CASES])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_kv_append_and_attention(ops, plain, case, dtype):
+    H, HK, D, PS, lens, new, window = case
+    geom, qkv, pool, table, tok_pos, tok_req = _attention_case(H, HK, D, PS, lens, new, window,
+                                                               dtype, seed=D + H)
+    st = _status()
+    pool_ref = pool.clone()
+    ops.kv_append(pool, qkv, table, tok_pos, tok_req, geom, st)
+    plain.kv_append(pool_ref, qkv, table, tok_pos, tok_req, geom, st)
+    assert torch.equal(torch.nan_to_num(pool, nan=123.0), torch.nan_to_num(pool_ref, nan=123.0))
+    T = qkv.shape[0]
+    out = torch.empty(T, H * D, device=DEV, dtype=dtype)
+    ref = torch.empty(T, H * D, device=DEV, dtype=torch.float64)
+    scale = 0.37 / D ** 0.5
+    ops.attention(out, qkv, pool, table, tok_pos, tok_req, geom, scale, st)
+    plain.attention(ref, qkv, pool, table, tok_pos, tok_req, geom, scale, st)
+    assert st.item() == 0
+    assert torch.isfinite(out).all()           # no poisoned (unwritten or foreign) slot was read
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert (out.double() - ref).abs().max() < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("far", [0, 15, 16, 255, 256, 511, 600])
+def test_one_far_key_among_hundreds_decides_the_output(ops, dtype, far):
+    """Random scores are nearly uniform, which hides a key that is dropped or misplaced.
+    Here one key's score stands out, so the output must be that key's value row."""
+    H, D, PS, n = 2, 64, 16, 640
+    geom, qkv, pool, table, tok_pos, tok_req = _attention_case(H, H, D, PS, [n], [1], 0, dtype, 3)
+    st = _status()
+    ops.kv_append(pool, qkv, table, tok_pos, tok_req, geom, st)
+    pv = pool.view(geom.num_pages, 2, H, PS, D)
+    q = qkv[0, :H * D].view(H, D).float()
+    page, slot = int(table[0, far // PS]), far % PS
+    pv[page, 0, :, slot, :] = (q / q.norm(dim=-1, keepdim=True) * 40).to(dtype)  # score ~ 40*|q|
+    out = torch.empty(1, H * D, device=DEV, dtype=dtype)
+    ops.attention(out, qkv, pool, table, tok_pos, tok_req, geom, 1.0, st)
+    want = pv[page, 1, :, slot, :].reshape(1, H * D).float()
+    assert (out.float() - want).abs().max() < (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+def test_window_edge_is_exact(ops):
+    """With a window w the key at p - w is out and the key at p - w + 1 is in."""
+    H, D, PS, n, w = 1, 16, 16, 50, 20
+    geom, qkv, pool, table, tok_pos, tok_req = _attention_case(H, H, D, PS, [n], [1], w,
+                                                               torch.float32, 4)
+    st = _status()
+    ops.kv_append(pool, qkv, table, tok_pos, tok_req, geom, st)
+    pv = pool.view(geom.num_pages, 2, H, PS, D)
+    q = qkv[0, :D].float()
+    big = q / q.norm() * 60
+    out = torch.empty(1, D, device=DEV)
+    p = n - 1
+    for key, inside in ((p - w, False), (p - w + 1, True)):
+        page, slot = int(table[0, key // PS]), key % PS
+        saved = pv[page, 0, 0, slot].clone()
+        pv[page, 0, 0, slot] = big
+        ops.attention(out, qkv, pool, table, tok_pos, tok_req, geom, 1.0, st)
+        hit = (out[0] - pv[page, 1, 0, slot]).abs().max() < 1e-4
+        assert bool(hit) == inside
+        pv[page, 0, 0, slot] = saved
+
+
+def test_attention_flags_a_bad_page(ops):
+    geom, qkv, pool, table, tok_pos, tok_req = _attention_case(2, 2, 16, 16, [20], [1])
+    table[0, 0] = geom.num_pages + 5
+    st = _status()
+    out = torch.empty(1, 32, device=DEV)
+    ops.attention(out, qkv, pool, table, tok_pos, tok_req, geom, 1.0, st)
+    assert st.item() & 4
+
+
+def test_attention_refuses_head_sizes_it_does_not_take(ops):
+    from hetero_serve_b200.kernels import AttentionGeometry, KernelError
+    for D in (24, 272):
+        g = AttentionGeometry(1, 1, D, 16, 2, 2, 0, D, 2 * D, 3 * D)
+        qkv = torch.zeros(1, 3 * D, device=DEV)
+        pool = torch.zeros(2, 2, 1, 16, D, device=DEV)
+        with pytest.raises(KernelError, match="unsupported"):
+            ops.attention(torch.empty(1, D, device=DEV), qkv, pool,
+                          torch.zeros(1, 2, dtype=torch.int32, device=DEV), _i32([0]), _i32([0]),
+                          g, 1.0, _status())
+
+
+# ------------------------------------------------------------------ sampling
+@pytest.mark.parametrize("vocab", [17, 1000, 50257])
+def test_argmax_lowest_index_on_ties(ops, vocab):
+    torch.manual_seed(vocab)
+    lg = torch.randn(5, vocab, device=DEV)
+    lg[1, vocab - 1] = lg[1, 3] = 50.0
+    lg[2, :] = 1.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops.argmax(out, lg)
+    want = [int(torch.argmax(lg[0])), 3, 0, int(torch.argmax(lg[3])), int(torch.argmax(lg[4]))]
+    assert out.tolist() == want
+
+
+@pytest.mark.parametrize("vocab,top_k", [(1000, 0), (1000, 1), (1000, 40), (50257, 0),
+                                         (50257, 50), (37, 36), (37, 100)])
+def test_sample_matches_the_plain_sampler(ops, plain, vocab, top_k):
+    torch.manual_seed(vocab + top_k)
+    rows = 8
+    lg = torch.randn(rows, vocab, device=DEV) * 2.5
+    lg[5, 7] = lg[5, 2] = lg[5].max() + 1                   # a tie at the top
+    temp = torch.tensor([0.8, 0.0, 1.7, 0.3, 1.0, 1.0, 0.05, 3.0], device=DEV)
+    k = torch.full((rows,), top_k, dtype=torch.int32, device=DEV)
+    lo = torch.arange(rows, dtype=torch.int32, device=DEV) * 1000003
+    hi = torch.arange(rows, dtype=torch.int32, device=DEV)
+    mism = 0
+    for pos in range(6):
+        p = torch.full((rows,), pos + 11, dtype=torch.int32, device=DEV)
+        out = torch.empty(rows, dtype=torch.int32, device=DEV)
+        ref = torch.empty(rows, dtype=torch.int32)
+        ops.sample(out, lg, temp, k, lo, hi, p)
+        plain.sample(ref, lg.cpu(), temp.cpu(), k.cpu(), lo.cpu(), hi.cpu(), p.cpu())
+        mism += sum(int(a != b) for a, b in zip(out.tolist(), ref.tolist()))
+    # float32 against float64 cumulative sums may disagree when u lands within rounding of a
+    # boundary; with 48 draws that is not expected at all
+    assert mism == 0
+
+
+def test_sample_distribution(ops):
+    """Over many positions the draws follow softmax(logits / T) restricted to the top k."""
+    vocab, n = 12, 4000
+    lg = torch.tensor([[0.1, 2.0, -1.0, 0.5, 1.5, 1.5, -3.0, 0.0, 0.7, 1.1, -0.4, 0.9]], device=DEV)
+    lgs = lg.expand(n, vocab).contiguous()
+    temp = torch.full((n,), 0.7, device=DEV)
+    k = torch.full((n,), 5, dtype=torch.int32, device=DEV)
+    z = torch.zeros(n, dtype=torch.int32, device=DEV)
+    pos = torch.arange(n, dtype=torch.int32, device=DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample(out, lgs, temp, k, z + 5, z, pos)
+    keep = torch.topk(lg[0], 5).indices
+    p = torch.zeros(vocab, device=DEV)
+    p[keep] = torch.softmax(lg[0, keep] / 0.7, 0)
+    freq = torch.bincount(out.long(), minlength=vocab).float() / n
+    assert (freq - p).abs().max() < 0.03
+    assert freq[p == 0].sum() == 0
