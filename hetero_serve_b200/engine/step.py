@@ -21,6 +21,7 @@ word, or nothing at all when the caller only wants device logits.  With
 
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Hashable, Sequence
 
@@ -390,8 +391,18 @@ class Runner:
                 self._forward(ctx, sample)
                 torch.cuda.synchronize(self.device)
                 graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    logits, tokens = self._forward(ctx, sample)
+                # An object freed by the garbage collector in the middle of a capture (an
+                # older runner's graphs, say) would invalidate it: collect first, then hold
+                # the collector off until the capture has ended.
+                gc.collect()
+                gc_was_on = gc.isenabled()
+                gc.disable()
+                try:
+                    with torch.cuda.graph(graph):
+                        logits, tokens = self._forward(ctx, sample)
+                finally:
+                    if gc_was_on:
+                        gc.enable()
                 self._graphs[key] = _Captured(graph, ctx, logits, tokens)
                 graph.replay()
             else:
