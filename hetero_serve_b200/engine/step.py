@@ -237,6 +237,7 @@ class Runner:
         self._layouts: dict[tuple, Layout] = {}
         self._copy_done = None
         self.steps_run = 0
+        self.kernel_launches = 0      # kernels of this package launched by steps so far
 
     # -- requests ---------------------------------------------------------------
     def open(self, req_id, token_ids=None):
@@ -382,6 +383,7 @@ class Runner:
         if cap is not None:
             cap.ctx.host = host_batch
             cap.graph.replay()
+            self.kernel_launches += cap.n_launches
             logits, tokens = cap.logits, cap.tokens
         else:
             ctx = StepContext(self, lay, dev)
@@ -397,16 +399,21 @@ class Runner:
                 gc.collect()
                 gc_was_on = gc.isenabled()
                 gc.disable()
+                before = getattr(self.ops, "launches", 0)
                 try:
                     with torch.cuda.graph(graph):
                         logits, tokens = self._forward(ctx, sample)
                 finally:
                     if gc_was_on:
                         gc.enable()
-                self._graphs[key] = _Captured(graph, ctx, logits, tokens)
+                n_launch = getattr(self.ops, "launches", 0) - before
+                self._graphs[key] = _Captured(graph, ctx, logits, tokens, n_launch)
                 graph.replay()
+                self.kernel_launches += 2 * n_launch
             else:
+                before = getattr(self.ops, "launches", 0)
                 logits, tokens = self._forward(ctx, sample)
+                self.kernel_launches += getattr(self.ops, "launches", 0) - before
 
         for e, start in zip(entries, starts):
             mgr.commit(e.req_id, start + len(e.tokens))
@@ -449,3 +456,4 @@ class _Captured:
     ctx: StepContext
     logits: torch.Tensor | None
     tokens: torch.Tensor | None
+    n_launches: int = 0

@@ -123,6 +123,7 @@ class CudaOps:
         if not torch.cuda.is_available():
             raise KernelError("hetero_serve_b200 needs a CUDA device: its kernels have no CPU path")
         self.lib = load_library()
+        self.launches = 0          # kernels launched through this object (graph captures count once)
 
     @staticmethod
     def _stream():
@@ -146,6 +147,7 @@ class CudaOps:
             if wpe.shape[1] != width:
                 raise KernelError(f"wpe width {wpe.shape[1]} != x width {width}")
             n_pos = wpe.shape[0]
+        self.launches += 1
         _check(self.lib.hs_embed(_ptr(x), _ptr(ids), _ptr(pos), _ptr(req), _ptr(wte), _ptr(wpe),
                                  n, width, wte.shape[0], n_pos, _DT[wte.dtype], _ptr(status),
                                  self._stream()), "embed")
@@ -165,6 +167,7 @@ class CudaOps:
                 raise KernelError("layernorm: fewer row indices than output rows")
         elif x.shape[0] < n:
             raise KernelError("layernorm: x has fewer rows than out")
+        self.launches += 1
         _check(self.lib.hs_layernorm(_ptr(out), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(rows), n,
                                      width, float(eps), _DT[out.dtype], self._stream()),
                f"layernorm(width={width})")
@@ -197,6 +200,7 @@ class CudaOps:
         self._linear(out, a, w, bias, ACTIVATIONS[act], residual, M, N, K)
 
     def _linear(self, out, a, w, bias, act, residual, M, N, K):
+        self.launches += 1
         _check(self.lib.hs_linear_simt(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual),
                                        M, N, K, act, _DT[a.dtype], _DT[out.dtype],
                                        self._stream()), f"linear(M={M},N={N},K={K})")
@@ -224,6 +228,7 @@ class CudaOps:
         """Write each token's key and value rows into its page (rows with req < 0 are skipped)."""
         n = qkv.shape[0] if n_tokens is None else n_tokens
         self._attn_common(qkv, pool, table, tok_pos, tok_req, g, n)
+        self.launches += 1
         _check(self.lib.hs_kv_append(_ptr(pool), _ptr(qkv), _ptr(table), _ptr(tok_pos),
                                      _ptr(tok_req), n, g.n_heads, g.n_kv_heads, g.head_dim,
                                      g.page_size, g.num_pages, g.max_pages, g.q_off, g.k_off,
@@ -244,6 +249,7 @@ class CudaOps:
         self._attention(out, qkv, pool, table, tok_pos, tok_req, g, float(scale), status, plan, n)
 
     def _attention(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan, n):
+        self.launches += 1
         _check(self.lib.hs_attention_simt(
             _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req), n,
             g.n_heads, g.n_kv_heads, g.head_dim, g.page_size, g.num_pages, g.max_pages, g.q_off,
@@ -257,6 +263,7 @@ class CudaOps:
         rows, vocab = logits.shape
         if out.shape[0] < rows:
             raise KernelError("argmax: out shorter than the rows")
+        self.launches += 1
         _check(self.lib.hs_argmax(_ptr(out), _ptr(logits), rows, vocab, self._stream()), "argmax")
 
     def sample(self, out, logits, temperature, top_k, seed_lo, seed_hi, position):
@@ -273,6 +280,7 @@ class CudaOps:
                 raise KernelError(f"sample: {nm} shorter than the rows")
         if out.shape[0] < rows or temperature.shape[0] < rows:
             raise KernelError("sample: out/temperature shorter than the rows")
+        self.launches += 1
         _check(self.lib.hs_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(top_k),
                                   _ptr(seed_lo), _ptr(seed_hi), _ptr(position), rows, vocab,
                                   self._stream()), "sample")
