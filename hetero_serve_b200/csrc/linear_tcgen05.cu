@@ -1,0 +1,424 @@
+// bfloat16 linear layer on the 5th-generation tensor cores (tcgen05) of sm_100a.
+//
+//   out[m, n] = act( sum_k a[m, k] * w[n, k] + bias[n] ) (+ residual[m, n])
+//
+// a [M, K] and w [N, K] are bfloat16 with K contiguous ("K-major" for both operands), the
+// accumulator is float32 in tensor memory (TMEM), out is bfloat16 or float32.  It replaces the
+// library matrix products of the reference (`h @ attn_w + attn_b`, `gelu(x @ fc_w + fc_b)`,
+// `x + (... @ proj_w + proj_b)`, `ln_f(x) @ wte.T`: heteroserve/model/torch_engine.py:77-87,122,139)
+// with the bias, the activation and the float32 residual sum fused into the epilogue.
+//
+// One CTA computes one 128 x BN tile of `out`:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of a [128 x 64] tile of `a` and a
+//               [BN x 64] tile of `w` per stage, 128-byte swizzle, completion on an mbarrier;
+//   warp 1      allocates TMEM, then one elected thread issues tcgen05.mma (M=128, N=BN, K=16,
+//               kind::f16, bf16 inputs, f32 accumulate), four per stage, and commits each
+//               stage's completion to the stage's "empty" barrier;
+//   warps 2..5  epilogue: tcgen05.ld of the accumulator (lane = row, 32 columns at a time),
+//               bias / activation / residual in float32, stores.
+// Rows and columns beyond M, N and K are zero-filled by TMA and never stored.
+//
+// Every wait on an mbarrier is bounded: after HS_SPIN_LIMIT failed polls the thread sets
+// HS_STATUS_PIPELINE_TIMEOUT in the status word and leaves the loop; the kernel then runs to
+// its end (no store of that tile is trusted; the host raises on the status bit), frees its
+// TMEM and returns.  Nothing can spin forever.
+//
+// The k-blocks of a tile are accumulated in index order by one MMA chain, whatever M is, so an
+// output row does not depend on which other rows share its tile.
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace hs {
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 64;          // 64 bf16 = 128 bytes = one swizzle row
+constexpr int TC_UMMA_K = 16;
+constexpr uint32_t HS_SPIN_LIMIT = 20u * 1000u * 1000u;
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait.  Returns false (and records it) when the limit is hit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < HS_SPIN_LIMIT; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  atomicOr(status, HS_STATUS_PIPELINE_TIMEOUT);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_dst)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+      "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile laid out by TMA with 128-byte swizzle:
+// rows of 128 bytes, groups of 8 rows 1024 bytes apart (stride byte offset), descriptor
+// version 1 (sm_100), layout type 2 = SWIZZLE_128B.  The tile base is 1024-byte aligned.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);        // start address, bits [0,14)
+  d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024u >> 4) << 32;               // stride byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                          // descriptor version
+  d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor for kind::f16: D = f32, A = B = bf16, both K-major, M x N.
+__host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
+  return (1u << 4)                 // c_format = F32
+         | (1u << 7)               // a_format = BF16
+         | (1u << 10)              // b_format = BF16
+         | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+template <int BN, int STAGES>
+struct TcSmem {
+  static constexpr int A_BYTES = TC_BM * TC_BK * 2;
+  static constexpr int B_BYTES = BN * TC_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;  // + alignment slack
+};
+
+template <int BN, int STAGES, typename TO>
+__global__ void __launch_bounds__(192, 1)
+linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                      const __grid_constant__ CUtensorMap map_w, TO* out,
+                      const float* __restrict__ bias, const float* residual, int M, int N, int K,
+                      int act, int* status) {
+  using S = TcSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzled tiles need 1024-byte alignment
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = (uint64_t*)(smem + S::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* accum_bar = empty_bar + STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(accum_bar + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+  const int num_kb = (K + TC_BK - 1) / TC_BK;
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;     // power of two >= 32
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(accum_bar, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t round = kb / STAGES;
+        if (round > 0) ok = mbar_wait(&empty_bar[s], (round - 1) & 1, status);
+        if (!ok) break;
+        uint8_t* a_dst = smem + s * S::STAGE_BYTES;
+        uint8_t* b_dst = a_dst + S::A_BYTES;
+        mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+        tma_load_2d(a_dst, &map_a, &full_bar[s], kb * TC_BK, m0);
+        tma_load_2d(b_dst, &map_w, &full_bar[s], kb * TC_BK, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer
+      constexpr uint32_t idesc = make_idesc(TC_BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t round = kb / STAGES;
+        ok = mbar_wait(&full_bar[s], round & 1, status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
+        const uint32_t b_addr = a_addr + S::A_BYTES;
+        const uint64_t adesc = make_smem_desc(a_addr);
+        const uint64_t bdesc = make_smem_desc(b_addr);
+#pragma unroll
+        for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
+          // advance 16 elements = 32 bytes along K inside the swizzled row: +2 in 16-byte units
+          umma_bf16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
+                    (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);     // the stage may be refilled once these MMAs are done
+      }
+      umma_commit(accum_bar);           // the accumulator is complete (or the pipeline gave up)
+    }
+  } else {
+    // ---------------- epilogue: 4 warps, warp (w % 4) owns TMEM lanes 32*(w%4) .. +31
+    const int q = warp & 3;
+    const bool ok = mbar_wait(accum_bar, 0, status);
+    tc_fence_after();
+    const int row = m0 + q * 32 + lane;
+    if (ok) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+        tmem_ld_wait();
+        if (row < M) {
+          const int nbase = n0 + c0;
+          if (nbase + 32 <= N && (N % 8 == 0)) {
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float x = __uint_as_float(v[j]);
+              if (bias) x += __ldg(bias + nbase + j);
+              f[j] = apply_act(x, act);
+            }
+            if (residual) {
+              const float4* r4 = (const float4*)(residual + (size_t)row * N + nbase);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 r = r4[j];
+                f[4 * j] += r.x; f[4 * j + 1] += r.y; f[4 * j + 2] += r.z; f[4 * j + 3] += r.w;
+              }
+            }
+            if constexpr (sizeof(TO) == 4) {
+              float4* o4 = (float4*)((float*)out + (size_t)row * N + nbase);
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                o4[j] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+            } else {
+              uint4* o4 = (uint4*)((__nv_bfloat16*)out + (size_t)row * N + nbase);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(f[8 * j], f[8 * j + 1]);
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(f[8 * j + 2], f[8 * j + 3]);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(f[8 * j + 4], f[8 * j + 5]);
+                __nv_bfloat162 p3 = __floats2bfloat162_rn(f[8 * j + 6], f[8 * j + 7]);
+                uint4 u;
+                u.x = *(uint32_t*)&p0; u.y = *(uint32_t*)&p1; u.z = *(uint32_t*)&p2; u.w = *(uint32_t*)&p3;
+                o4[j] = u;
+              }
+            }
+          } else {
+            for (int j = 0; j < 32; ++j) {
+              const int n = nbase + j;
+              if (n >= N) break;
+              float x = __uint_as_float(v[j]);
+              if (bias) x += bias[n];
+              x = apply_act(x, act);
+              if (residual) x += residual[(size_t)row * N + n];
+              out[(size_t)row * N + n] = from_f<TO>(x);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A [rows, K] bfloat16 matrix with K contiguous, fetched in boxes of [box_rows x 64].
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return HS_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                   strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? HS_OK : HS_ERR_ARGUMENT;
+}
+
+template <int BN, int STAGES, typename TO>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, const float* bias,
+                  const float* residual, int M, int N, int K, int act, int* status,
+                  cudaStream_t st) {
+  auto kern = linear_tcgen05_kernel<BN, STAGES, TO>;
+  constexpr int smem = TcSmem<BN, STAGES>::TOTAL;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
+  kern<<<grid, 192, smem, st>>>(ma, mw, (TO*)out, bias, residual, M, N, K, act, status);
+  HS_LAUNCH_CHECK();
+  return HS_OK;
+}
+
+}  // namespace hs
+
+// Returns HS_ERR_UNSUPPORTED for shapes the TMA path cannot take (K not a multiple of 8:
+// row strides must be multiples of 16 bytes; pointers not 16-byte aligned); the caller falls
+// back to the CUDA-core kernel.
+HS_EXPORT int hs_linear_tcgen05(void* out, const void* a, const void* w, const float* bias,
+                                const float* residual, int M, int N, int K, int act,
+                                int out_dtype, int tile_n, int* status, void* stream) {
+  using namespace hs;
+  if (!out || !a || !w || !status) return HS_ERR_ARGUMENT;
+  if (M <= 0 || N <= 0) return HS_OK;
+  if (K <= 0) return HS_ERR_ARGUMENT;
+  if (K % 8 != 0) return HS_ERR_UNSUPPORTED;
+  if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15)) return HS_ERR_UNSUPPORTED;
+  if (residual && ((uintptr_t)residual & 15)) return HS_ERR_UNSUPPORTED;
+  if (act < HS_ACT_NONE || act > HS_ACT_GELU_ERF) return HS_ERR_UNSUPPORTED;
+  if ((M + TC_BM - 1) / TC_BM > 65535) return HS_ERR_UNSUPPORTED;
+  int bn = tile_n;
+  if (bn == 0) {
+    // A tile's time grows with the bytes it loads per k-block (128 + width rows) plus a fixed
+    // part; pick the width for which waves x that is smallest.
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    long best = -1;
+    const int mt = (M + TC_BM - 1) / TC_BM;
+    for (int cand : {256, 128, 64}) {
+      if (cand > 64 && cand / 2 >= N) continue;
+      const long tiles = (long)mt * ((N + cand - 1) / cand);
+      const long cost = ((tiles + sms - 1) / sms) * (cand + 128 + 64);
+      if (best < 0 || cost < best) {
+        best = cost;
+        bn = cand;
+      }
+    }
+  }
+  CUtensorMap ma, mw;
+  if (int e = make_map(&ma, a, M, K, TC_BM)) return e;
+  if (int e = make_map(&mw, w, N, K, bn)) return e;
+  cudaStream_t st = (cudaStream_t)stream;
+  using bf16 = __nv_bfloat16;
+#define HS_TC(BN, ST)                                                                          \
+  (out_dtype == HS_DT_F32                                                                      \
+       ? launch<BN, ST, float>(ma, mw, out, bias, residual, M, N, K, act, status, st)          \
+       : launch<BN, ST, bf16>(ma, mw, out, bias, residual, M, N, K, act, status, st))
+  if (out_dtype != HS_DT_F32 && out_dtype != HS_DT_BF16) return HS_ERR_UNSUPPORTED;
+  switch (bn) {
+    case 256: return HS_TC(256, 4);
+    case 128: return HS_TC(128, 6);
+    case 64: return HS_TC(64, 8);
+    default: return HS_ERR_UNSUPPORTED;
+  }
+#undef HS_TC
+}

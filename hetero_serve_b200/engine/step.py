@@ -229,6 +229,8 @@ class Runner:
         self.max_positions = model.spec.max_positions
         self.max_pages = [self.manager.pages_for(self.max_positions) for _ in model.cache_groups]
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        if hasattr(ops, "status"):
+            ops.status = self.status       # kernels that take no status argument report here
         self.cuda = self.device.type == "cuda"
         self.use_graphs = bool(cuda_graphs and self.cuda)
         self._graphs: dict[tuple, "_Captured"] = {}

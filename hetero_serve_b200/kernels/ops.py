@@ -72,6 +72,7 @@ def _declare(lib) -> None:
         "hs_embed": [P, P, P, P, P, P, I, I, I, I, I, P, P],
         "hs_layernorm": [P, P, P, P, P, I, I, F, I, P],
         "hs_linear_simt": [P, P, P, P, P, I, I, I, I, I, I, P],
+        "hs_linear_tcgen05": [P, P, P, P, P, I, I, I, I, I, I, P, P],
         "hs_kv_append": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "hs_attention_simt": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
         "hs_argmax": [P, P, I, I, P],
@@ -124,6 +125,11 @@ class CudaOps:
             raise KernelError("hetero_serve_b200 needs a CUDA device: its kernels have no CPU path")
         self.lib = load_library()
         self.launches = 0          # kernels launched through this object (graph captures count once)
+        self.tensor_cores = True   # bfloat16 linears on tcgen05 (False: CUDA cores, for tests)
+        self.tile_n = 0            # 0: chosen per shape; 64/128/256 force a tile width
+        # pipeline time-outs of the TMA/tcgen05 kernels are ORed into this word; the runner
+        # replaces it with its own so that they surface with the step's results
+        self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
 
     @staticmethod
     def _stream():
@@ -200,7 +206,16 @@ class CudaOps:
         self._linear(out, a, w, bias, ACTIVATIONS[act], residual, M, N, K)
 
     def _linear(self, out, a, w, bias, act, residual, M, N, K):
+        """bfloat16 goes to the tcgen05 kernel when TMA can address the operands (K a multiple
+        of 8, 16-byte aligned pointers); everything else, and all of float32, to the CUDA cores."""
         self.launches += 1
+        if a.dtype == torch.bfloat16 and self.tensor_cores and K % 8 == 0:
+            code = self.lib.hs_linear_tcgen05(
+                _ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), M, N, K, act,
+                _DT[out.dtype], self.tile_n, _ptr(self.status), self._stream())
+            if code != -1:
+                _check(code, f"linear_tcgen05(M={M},N={N},K={K})")
+                return
         _check(self.lib.hs_linear_simt(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual),
                                        M, N, K, act, _DT[a.dtype], _DT[out.dtype],
                                        self._stream()), f"linear(M={M},N={N},K={K})")
