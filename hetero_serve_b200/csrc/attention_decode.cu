@@ -1,0 +1,288 @@
+// Split-context paged attention for tokens that bring one query each (decoding), bfloat16.
+//
+// The successor of the reference's split-K decode kernels (heteroserve/model/paged_attn_v3.py:
+// split kernel :75-165, merge kernel :170-208, split heuristic :212-232): the keys 0..p of a
+// query are cut into `splits` slices; one CTA streams one slice of one (token, head) with an
+// online softmax in float32 (running maximum m, running sum l, un-normalised accumulator),
+// writes its partial (acc, m, l) to scratch memory, and the LAST CTA of a (token, head) to
+// finish — found with a counter in scratch — merges the partials in slice order:
+//     m_g = max_s m_s;  l_g = sum_s l_s * exp(m_s - m_g);  out = sum_s acc_s * exp(m_s - m_g) / l_g
+// (paged_attn_v3.py:170-208), so no second launch is needed.  The slice length is read from
+// device memory (the batch's longest context / splits, rounded up to whole pages), which keeps a
+// captured CUDA graph valid while contexts grow.
+//
+// Inside a CTA each warp takes every 4th page of the slice.  A key row of D bfloat16 is read by
+// D/8 adjacent lanes with one 16-byte load each, so a warp covers 256/D keys per load and the
+// loads of a page (keys and values) are all in flight before the first is used.  Scores are
+// (q . k) * scale with the multiply after the dot product (heteroserve/model/torch_engine.py:135).
+//
+// Scratch layout (float32 unless noted), T = token capacity, H = heads, S = splits:
+//     acc  [T][H][S][D]      ml [T][H][S][2]      counters [T][H] (int32, zero between launches)
+#include "common.cuh"
+
+namespace hs {
+
+constexpr int AD_WARPS = 4;
+
+struct DecodeParams {
+  const __nv_bfloat16* qkv;
+  const __nv_bfloat16* pool;
+  __nv_bfloat16* out;
+  const int* table;
+  const int* tok_pos;
+  const int* tok_req;
+  const int* tok_list;     // flat indices of the tokens this launch serves
+  const int* plan_head;    // [0] = number of tokens in tok_list, [2] = longest context among them
+  float* acc;
+  float* ml;
+  int* counters;
+  int* status;
+  int n_heads, n_kv_heads, page_size, num_pages, max_pages;
+  int q_off, qkv_stride, splits, window;
+  float scale;
+};
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(AD_WARPS * 32)
+attention_decode_kernel(const DecodeParams p) {
+  constexpr int LPK = D / 8;          // lanes per key row
+  constexpr int KPW = 32 / LPK;       // keys per warp-wide load
+  static_assert(D == 16 || D == 32 || D == 64 || D == 128 || D == 256, "head size");
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = blockIdx.x;                       // index into tok_list
+  const int h = blockIdx.y, split = blockIdx.z;
+  if (slot >= p.plan_head[0]) return;
+  const int t = p.tok_list[slot];
+  const int r = p.tok_req[t];
+  const int pos = p.tok_pos[t];
+  __nv_bfloat16* orow = p.out + ((size_t)t * p.n_heads + h) * D;
+  if (r < 0 || pos < 0 || pos / p.page_size >= p.max_pages) {
+    if (split == 0)
+      for (int d = threadIdx.x; d < D; d += blockDim.x) orow[d] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int hk = h / (p.n_heads / p.n_kv_heads);
+  const int PS = p.page_size;
+  const int lo_all = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+  // slice boundaries in whole pages, from the batch's longest context
+  const int max_ctx = p.plan_head[2];
+  int chunk = (max_ctx + p.splits - 1) / p.splits;
+  chunk = (chunk + PS - 1) / PS * PS;
+  const int k_begin = max(split * chunk, lo_all);
+  const int k_end = min((split + 1) * chunk, pos + 1);       // exclusive
+
+  // the query, 8 elements per lane (the same 8 its key lanes read)
+  const int part = lane % LPK, sub = lane / LPK;
+  float q[8];
+  {
+    const uint4 qu = *(const uint4*)(p.qkv + (size_t)t * p.qkv_stride + p.q_off + (size_t)h * D +
+                                     part * 8);
+    unpack8(qu, q);
+  }
+  float m = -INFINITY, l = 0.f, acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+
+  const size_t tile = (size_t)PS * D;
+  const size_t page_stride = 2 * (size_t)p.n_kv_heads * tile;
+  const int* trow = p.table + (size_t)r * p.max_pages;
+
+  if (k_begin < k_end) {
+    const int pg_first = k_begin / PS, pg_last = (k_end - 1) / PS;
+    for (int pg = pg_first + warp; pg <= pg_last; pg += AD_WARPS) {
+      const int page = trow[pg];
+      if (page < 0 || page >= p.num_pages) {
+        if (lane == 0) atomicOr(p.status, HS_STATUS_BAD_PAGE);
+        continue;
+      }
+      const __nv_bfloat16* kbase = p.pool + (size_t)page * page_stride + (size_t)hk * tile;
+      const __nv_bfloat16* vbase = kbase + (size_t)p.n_kv_heads * tile;
+      const int j0 = pg * PS;
+      // keys of this page in groups of KPW; a page of 16 and D = 64 gives 4 groups
+      for (int g0 = 0; g0 < PS; g0 += 4 * KPW) {
+        uint4 ku[4], vu[4];
+        float s[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int slot_in_page = g0 + i * KPW + sub;
+          const int j = j0 + slot_in_page;
+          const bool valid = slot_in_page < PS && j >= k_begin && j < k_end;
+          if (valid) {
+            ku[i] = *(const uint4*)(kbase + (size_t)slot_in_page * D + part * 8);
+            vu[i] = *(const uint4*)(vbase + (size_t)slot_in_page * D + part * 8);
+          } else {
+            ku[i] = make_uint4(0, 0, 0, 0);
+            vu[i] = make_uint4(0, 0, 0, 0);
+          }
+        }
+        float bm = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float kf[8];
+          unpack8(ku[i], kf);
+          float dot = 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) dot = fmaf(q[e], kf[e], dot);
+#pragma unroll
+          for (int o = 1; o < LPK; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+          const int slot_in_page = g0 + i * KPW + sub;
+          const int j = j0 + slot_in_page;
+          const bool valid = slot_in_page < PS && j >= k_begin && j < k_end;
+          s[i] = valid ? dot * p.scale : -INFINITY;
+          bm = fmaxf(bm, s[i]);
+        }
+        // maximum over the key groups of the warp (lanes with the same `part`)
+#pragma unroll
+        for (int o = LPK; o < 32; o <<= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+        if (bm == -INFINITY) continue;
+        const float m_new = fmaxf(m, bm);
+        const float corr = __expf(m - m_new);
+        l *= corr;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] *= corr;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float pr = (s[i] == -INFINITY) ? 0.f : __expf(s[i] - m_new);
+          l += pr;
+          float vf[8];
+          unpack8(vu[i], vf);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = fmaf(pr, vf[e], acc[e]);
+        }
+        m = m_new;
+      }
+    }
+  }
+  // ---- combine the key groups of a warp, then the warps of the CTA (all share m per warp)
+  // every lane of a warp holds the same m; l and acc are per key group: sum over groups
+#pragma unroll
+  for (int o = LPK; o < 32; o <<= 1) {
+    l += __shfl_xor_sync(0xffffffffu, l, o);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+  }
+  // l was added once per lane of a key group: every lane of a group holds the same l, fine
+  __shared__ float s_m[AD_WARPS], s_l[AD_WARPS], s_acc[AD_WARPS][D];
+  if (sub == 0) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s_acc[warp][part * 8 + e] = acc[e];
+  }
+  if (lane == 0) {
+    s_m[warp] = m;
+    s_l[warp] = l;
+  }
+  __syncthreads();
+  const size_t pidx = ((size_t)slot * p.n_heads + h) * p.splits + split;
+  float* pacc = p.acc + pidx * D;
+  float cm = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < AD_WARPS; ++w) cm = fmaxf(cm, s_m[w]);
+  float cl = 0.f;
+  float wscale[AD_WARPS];
+#pragma unroll
+  for (int w = 0; w < AD_WARPS; ++w) {
+    wscale[w] = (s_m[w] == -INFINITY) ? 0.f : __expf(s_m[w] - cm);
+    cl += s_l[w] * wscale[w];
+  }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float a = 0.f;
+#pragma unroll
+    for (int w = 0; w < AD_WARPS; ++w) a += s_acc[w][d] * wscale[w];
+    if (p.splits == 1) {
+      orow[d] = __float2bfloat16_rn(cl > 0.f ? a / cl : 0.f);
+    } else {
+      pacc[d] = a;
+    }
+  }
+  if (p.splits == 1) return;
+  if (threadIdx.x == 0) {
+    p.ml[pidx * 2] = cm;
+    p.ml[pidx * 2 + 1] = cl;
+  }
+  // ---- the last CTA of this (token, head) merges
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(&p.counters[slot * p.n_heads + h], 1);
+    s_last = (done == p.splits - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const size_t base = ((size_t)slot * p.n_heads + h) * p.splits;
+  float gm = -INFINITY;
+  for (int s2 = 0; s2 < p.splits; ++s2) gm = fmaxf(gm, __ldcg(&p.ml[(base + s2) * 2]));
+  float gl = 0.f;
+  for (int s2 = 0; s2 < p.splits; ++s2) {
+    const float ms = __ldcg(&p.ml[(base + s2) * 2]);
+    if (ms != -INFINITY) gl += __ldcg(&p.ml[(base + s2) * 2 + 1]) * __expf(ms - gm);
+  }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float a = 0.f;
+    for (int s2 = 0; s2 < p.splits; ++s2) {
+      const float ms = __ldcg(&p.ml[(base + s2) * 2]);
+      if (ms != -INFINITY) a += __ldcg(&p.acc[(base + s2) * D + d]) * __expf(ms - gm);
+    }
+    orow[d] = __float2bfloat16_rn(gl > 0.f ? a / gl : 0.f);
+  }
+  if (threadIdx.x == 0) p.counters[slot * p.n_heads + h] = 0;     // ready for the next launch
+}
+
+}  // namespace hs
+
+// Bytes of scratch one launch needs (acc + ml + counters), for a token capacity.
+HS_EXPORT long long hs_attention_decode_scratch_floats(int token_cap, int n_heads, int head_dim,
+                                                       int splits) {
+  return (long long)token_cap * n_heads * splits * (head_dim + 2);
+}
+
+HS_EXPORT int hs_attention_decode(void* out, const void* qkv, const void* pool, const int* table,
+                                  const int* tok_pos, const int* tok_req, const int* tok_list,
+                                  const int* plan_head, int token_cap, int n_heads,
+                                  int n_kv_heads, int head_dim, int page_size, int num_pages,
+                                  int max_pages, int q_off, int qkv_stride, int window,
+                                  float scale, int splits, float* scratch_acc, float* scratch_ml,
+                                  int* counters, int* status, void* stream) {
+  using namespace hs;
+  if (!out || !qkv || !pool || !table || !tok_pos || !tok_req || !tok_list || !plan_head ||
+      !status)
+    return HS_ERR_ARGUMENT;
+  if (token_cap <= 0) return HS_OK;
+  if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return HS_ERR_UNSUPPORTED;
+  if (page_size <= 0 || page_size % 16 || splits < 1 || splits > 65535) return HS_ERR_UNSUPPORTED;
+  if (n_heads > 65535) return HS_ERR_UNSUPPORTED;
+  if (splits > 1 && (!scratch_acc || !scratch_ml || !counters)) return HS_ERR_ARGUMENT;
+  if ((qkv_stride % 8) || (q_off % 8)) return HS_ERR_UNSUPPORTED;   // 16-byte query loads
+  DecodeParams p;
+  p.qkv = (const __nv_bfloat16*)qkv;
+  p.pool = (const __nv_bfloat16*)pool;
+  p.out = (__nv_bfloat16*)out;
+  p.table = table; p.tok_pos = tok_pos; p.tok_req = tok_req; p.tok_list = tok_list;
+  p.plan_head = plan_head; p.acc = scratch_acc; p.ml = scratch_ml; p.counters = counters;
+  p.status = status;
+  p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
+  p.num_pages = num_pages; p.max_pages = max_pages; p.q_off = q_off; p.qkv_stride = qkv_stride;
+  p.splits = splits; p.window = window; p.scale = scale;
+  dim3 grid(token_cap, n_heads, splits);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (head_dim) {
+    case 16: attention_decode_kernel<16><<<grid, AD_WARPS * 32, 0, st>>>(p); break;
+    case 32: attention_decode_kernel<32><<<grid, AD_WARPS * 32, 0, st>>>(p); break;
+    case 64: attention_decode_kernel<64><<<grid, AD_WARPS * 32, 0, st>>>(p); break;
+    case 128: attention_decode_kernel<128><<<grid, AD_WARPS * 32, 0, st>>>(p); break;
+    case 256: attention_decode_kernel<256><<<grid, AD_WARPS * 32, 0, st>>>(p); break;
+    default: return HS_ERR_UNSUPPORTED;
+  }
+  HS_LAUNCH_CHECK();
+  return HS_OK;
+}

@@ -139,7 +139,7 @@ class StepContext:
         self.samp_pos = meta[L.samp_pos:L.samp_pos + L.W]
         self.tables = [meta[o:o + L.R * mp].view(L.R, mp)
                        for o, mp in zip(L.tables, L.max_pages)]
-        self.plan = AttentionPlan(meta[L.plan:L.plan + L.plan_ints], L.T, L.R)
+        self.plan = None          # work lists for the specialised attention kernels, if any
         self.call_index: int | None = None
         # host-side view of the batch for parts written in plain PyTorch
         self.host: list[tuple[Hashable, int, int, int]] = []   # (req, slot, start, n)
@@ -160,16 +160,6 @@ class StepContext:
         """State tensor ``[slots, ...]`` of the mixer running now; rows are indexed with
         ``req_slot``."""
         return self.runner.storage.states[self.call_index]
-
-
-@dataclass
-class AttentionPlan:
-    """Work lists a specialised attention kernel reads (filled by ``ops.plan_attention``)."""
-
-    data: torch.Tensor
-    n_rows: int
-    n_requests: int
-    info: dict = field(default_factory=dict)
 
 
 class Workspace:
@@ -365,12 +355,13 @@ class Runner:
                 w_i += 1
             host_batch.append((e.req_id, slot, start, n))
             t += n
+        plan_shape = None
         if lay.plan_ints:
-            self.ops.plan_attention(hm[lay.plan:lay.plan + lay.plan_ints], host_batch, T, R,
-                                    mgr.page_size)
+            plan_shape = self.ops.plan_attention(hm[lay.plan:lay.plan + lay.plan_ints],
+                                                 host_batch, T, R, mgr.page_size, self.use_graphs)
 
         # ---- device side -------------------------------------------------------------
-        key = (T, R, W, bool(sample))
+        key = (T, R, W, bool(sample), plan_shape)
         dev = self._dev_meta.get(key[:3])
         if dev is None:
             dev = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
@@ -390,6 +381,9 @@ class Runner:
         else:
             ctx = StepContext(self, lay, dev)
             ctx.host = host_batch
+            if plan_shape is not None:
+                from ..kernels.ops import AttentionPlan
+                ctx.plan = AttentionPlan(dev[lay.plan:lay.plan + lay.plan_ints], T, *plan_shape)
             if self.use_graphs and not self.model.state_shapes:
                 # run once eagerly (loads kernels, sizes buffers), then capture and replay
                 self._forward(ctx, sample)

@@ -1,3 +1,3 @@
-from .ops import AttentionGeometry, CudaOps, KernelError, load_library
+from .ops import AttentionGeometry, AttentionPlan, CudaOps, KernelError, load_library
 
-__all__ = ["AttentionGeometry", "CudaOps", "KernelError", "load_library"]
+__all__ = ["AttentionGeometry", "AttentionPlan", "CudaOps", "KernelError", "load_library"]

@@ -48,6 +48,42 @@ class AttentionGeometry:
         return 2 * self.n_kv_heads * self.page_size * self.head_dim
 
 
+@dataclass
+class AttentionPlan:
+    """Work lists of one step for the specialised attention kernels, in device memory.
+
+    ``data`` (int32): ``[0]`` number of single-query tokens, ``[1]`` number of 64-query
+    tiles, ``[2]`` longest context among the single-query tokens, ``[3]`` unused; then the
+    flat indices of the single-query tokens (``n_rows`` entries), then for each tile the
+    flat index of its first query and its number of queries (``tile_slots`` entries each).
+    ``decode_cap`` / ``tile_cap`` are the grid sizes the kernels are launched with (at
+    least the counts; fixed per size class so that a captured graph stays valid)."""
+
+    data: torch.Tensor
+    n_rows: int
+    decode_cap: int
+    tile_cap: int
+
+    @property
+    def tile_slots(self) -> int:
+        return plan_tile_slots(self.n_rows)
+
+
+DECODE_MAX_NEW = 4        # requests bringing at most this many tokens use the decode kernel
+PREFILL_TILE = 64
+
+
+def plan_tile_slots(n_rows: int) -> int:
+    return n_rows // PREFILL_TILE + n_rows // (DECODE_MAX_NEW + 1) + 1
+
+
+def _pow2(n: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return b
+
+
 _ERRORS = {-1: "unsupported size, type or option", -2: "bad argument"}
 
 _lib = None
@@ -75,6 +111,9 @@ def _declare(lib) -> None:
         "hs_linear_tcgen05": [P, P, P, P, P, I, I, I, I, I, I, P, P],
         "hs_kv_append": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "hs_attention_simt": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
+        "hs_attention_decode": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P,
+                                P, P, P],
+        "hs_attention_prefill": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
         "hs_argmax": [P, P, I, I, P],
         "hs_sample": [P, P, P, P, P, P, P, I, I, P],
     }
@@ -126,6 +165,10 @@ class CudaOps:
         self.lib = load_library()
         self.launches = 0          # kernels launched through this object (graph captures count once)
         self.tensor_cores = True   # bfloat16 linears on tcgen05 (False: CUDA cores, for tests)
+        self.fast_attention = True  # bfloat16 attention on the split-context / tensor-core kernels
+        self.sm_count = torch.cuda.get_device_properties(0).multi_processor_count
+        self._scratch: dict = {}
+        self._retired: list = []
         self.tile_n = 0            # 0: chosen per shape; 64/128/256 force a tile width
         # pipeline time-outs of the TMA/tcgen05 kernels are ORed into this word; the runner
         # replaces it with its own so that they surface with the step's results
@@ -263,13 +306,114 @@ class CudaOps:
         self._attn_common(qkv, pool, table, tok_pos, tok_req, g, n)
         self._attention(out, qkv, pool, table, tok_pos, tok_req, g, float(scale), status, plan, n)
 
+    # -- attention work lists ---------------------------------------------------------
+    @staticmethod
+    def attention_plan_ints(n_rows: int, n_requests: int) -> int:
+        return 4 + n_rows + 2 * plan_tile_slots(n_rows)
+
+    @staticmethod
+    def plan_attention(view, host_batch, n_rows: int, n_requests: int, page_size: int,
+                       bucketed: bool) -> tuple[int, int]:
+        """Fill the plan section (a numpy int32 view of the step's metadata) for a batch given
+        as ``[(request, slot, start, n_new)]`` in flat order; returns ``(decode_cap,
+        tile_cap)``.  Requests bringing up to DECODE_MAX_NEW tokens go to the single-query
+        list, the others are cut into tiles of 64 queries."""
+        slots = plan_tile_slots(n_rows)
+        tok_list = view[4:4 + n_rows]
+        tile_tok = view[4 + n_rows:4 + n_rows + slots]
+        tile_n = view[4 + n_rows + slots:4 + n_rows + 2 * slots]
+        n_dec = n_tiles = max_ctx = 0
+        t = 0
+        for _req, _slot, start, n in host_batch:
+            if n <= DECODE_MAX_NEW:
+                for i in range(n):
+                    tok_list[n_dec] = t + i
+                    n_dec += 1
+                max_ctx = max(max_ctx, start + n)
+            else:
+                for q0 in range(0, n, PREFILL_TILE):
+                    tile_tok[n_tiles] = t + q0
+                    tile_n[n_tiles] = min(PREFILL_TILE, n - q0)
+                    n_tiles += 1
+            t += n
+        view[0], view[1], view[2], view[3] = n_dec, n_tiles, max_ctx, 0
+        if bucketed:
+            return (_pow2(n_dec) if n_dec else 0, _pow2(n_tiles) if n_tiles else 0)
+        return n_dec, n_tiles
+
+    def make_plan(self, host_batch, n_rows: int, page_size: int) -> AttentionPlan:
+        """A plan built and uploaded on the spot (the runner packs it into the step's single
+        upload instead)."""
+        import numpy as np
+        view = np.zeros(self.attention_plan_ints(n_rows, len(host_batch)), dtype=np.int32)
+        dec, tiles = self.plan_attention(view, host_batch, n_rows, len(host_batch), page_size,
+                                         False)
+        return AttentionPlan(torch.from_numpy(view).to("cuda"), n_rows, dec, tiles)
+
+    def _scratch_buffer(self, name, numel, dtype):
+        key = (name, dtype)
+        buf = self._scratch.get(key)
+        if buf is None or buf.numel() < numel:
+            if buf is not None:
+                self._retired.append(buf)       # captured graphs may still point into it
+            buf = torch.zeros(max(numel, 1), dtype=dtype, device="cuda")
+            self._scratch[key] = buf
+        return buf
+
+    def decode_splits(self, decode_cap: int, n_heads: int, max_context: int) -> int:
+        """Slices the context of a single-query token is cut into: enough CTAs to fill the
+        GPU twice, slices of at least 64 keys (in the manner of the reference's
+        ``choose_num_splits``, heteroserve/model/paged_attn_v3.py:212-232)."""
+        want = -(-2 * self.sm_count // max(1, decode_cap * n_heads))
+        return max(1, min(want, max(1, max_context // 64), 32))
+
+    FAST_HEAD_DIMS = (16, 32, 64, 128)
+
     def _attention(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan, n):
+        if (plan is not None and self.fast_attention and qkv.dtype == torch.bfloat16
+                and g.window == 0 and g.head_dim in self.FAST_HEAD_DIMS
+                and plan.n_rows >= n):
+            self._attention_fast(out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan)
+            return
         self.launches += 1
         _check(self.lib.hs_attention_simt(
             _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req), n,
             g.n_heads, g.n_kv_heads, g.head_dim, g.page_size, g.num_pages, g.max_pages, g.q_off,
             g.k_off, g.v_off, g.qkv_stride, g.window, scale, _DT[qkv.dtype], _ptr(status),
             self._stream()), f"attention(head_dim={g.head_dim}, heads={g.n_heads})")
+
+    def _attention_fast(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan):
+        d = plan.data
+        nr, slots = plan.n_rows, plan.tile_slots
+        head = d
+        tok_list = d[4:]
+        tile_tok = d[4 + nr:]
+        tile_n = d[4 + nr + slots:]
+        st = self._stream()
+        if plan.decode_cap:
+            max_ctx = g.max_pages * g.page_size
+            splits = self.decode_splits(plan.decode_cap, g.n_heads, max_ctx)
+            acc = ml = cnt = None
+            if splits > 1:
+                rows = plan.decode_cap * g.n_heads * splits
+                acc = self._scratch_buffer("decode_acc", rows * g.head_dim, torch.float32)
+                ml = self._scratch_buffer("decode_ml", rows * 2, torch.float32)
+                cnt = self._scratch_buffer("decode_counters", plan.decode_cap * g.n_heads,
+                                           torch.int32)
+            self.launches += 1
+            _check(self.lib.hs_attention_decode(
+                _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req),
+                _ptr(tok_list), _ptr(head), plan.decode_cap, g.n_heads, g.n_kv_heads, g.head_dim,
+                g.page_size, g.num_pages, g.max_pages, g.q_off, g.qkv_stride, g.window, scale,
+                splits, _ptr(acc), _ptr(ml), _ptr(cnt), _ptr(status), st),
+                f"attention_decode(head_dim={g.head_dim})")
+        if plan.tile_cap:
+            self.launches += 1
+            _check(self.lib.hs_attention_prefill(
+                _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req),
+                _ptr(tile_tok), _ptr(tile_n), _ptr(head), plan.tile_cap, g.n_heads, g.n_kv_heads,
+                g.head_dim, g.page_size, g.num_pages, g.max_pages, g.q_off, g.qkv_stride, scale,
+                _ptr(status), st), f"attention_prefill(head_dim={g.head_dim})")
 
     # -- sampling ---------------------------------------------------------------
     def argmax(self, out, logits):

@@ -208,6 +208,74 @@ def test_kv_append_and_attention(ops, plain, case, dtype):
     assert (out.double() - ref).abs().max() < tol
 
 
+def _host_batch(lens, new):
+    return [(f"r{r}", r, n - k, k) for r, (n, k) in enumerate(zip(lens, new))]
+
+
+FAST_CASES = [
+    # H, HK, D, PS, lens, new     (bfloat16, no window: the specialised kernels)
+    (4, 4, 16, 16, [5, 17, 33, 200], [5, 17, 33, 200]),          # prompts: tensor-core tiles
+    (3, 3, 32, 16, [40, 16, 70, 1, 300], [1, 1, 1, 1, 1]),       # single queries: split contexts
+    (16, 16, 64, 16, [1024, 700, 64, 65], [1, 1, 1, 2]),         # long contexts, many splits
+    (6, 2, 64, 16, [150, 23, 90, 77], [70, 23, 3, 1]),           # grouped heads; both kernels
+    (2, 1, 128, 32, [300, 64, 129], [130, 1, 129]),              # pages of 32, head size 128
+    (5, 5, 32, 48, [100, 130], [100, 2]),                        # pages of 48
+    (2, 2, 64, 16, [64, 63, 65, 128, 1], [64, 63, 65, 64, 1]),   # tile edges
+]
+
+
+@pytest.mark.parametrize("case", FAST_CASES,
+                         ids=[f"H{c[0]}k{c[1]}D{c[2]}P{c[3]}n{len(c[4])}" for c in FAST_CASES])
+def test_specialised_attention_kernels(ops, plain, case):
+    H, HK, D, PS, lens, new = case
+    geom, qkv, pool, table, tok_pos, tok_req = _attention_case(H, HK, D, PS, lens, new, 0,
+                                                               torch.bfloat16, seed=H * D)
+    st = _status()
+    ops.kv_append(pool, qkv, table, tok_pos, tok_req, geom, st)
+    T = qkv.shape[0]
+    plan = ops.make_plan(_host_batch(lens, new), T, PS)
+    assert plan.decode_cap == sum(k for k in new if k <= 4)
+    assert plan.tile_cap == sum(-(-k // 64) for k in new if k > 4)
+    out = torch.full((T, H * D), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ref = torch.empty(T, H * D, device=DEV, dtype=torch.float64)
+    scale = 0.9 / D ** 0.5
+    before = ops.launches
+    ops.attention(out, qkv, pool, table, tok_pos, tok_req, geom, scale, st, plan)
+    assert ops.launches - before == (plan.decode_cap > 0) + (plan.tile_cap > 0)
+    plain.attention(ref, qkv, pool, table, tok_pos, tok_req, geom, scale, st)
+    assert st.item() == 0
+    assert torch.isfinite(out).all()
+    assert (out.double() - ref).abs().max() < 2e-2
+    # a second launch reuses the scratch memory and its counters
+    out2 = torch.empty_like(out)
+    ops.attention(out2, qkv, pool, table, tok_pos, tok_req, geom, scale, st, plan)
+    assert torch.equal(out, out2)
+    # and agrees with the general kernel to rounding
+    gen = torch.empty_like(out)
+    ops.attention(gen, qkv, pool, table, tok_pos, tok_req, geom, scale, st, None)
+    assert (out.float() - gen.float()).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("far", [0, 63, 64, 500, 1000])
+@pytest.mark.parametrize("new", [1, 100])
+def test_far_key_with_the_specialised_kernels(ops, far, new):
+    H, D, PS, n = 4, 64, 16, 1024
+    geom, qkv, pool, table, tok_pos, tok_req = _attention_case(H, H, D, PS, [n], [new], 0,
+                                                               torch.bfloat16, 3)
+    st = _status()
+    ops.kv_append(pool, qkv, table, tok_pos, tok_req, geom, st)
+    far = min(far, n - new)                      # a key every query of the portion can see
+    pv = pool.view(geom.num_pages, 2, H, PS, D)
+    q = qkv[-1, :H * D].view(H, D).float()       # the last query
+    page, slot = int(table[0, far // PS]), far % PS
+    pv[page, 0, :, slot, :] = (q / q.norm(dim=-1, keepdim=True) * 40).to(torch.bfloat16)
+    out = torch.empty(new, H * D, device=DEV, dtype=torch.bfloat16)
+    plan = ops.make_plan(_host_batch([n], [new]), new, PS)
+    ops.attention(out, qkv, pool, table, tok_pos, tok_req, geom, 1.0, st, plan)
+    want = pv[page, 1, :, slot, :].reshape(H * D).float()
+    assert (out[-1].float() - want).abs().max() < 2e-2
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("far", [0, 15, 16, 255, 256, 511, 600])
 def test_one_far_key_among_hundreds_decides_the_output(ops, dtype, far):
