@@ -1,0 +1,256 @@
+// bfloat16 linear layer for few rows (M <= 64: decoding), bound by streaming the weights.
+//
+//   out[m, n] = act( sum_k a[m, k] * w[n, k] + bias[n] ) (+ residual[m, n])
+//   a = the bfloat16 input, or LayerNorm(x) of a float32 input computed on the fly.
+//
+// With M this small a 128-row tensor-core tile would be nearly empty and only N/128 CTAs would
+// stream the weights.  Here the roles are swapped: a warp owns 16 output features, the weights
+// are the row operand of mma.sync m16n8k16 and the (few) tokens are the 8-wide column operand.
+// Each lane loads 16 bytes (8 consecutive k) of two weight rows straight from global memory into
+// the registers of two MMA k-steps — the k order inside a 32-wide block is permuted the same way
+// for both operands, which a dot product allows — so the weights are read once, fully coalesced,
+// with no shared-memory round trip.  The activations (M_pad x K, bfloat16) sit in shared memory,
+// padded so that the 16-byte fragment reads are conflict-free.  A CTA = 8 warps owns 16 features;
+// the warps take the 32-wide k blocks round-robin and their partial tiles are added in warp
+// order (for a wide layer such as the vocabulary head a CTA owns up to 128 features, 16 per
+// warp, so that the activations are staged less often) (a fixed order: no atomics), then bias, activation and the float32 residual are applied.
+//
+// Optional fused LayerNorm (the reference's `F.layer_norm` before each projection,
+// heteroserve/model/torch_engine.py:74-75,121,140): every CTA normalises the M rows itself
+// (statistics in float32: mean, then centred variance) while it stages them.
+#include "common.cuh"
+
+namespace hs {
+
+constexpr int SK_WARPS = 8, SK_THREADS = SK_WARPS * 32, SK_FEATS = 16;
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+struct SkinnyParams {
+  const __nv_bfloat16* a;      // [M, K] bf16, or null when x is given
+  const float* x;              // [M, K] f32 to be normalised, or null
+  const float* gamma;
+  const float* beta;
+  const __nv_bfloat16* w;      // [N, K]
+  const float* bias;
+  const float* residual;
+  void* out;
+  int M, N, K, act, out_f32, kc, stride;   // kc: k per staging chunk; stride: smem row stride
+  int ng;                                  // feature groups (of 16) per CTA: 1, 2, 4 or 8
+  float eps;
+};
+
+template <int MT>
+__global__ void __launch_bounds__(SK_THREADS)
+linear_skinny_kernel(const SkinnyParams p) {
+  constexpr int MP = MT * 8;
+  extern __shared__ __align__(16) uint8_t sk_smem[];
+  __nv_bfloat16* sx = (__nv_bfloat16*)sk_smem;             // [MP][stride]
+  __shared__ float s_mu[MP], s_rs[MP];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  // warp -> (feature group, k group): ng groups of 16 features, 8 / ng warps share each
+  const int fg = warp % p.ng, kg = warp / p.ng, n_kg = SK_WARPS / p.ng;
+  const int n0 = (blockIdx.x * p.ng + fg) * SK_FEATS;
+  const int K = p.K, M = p.M;
+
+  if (p.x) {        // LayerNorm statistics of every row, one warp per row
+    for (int m = warp; m < MP; m += SK_WARPS) {
+      float mu = 0.f, rs = 0.f;
+      if (m < M) {
+        const float* xr = p.x + (size_t)m * K;
+        float s = 0.f;
+        for (int k = lane; k < K; k += 32) s += xr[k];
+        mu = warp_sum(s) / (float)K;
+        float q = 0.f;
+        for (int k = lane; k < K; k += 32) {
+          const float c = xr[k] - mu;
+          q += c * c;
+        }
+        rs = 1.0f / sqrtf(warp_sum(q) / (float)K + p.eps);
+      }
+      if (lane == 0) {
+        s_mu[m] = mu;
+        s_rs[m] = rs;
+      }
+    }
+    __syncthreads();
+  }
+
+  float c[MT][4];
+#pragma unroll
+  for (int i = 0; i < MT; ++i) c[i][0] = c[i][1] = c[i][2] = c[i][3] = 0.f;
+
+  const int row_a = min(n0 + g, p.N - 1), row_b = min(n0 + g + 8, p.N - 1);   // clamped: never stored
+  const __nv_bfloat16* wa = p.w + (size_t)row_a * K + t * 8;
+  const __nv_bfloat16* wb = p.w + (size_t)row_b * K + t * 8;
+
+  for (int k0 = 0; k0 < K; k0 += p.kc) {
+    const int kn = min(p.kc, K - k0);
+    if (k0 > 0) __syncthreads();            // the previous chunk has been consumed
+    // ---- stage activations [MP][kn] (rows past M are zero)
+    for (int i = threadIdx.x; i < MP * (kn / 8); i += SK_THREADS) {
+      const int m = i / (kn / 8), kk = (i % (kn / 8)) * 8;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (m < M) {
+        if (p.x) {
+          const float4* xr = (const float4*)(p.x + (size_t)m * K + k0 + kk);
+          const float4 x0 = xr[0], x1 = xr[1];
+          const float4* gp = (const float4*)(p.gamma + k0 + kk);
+          const float4* bp = (const float4*)(p.beta + k0 + kk);
+          const float4 g0 = gp[0], g1 = gp[1], b0 = bp[0], b1 = bp[1];
+          const float mu = s_mu[m], rs = s_rs[m];
+          __nv_bfloat162 o0 = __floats2bfloat162_rn((x0.x - mu) * rs * g0.x + b0.x,
+                                                    (x0.y - mu) * rs * g0.y + b0.y);
+          __nv_bfloat162 o1 = __floats2bfloat162_rn((x0.z - mu) * rs * g0.z + b0.z,
+                                                    (x0.w - mu) * rs * g0.w + b0.w);
+          __nv_bfloat162 o2 = __floats2bfloat162_rn((x1.x - mu) * rs * g1.x + b1.x,
+                                                    (x1.y - mu) * rs * g1.y + b1.y);
+          __nv_bfloat162 o3 = __floats2bfloat162_rn((x1.z - mu) * rs * g1.z + b1.z,
+                                                    (x1.w - mu) * rs * g1.w + b1.w);
+          v.x = *(uint32_t*)&o0; v.y = *(uint32_t*)&o1; v.z = *(uint32_t*)&o2; v.w = *(uint32_t*)&o3;
+        } else {
+          v = *(const uint4*)(p.a + (size_t)m * K + k0 + kk);
+        }
+      }
+      *(uint4*)(sx + (size_t)m * p.stride + kk) = v;
+    }
+    __syncthreads();
+    // ---- this warp's 32-wide k blocks of the chunk, four in flight
+    const int nblk = kn / 32;
+    for (int b = kg; b < nblk; b += n_kg * 4) {
+      uint4 ua[4], ub[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int blk = b + u * n_kg;
+        if (blk < nblk) {
+          ua[u] = ld_stream16(wa + k0 + blk * 32);
+          ub[u] = ld_stream16(wb + k0 + blk * 32);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int blk = b + u * n_kg;
+        if (blk < nblk) {
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint4 xb = *(const uint4*)(sx + (size_t)(mt * 8 + g) * p.stride + blk * 32 + t * 8);
+            mma16816(c[mt], ua[u].x, ub[u].x, ua[u].y, ub[u].y, xb.x, xb.y);
+            mma16816(c[mt], ua[u].z, ub[u].z, ua[u].w, ub[u].w, xb.z, xb.w);
+          }
+        }
+      }
+    }
+  }
+  // ---- add the warps' partial tiles in warp order, then the epilogue
+  __syncthreads();
+  float* red = (float*)sk_smem;                          // [SK_WARPS][16][MP]
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    const int m = mt * 8 + t * 2;
+    red[(warp * 16 + g) * MP + m] = c[mt][0];
+    red[(warp * 16 + g) * MP + m + 1] = c[mt][1];
+    red[(warp * 16 + g + 8) * MP + m] = c[mt][2];
+    red[(warp * 16 + g + 8) * MP + m + 1] = c[mt][3];
+  }
+  __syncthreads();
+  const int feats = 16 * p.ng;
+  for (int i = threadIdx.x; i < feats * MP; i += SK_THREADS) {
+    const int m = i / feats, ff = i % feats;             // consecutive threads -> consecutive n
+    const int n = blockIdx.x * feats + ff;
+    if (m >= M || n >= p.N) continue;
+    const int grp = ff / 16, f = ff % 16;
+    float v = 0.f;
+    for (int k8 = 0; k8 < n_kg; ++k8) v += red[((k8 * p.ng + grp) * 16 + f) * MP + m];
+    if (p.bias) v += p.bias[n];
+    v = apply_act(v, p.act);
+    if (p.residual) v += p.residual[(size_t)m * p.N + n];
+    if (p.out_f32) ((float*)p.out)[(size_t)m * p.N + n] = v;
+    else ((__nv_bfloat16*)p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
+  }
+}
+
+template <int MT>
+static int launch_skinny(const SkinnyParams& p, size_t smem, cudaStream_t st) {
+  auto kern = linear_skinny_kernel<MT>;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  const int per_cta = SK_FEATS * p.ng;
+  kern<<<(p.N + per_cta - 1) / per_cta, SK_THREADS, smem, st>>>(p);
+  HS_LAUNCH_CHECK();
+  return HS_OK;
+}
+
+}  // namespace hs
+
+// Refuses (HS_ERR_UNSUPPORTED) M > 64, K not a multiple of 32, and unaligned pointers; the
+// caller then uses another kernel.
+HS_EXPORT int hs_linear_skinny(void* out, const void* a, const float* x, const float* gamma,
+                               const float* beta, float eps, const void* w, const float* bias,
+                               const float* residual, int M, int N, int K, int act, int out_dtype,
+                               void* stream) {
+  using namespace hs;
+  if (!out || !w || (!a && !x)) return HS_ERR_ARGUMENT;
+  if (x && (!gamma || !beta)) return HS_ERR_ARGUMENT;
+  if (M <= 0 || N <= 0) return HS_OK;
+  if (M > 64 || K <= 0 || K % 32) return HS_ERR_UNSUPPORTED;
+  if (((uintptr_t)w & 15) || (a && ((uintptr_t)a & 15)) || (x && ((uintptr_t)x & 15)) ||
+      (gamma && ((uintptr_t)gamma & 15)) || (beta && ((uintptr_t)beta & 15)))
+    return HS_ERR_UNSUPPORTED;
+  if (act < HS_ACT_NONE || act > HS_ACT_GELU_ERF) return HS_ERR_UNSUPPORTED;
+  if (out_dtype != HS_DT_F32 && out_dtype != HS_DT_BF16) return HS_ERR_UNSUPPORTED;
+  const int mt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
+  const int mp = mt * 8;
+  // staging chunk: whole K if it fits ~96 KB, else the largest multiple of 256 that does
+  const size_t budget = 96 * 1024;
+  int kc = K;
+  if ((size_t)mp * (K + 64) * 2 > budget) {
+    kc = (int)(budget / (2 * (size_t)mp)) - 64;
+    kc = kc / 256 * 256;
+    if (kc < 256) return HS_ERR_UNSUPPORTED;
+  }
+  // row stride with (stride * 2) % 128 == 64: the fragment reads of two adjacent rows then
+  // fall into different halves of the 32 banks
+  int stride = kc + ((32 - kc % 64) + 64) % 64;
+  if (stride == kc) stride += 64;
+  size_t smem = (size_t)mp * stride * 2;
+  const size_t red = (size_t)SK_WARPS * 16 * mp * 4;
+  if (red > smem) smem = red;
+  SkinnyParams p;
+  p.a = (const __nv_bfloat16*)a; p.x = x; p.gamma = gamma; p.beta = beta;
+  p.w = (const __nv_bfloat16*)w; p.bias = bias; p.residual = residual; p.out = out;
+  p.M = M; p.N = N; p.K = K; p.act = act; p.out_f32 = out_dtype == HS_DT_F32; p.kc = kc;
+  p.stride = stride; p.eps = eps;
+  // more features per CTA (fewer re-stagings of the activations) while the grid still fills
+  // the GPU twice
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+  p.ng = 1;
+  while (p.ng < 8 && (N + 32 * p.ng - 1) / (32 * p.ng) >= 2 * sms) p.ng *= 2;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (mt) {
+    case 1: return launch_skinny<1>(p, smem, st);
+    case 2: return launch_skinny<2>(p, smem, st);
+    case 4: return launch_skinny<4>(p, smem, st);
+    default: return launch_skinny<8>(p, smem, st);
+  }
+}

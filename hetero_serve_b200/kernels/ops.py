@@ -109,6 +109,7 @@ def _declare(lib) -> None:
         "hs_layernorm": [P, P, P, P, P, I, I, F, I, P],
         "hs_linear_simt": [P, P, P, P, P, I, I, I, I, I, I, P],
         "hs_linear_tcgen05": [P, P, P, P, P, I, I, I, I, I, I, P, P],
+        "hs_linear_skinny": [P, P, P, P, P, F, P, P, P, I, I, I, I, I, P],
         "hs_kv_append": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "hs_attention_simt": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
         "hs_attention_decode": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P,
@@ -170,6 +171,7 @@ class CudaOps:
         self._scratch: dict = {}
         self._retired: list = []
         self.tile_n = 0            # 0: chosen per shape; 64/128/256 force a tile width
+        self.skinny_max_rows = 16  # up to this many rows the weight-streaming kernel is used
         # pipeline time-outs of the TMA/tcgen05 kernels are ORed into this word; the runner
         # replaces it with its own so that they surface with the step's results
         self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -252,6 +254,14 @@ class CudaOps:
         """bfloat16 goes to the tcgen05 kernel when TMA can address the operands (K a multiple
         of 8, 16-byte aligned pointers); everything else, and all of float32, to the CUDA cores."""
         self.launches += 1
+        if a.dtype == torch.bfloat16 and self.tensor_cores and (
+                M <= self.skinny_max_rows or (M <= 64 and N >= 16384)):
+            code = self.lib.hs_linear_skinny(
+                _ptr(out), _ptr(a), None, None, None, 0.0, _ptr(w), _ptr(bias), _ptr(residual),
+                M, N, K, act, _DT[out.dtype], self._stream())
+            if code != -1:
+                _check(code, f"linear_skinny(M={M},N={N},K={K})")
+                return
         if a.dtype == torch.bfloat16 and self.tensor_cores and K % 8 == 0:
             code = self.lib.hs_linear_tcgen05(
                 _ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), M, N, K, act,
