@@ -11,7 +11,8 @@
 // device memory (the batch's longest context / splits, rounded up to whole pages), which keeps a
 // captured CUDA graph valid while contexts grow.
 //
-// Inside a CTA each warp takes every 4th page of the slice.  A key row of D bfloat16 is read by
+// Inside a CTA each warp takes every 4th page of the slice; the next group of keys is loaded
+// while the current one is used.  A key row of D bfloat16 is read by
 // D/8 adjacent lanes with one 16-byte load each, so a warp covers 256/D keys per load and the
 // loads of a page (keys and values) are all in flight before the first is used.  Scores are
 // (q . k) * scale with the multiply after the dot product (heteroserve/model/torch_engine.py:135).
@@ -31,7 +32,7 @@ struct DecodeParams {
   const int* table;
   const int* tok_pos;
   const int* tok_req;
-  const int* tok_list;     // flat indices of the tokens this launch serves
+  const int* dec_info;     // per served token: flat index, request row, position
   const int* plan_head;    // [0] = number of tokens in tok_list, [2] = longest context among them
   float* acc;
   float* ml;
@@ -60,10 +61,9 @@ attention_decode_kernel(const DecodeParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = blockIdx.x;                       // index into tok_list
   const int h = blockIdx.y, split = blockIdx.z;
-  if (slot >= p.plan_head[0]) return;
-  const int t = p.tok_list[slot];
-  const int r = p.tok_req[t];
-  const int pos = p.tok_pos[t];
+  const int n_served = p.plan_head[0];
+  const int t = p.dec_info[3 * slot], r = p.dec_info[3 * slot + 1], pos = p.dec_info[3 * slot + 2];
+  if (slot >= n_served) return;
   __nv_bfloat16* orow = p.out + ((size_t)t * p.n_heads + h) * D;
   if (r < 0 || pos < 0 || pos / p.page_size >= p.max_pages) {
     if (split == 0)
@@ -98,52 +98,71 @@ attention_decode_kernel(const DecodeParams p) {
 
   if (k_begin < k_end) {
     const int pg_first = k_begin / PS, pg_last = (k_end - 1) / PS;
-    for (int pg = pg_first + warp; pg <= pg_last; pg += AD_WARPS) {
-      const int page = trow[pg];
-      if (page < 0 || page >= p.num_pages) {
-        if (lane == 0) atomicOr(p.status, HS_STATUS_BAD_PAGE);
-        continue;
-      }
-      const __nv_bfloat16* kbase = p.pool + (size_t)page * page_stride + (size_t)hk * tile;
+    // This warp's pages: pg_first + warp, + AD_WARPS, ...  Their page numbers are fetched at
+    // once, one per lane (the host keeps a slice within 32 pages per warp), so that no key
+    // load waits for a table lookup.
+    const int my_pg = pg_first + warp + AD_WARPS * lane;
+    const int my_page = my_pg <= pg_last ? trow[my_pg] : -1;
+    const int n_pages = (pg_last - pg_first - warp + AD_WARPS) / AD_WARPS;   // may be <= 0
+    constexpr int UNIT = 4 * KPW;                        // keys per unit of work
+    const int upp = (PS + UNIT - 1) / UNIT;              // units per page
+    const int n_units = n_pages > 0 ? n_pages * upp : 0;
+
+    struct Unit {
+      uint4 k[4], v[4];
+      int j0;                                            // position of the unit's first key
+      int g0;
+    };
+    auto load_unit = [&](int u, Unit& un) {
+      const int it = u / upp;
+      un.g0 = (u - it * upp) * UNIT;
+      const int pg = pg_first + warp + AD_WARPS * it;
+      const int page = __shfl_sync(0xffffffffu, my_page, it & 31);
+      un.j0 = pg * PS;
+      const bool page_ok = page >= 0 && page < p.num_pages;
+      if (!page_ok && lane == 0) atomicOr(p.status, HS_STATUS_BAD_PAGE);
+      const __nv_bfloat16* kbase = p.pool + (size_t)(page_ok ? page : 0) * page_stride +
+                                   (size_t)hk * tile;
       const __nv_bfloat16* vbase = kbase + (size_t)p.n_kv_heads * tile;
-      const int j0 = pg * PS;
-      // keys of this page in groups of KPW; a page of 16 and D = 64 gives 4 groups
-      for (int g0 = 0; g0 < PS; g0 += 4 * KPW) {
-        uint4 ku[4], vu[4];
-        float s[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int slot_in_page = g0 + i * KPW + sub;
-          const int j = j0 + slot_in_page;
-          const bool valid = slot_in_page < PS && j >= k_begin && j < k_end;
-          if (valid) {
-            ku[i] = *(const uint4*)(kbase + (size_t)slot_in_page * D + part * 8);
-            vu[i] = *(const uint4*)(vbase + (size_t)slot_in_page * D + part * 8);
-          } else {
-            ku[i] = make_uint4(0, 0, 0, 0);
-            vu[i] = make_uint4(0, 0, 0, 0);
-          }
+      for (int i = 0; i < 4; ++i) {
+        const int sip = un.g0 + i * KPW + sub;
+        const int j = un.j0 + sip;
+        if (page_ok && sip < PS && j >= k_begin && j < k_end) {
+          un.k[i] = *(const uint4*)(kbase + (size_t)sip * D + part * 8);
+          un.v[i] = *(const uint4*)(vbase + (size_t)sip * D + part * 8);
+        } else {
+          un.k[i] = make_uint4(0, 0, 0, 0);
+          un.v[i] = make_uint4(0, 0, 0, 0);
+          if (!page_ok) un.j0 = -(1 << 30);              // every key of it fails the range test
         }
-        float bm = -INFINITY;
+      }
+    };
+    Unit cur, nxt;
+    if (n_units > 0) load_unit(0, cur);
+    for (int u = 0; u < n_units; ++u) {
+      if (u + 1 < n_units) load_unit(u + 1, nxt);        // in flight while `cur` is used
+      float s[4];
+      float bm = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float kf[8];
-          unpack8(ku[i], kf);
-          float dot = 0.f;
+      for (int i = 0; i < 4; ++i) {
+        float kf[8];
+        unpack8(cur.k[i], kf);
+        float dot = 0.f;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) dot = fmaf(q[e], kf[e], dot);
+        for (int e = 0; e < 8; ++e) dot = fmaf(q[e], kf[e], dot);
 #pragma unroll
-          for (int o = 1; o < LPK; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-          const int slot_in_page = g0 + i * KPW + sub;
-          const int j = j0 + slot_in_page;
-          const bool valid = slot_in_page < PS && j >= k_begin && j < k_end;
-          s[i] = valid ? dot * p.scale : -INFINITY;
-          bm = fmaxf(bm, s[i]);
-        }
-        // maximum over the key groups of the warp (lanes with the same `part`)
+        for (int o = 1; o < LPK; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        const int sip = cur.g0 + i * KPW + sub;
+        const int j = cur.j0 + sip;
+        const bool valid = sip < PS && j >= k_begin && j < k_end;
+        s[i] = valid ? dot * p.scale : -INFINITY;
+        bm = fmaxf(bm, s[i]);
+      }
+      // maximum over the key groups of the warp (lanes with the same `part`)
 #pragma unroll
-        for (int o = LPK; o < 32; o <<= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
-        if (bm == -INFINITY) continue;
+      for (int o = LPK; o < 32; o <<= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+      if (bm != -INFINITY) {
         const float m_new = fmaxf(m, bm);
         const float corr = __expf(m - m_new);
         l *= corr;
@@ -154,12 +173,13 @@ attention_decode_kernel(const DecodeParams p) {
           const float pr = (s[i] == -INFINITY) ? 0.f : __expf(s[i] - m_new);
           l += pr;
           float vf[8];
-          unpack8(vu[i], vf);
+          unpack8(cur.v[i], vf);
 #pragma unroll
           for (int e = 0; e < 8; ++e) acc[e] = fmaf(pr, vf[e], acc[e]);
         }
         m = m_new;
       }
+      cur = nxt;
     }
   }
   // ---- combine the key groups of a warp, then the warps of the CTA (all share m per warp)
@@ -247,14 +267,14 @@ HS_EXPORT long long hs_attention_decode_scratch_floats(int token_cap, int n_head
 }
 
 HS_EXPORT int hs_attention_decode(void* out, const void* qkv, const void* pool, const int* table,
-                                  const int* tok_pos, const int* tok_req, const int* tok_list,
+                                  const int* tok_pos, const int* tok_req, const int* dec_info,
                                   const int* plan_head, int token_cap, int n_heads,
                                   int n_kv_heads, int head_dim, int page_size, int num_pages,
                                   int max_pages, int q_off, int qkv_stride, int window,
                                   float scale, int splits, float* scratch_acc, float* scratch_ml,
                                   int* counters, int* status, void* stream) {
   using namespace hs;
-  if (!out || !qkv || !pool || !table || !tok_pos || !tok_req || !tok_list || !plan_head ||
+  if (!out || !qkv || !pool || !table || !tok_pos || !tok_req || !dec_info || !plan_head ||
       !status)
     return HS_ERR_ARGUMENT;
   if (token_cap <= 0) return HS_OK;
@@ -263,11 +283,13 @@ HS_EXPORT int hs_attention_decode(void* out, const void* qkv, const void* pool, 
   if (n_heads > 65535) return HS_ERR_UNSUPPORTED;
   if (splits > 1 && (!scratch_acc || !scratch_ml || !counters)) return HS_ERR_ARGUMENT;
   if ((qkv_stride % 8) || (q_off % 8)) return HS_ERR_UNSUPPORTED;   // 16-byte query loads
+  // a slice may span at most 32 pages per warp
+  if ((long long)splits * 32 * hs::AD_WARPS < max_pages) return HS_ERR_UNSUPPORTED;
   DecodeParams p;
   p.qkv = (const __nv_bfloat16*)qkv;
   p.pool = (const __nv_bfloat16*)pool;
   p.out = (__nv_bfloat16*)out;
-  p.table = table; p.tok_pos = tok_pos; p.tok_req = tok_req; p.tok_list = tok_list;
+  p.table = table; p.tok_pos = tok_pos; p.tok_req = tok_req; p.dec_info = dec_info;
   p.plan_head = plan_head; p.acc = scratch_acc; p.ml = scratch_ml; p.counters = counters;
   p.status = status;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;

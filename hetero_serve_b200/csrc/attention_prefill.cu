@@ -16,7 +16,8 @@
 // no special case.  Tiles past a warp's last query are skipped.
 //
 // Work list (device memory, written by the host per step): plan_head[1] = number of tiles;
-// tile_tok[i] = flat index of the tile's first query, tile_n[i] = its number of queries (<= 64).
+// tile_info[4 i ..] = flat index of the tile's first query, its number of queries (<= 64), its
+// request's row in the block table, the position of its first query.
 #include "common.cuh"
 
 namespace hs {
@@ -30,8 +31,7 @@ struct PrefillParams {
   const int* table;
   const int* tok_pos;
   const int* tok_req;
-  const int* tile_tok;
-  const int* tile_n;
+  const int* tile_info;    // per tile: first query's flat index, queries, request row, first position
   const int* plan_head;
   int* status;
   int n_heads, n_kv_heads, page_size, num_pages, max_pages;
@@ -93,11 +93,10 @@ attention_prefill_kernel(const PrefillParams p) {
   uint4* sV = sK + 2 * AP_BKV * CPR;                     // [2][64][CPR]
 
   const int tile = blockIdx.x, h = blockIdx.y;
-  if (tile >= p.plan_head[1]) return;
-  const int tok0 = p.tile_tok[tile];
-  const int nq = p.tile_n[tile];
-  const int r = p.tok_req[tok0];
-  const int pos0 = p.tok_pos[tok0];
+  const int n_tiles_served = p.plan_head[1];
+  const int4 ti = *(const int4*)(p.tile_info + 4 * tile);
+  if (tile >= n_tiles_served) return;
+  const int tok0 = ti.x, nq = ti.y, r = ti.z, pos0 = ti.w;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   if (r < 0 || nq <= 0 || pos0 < 0) return;
@@ -292,13 +291,13 @@ static int launch_prefill(const PrefillParams& p, int tile_cap, cudaStream_t st)
 }  // namespace hs
 
 HS_EXPORT int hs_attention_prefill(void* out, const void* qkv, const void* pool, const int* table,
-                                   const int* tok_pos, const int* tok_req, const int* tile_tok,
-                                   const int* tile_n, const int* plan_head, int tile_cap,
+                                   const int* tok_pos, const int* tok_req, const int* tile_info,
+                                   const int* plan_head, int tile_cap,
                                    int n_heads, int n_kv_heads, int head_dim, int page_size,
                                    int num_pages, int max_pages, int q_off, int qkv_stride,
                                    float scale, int* status, void* stream) {
   using namespace hs;
-  if (!out || !qkv || !pool || !table || !tok_pos || !tok_req || !tile_tok || !tile_n ||
+  if (!out || !qkv || !pool || !table || !tok_pos || !tok_req || !tile_info ||
       !plan_head || !status)
     return HS_ERR_ARGUMENT;
   if (tile_cap <= 0) return HS_OK;
@@ -309,7 +308,7 @@ HS_EXPORT int hs_attention_prefill(void* out, const void* qkv, const void* pool,
   PrefillParams p;
   p.qkv = (const __nv_bfloat16*)qkv; p.pool = (const __nv_bfloat16*)pool;
   p.out = (__nv_bfloat16*)out; p.table = table; p.tok_pos = tok_pos; p.tok_req = tok_req;
-  p.tile_tok = tile_tok; p.tile_n = tile_n; p.plan_head = plan_head; p.status = status;
+  p.tile_info = tile_info; p.plan_head = plan_head; p.status = status;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
   p.num_pages = num_pages; p.max_pages = max_pages; p.q_off = q_off; p.qkv_stride = qkv_stride;
   p.scale = scale;

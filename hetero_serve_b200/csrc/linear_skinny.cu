@@ -10,10 +10,13 @@
 // the registers of two MMA k-steps — the k order inside a 32-wide block is permuted the same way
 // for both operands, which a dot product allows — so the weights are read once, fully coalesced,
 // with no shared-memory round trip.  The activations (M_pad x K, bfloat16) sit in shared memory,
-// padded so that the 16-byte fragment reads are conflict-free.  A CTA = 8 warps owns 16 features;
-// the warps take the 32-wide k blocks round-robin and their partial tiles are added in warp
-// order (for a wide layer such as the vocabulary head a CTA owns up to 128 features, 16 per
-// warp, so that the activations are staged less often) (a fixed order: no atomics), then bias, activation and the float32 residual are applied.
+// padded so that the 16-byte fragment reads are conflict-free.  A CTA = 8 warps owns 16 features
+// (up to 128 for a wide layer such as the vocabulary head, so that the activations are staged
+// less often); its warps take the 32-wide k blocks round-robin and their partial tiles are added
+// in warp order.  Narrow, deep layers are also split over k between CTAs: each writes its share
+// to scratch memory and the last to arrive (a counter in scratch) adds the shares in split
+// order.  Every order is fixed, there are no floating-point atomics; then bias, activation
+// and the float32 residual are applied.
 //
 // Optional fused LayerNorm (the reference's `F.layer_norm` before each projection,
 // heteroserve/model/torch_engine.py:74-75,121,140): every CTA normalises the M rows itself
@@ -49,9 +52,16 @@ struct SkinnyParams {
   const float* bias;
   const float* residual;
   void* out;
-  int M, N, K, act, out_f32, kc, stride;   // kc: k per staging chunk; stride: smem row stride
-  int ng;                                  // feature groups (of 16) per CTA: 1, 2, 4 or 8
+  float* partial;              // [ksplit][MP][N] float32 scratch (ksplit > 1)
+  int* counters;               // one per feature block, zero between launches (ksplit > 1)
+  int M, N, K, act, out_f32;
+  int kper, stride;            // k per CTA (multiple of 32); smem row stride in elements
+  int ng;                      // feature groups (of 16) per CTA: 1, 2, 4 or 8
   float eps;
+};
+
+struct WBatch {
+  uint4 a[4], b[4];
 };
 
 template <int MT>
@@ -61,25 +71,54 @@ linear_skinny_kernel(const SkinnyParams p) {
   extern __shared__ __align__(16) uint8_t sk_smem[];
   __nv_bfloat16* sx = (__nv_bfloat16*)sk_smem;             // [MP][stride]
   __shared__ float s_mu[MP], s_rs[MP];
+  __shared__ int s_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   // warp -> (feature group, k group): ng groups of 16 features, 8 / ng warps share each
   const int fg = warp % p.ng, kg = warp / p.ng, n_kg = SK_WARPS / p.ng;
   const int n0 = (blockIdx.x * p.ng + fg) * SK_FEATS;
   const int K = p.K, M = p.M;
+  const int ksplit = gridDim.y;
+  const int k0 = blockIdx.y * p.kper;
+  const int kn = min(p.kper, K - k0);                       // may be <= 0 for the last splits
+  const int nblk = kn > 0 ? kn / 32 : 0;
+
+  const int row_a = min(n0 + g, p.N - 1), row_b = min(n0 + g + 8, p.N - 1);   // clamped: never stored
+  const __nv_bfloat16* wa = p.w + (size_t)row_a * K + k0 + t * 8;
+  const __nv_bfloat16* wb = p.w + (size_t)row_b * K + k0 + t * 8;
+  auto load_batch = [&](int b, WBatch& wbt) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int blk = b + u * n_kg;
+      if (blk < nblk) {
+        wbt.a[u] = ld_stream16(wa + blk * 32);
+        wbt.b[u] = ld_stream16(wb + blk * 32);
+      }
+    }
+  };
+  // the first weight fragments are requested before anything else: they do not depend on the
+  // activations, so their latency overlaps the staging below
+  WBatch cur;
+  load_batch(kg, cur);
 
   if (p.x) {        // LayerNorm statistics of every row, one warp per row
     for (int m = warp; m < MP; m += SK_WARPS) {
       float mu = 0.f, rs = 0.f;
       if (m < M) {
-        const float* xr = p.x + (size_t)m * K;
+        const float4* xr = (const float4*)(p.x + (size_t)m * K);
         float s = 0.f;
-        for (int k = lane; k < K; k += 32) s += xr[k];
+#pragma unroll 8
+        for (int k = lane; k < K / 4; k += 32) {
+          const float4 v = xr[k];
+          s += (v.x + v.y) + (v.z + v.w);
+        }
         mu = warp_sum(s) / (float)K;
         float q = 0.f;
-        for (int k = lane; k < K; k += 32) {
-          const float c = xr[k] - mu;
-          q += c * c;
+#pragma unroll 8
+        for (int k = lane; k < K / 4; k += 32) {
+          const float4 v = xr[k];
+          const float c0 = v.x - mu, c1 = v.y - mu, c2 = v.z - mu, c3 = v.w - mu;
+          q += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
         }
         rs = 1.0f / sqrtf(warp_sum(q) / (float)K + p.eps);
       }
@@ -91,18 +130,9 @@ linear_skinny_kernel(const SkinnyParams p) {
     __syncthreads();
   }
 
-  float c[MT][4];
-#pragma unroll
-  for (int i = 0; i < MT; ++i) c[i][0] = c[i][1] = c[i][2] = c[i][3] = 0.f;
-
-  const int row_a = min(n0 + g, p.N - 1), row_b = min(n0 + g + 8, p.N - 1);   // clamped: never stored
-  const __nv_bfloat16* wa = p.w + (size_t)row_a * K + t * 8;
-  const __nv_bfloat16* wb = p.w + (size_t)row_b * K + t * 8;
-
-  for (int k0 = 0; k0 < K; k0 += p.kc) {
-    const int kn = min(p.kc, K - k0);
-    if (k0 > 0) __syncthreads();            // the previous chunk has been consumed
-    // ---- stage activations [MP][kn] (rows past M are zero)
+  // ---- stage this CTA's k range of the activations [MP][kn] (rows past M are zero)
+  if (kn > 0) {
+#pragma unroll 4
     for (int i = threadIdx.x; i < MP * (kn / 8); i += SK_THREADS) {
       const int m = i / (kn / 8), kk = (i % (kn / 8)) * 8;
       uint4 v = make_uint4(0, 0, 0, 0);
@@ -129,34 +159,31 @@ linear_skinny_kernel(const SkinnyParams p) {
       }
       *(uint4*)(sx + (size_t)m * p.stride + kk) = v;
     }
-    __syncthreads();
-    // ---- this warp's 32-wide k blocks of the chunk, four in flight
-    const int nblk = kn / 32;
-    for (int b = kg; b < nblk; b += n_kg * 4) {
-      uint4 ua[4], ub[4];
+  }
+  __syncthreads();
+
+  float c[MT][4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int blk = b + u * n_kg;
-        if (blk < nblk) {
-          ua[u] = ld_stream16(wa + k0 + blk * 32);
-          ub[u] = ld_stream16(wb + k0 + blk * 32);
-        }
-      }
+  for (int i = 0; i < MT; ++i) c[i][0] = c[i][1] = c[i][2] = c[i][3] = 0.f;
+  // ---- this warp's 32-wide k blocks, four per batch, the next batch in flight meanwhile
+  for (int b = kg; b < nblk; b += n_kg * 4) {
+    WBatch nxt;
+    load_batch(b + n_kg * 4, nxt);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int blk = b + u * n_kg;
-        if (blk < nblk) {
+    for (int u = 0; u < 4; ++u) {
+      const int blk = b + u * n_kg;
+      if (blk < nblk) {
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            const uint4 xb = *(const uint4*)(sx + (size_t)(mt * 8 + g) * p.stride + blk * 32 + t * 8);
-            mma16816(c[mt], ua[u].x, ub[u].x, ua[u].y, ub[u].y, xb.x, xb.y);
-            mma16816(c[mt], ua[u].z, ub[u].z, ua[u].w, ub[u].w, xb.z, xb.w);
-          }
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint4 xb = *(const uint4*)(sx + (size_t)(mt * 8 + g) * p.stride + blk * 32 + t * 8);
+          mma16816(c[mt], cur.a[u].x, cur.b[u].x, cur.a[u].y, cur.b[u].y, xb.x, xb.y);
+          mma16816(c[mt], cur.a[u].z, cur.b[u].z, cur.a[u].w, cur.b[u].w, xb.z, xb.w);
         }
       }
     }
+    cur = nxt;
   }
-  // ---- add the warps' partial tiles in warp order, then the epilogue
+  // ---- add the warps' partial tiles in warp order
   __syncthreads();
   float* red = (float*)sk_smem;                          // [SK_WARPS][16][MP]
 #pragma unroll
@@ -169,23 +196,49 @@ linear_skinny_kernel(const SkinnyParams p) {
   }
   __syncthreads();
   const int feats = 16 * p.ng;
+  if (ksplit > 1) {
+    // this CTA's share goes to scratch; the last CTA of the feature block to arrive adds the
+    // shares in split order
+    float* mine = p.partial + (size_t)blockIdx.y * MP * p.N;
+    for (int i = threadIdx.x; i < feats * MP; i += SK_THREADS) {
+      const int m = i / feats, ff = i % feats;
+      const int n = blockIdx.x * feats + ff;
+      if (n >= p.N) continue;
+      const int grp = ff / 16, f = ff % 16;
+      float v = 0.f;
+      for (int k8 = 0; k8 < n_kg; ++k8) v += red[((k8 * p.ng + grp) * 16 + f) * MP + m];
+      mine[(size_t)m * p.N + n] = v;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(&p.counters[blockIdx.x], 1) == ksplit - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+  }
   for (int i = threadIdx.x; i < feats * MP; i += SK_THREADS) {
     const int m = i / feats, ff = i % feats;             // consecutive threads -> consecutive n
     const int n = blockIdx.x * feats + ff;
     if (m >= M || n >= p.N) continue;
-    const int grp = ff / 16, f = ff % 16;
     float v = 0.f;
-    for (int k8 = 0; k8 < n_kg; ++k8) v += red[((k8 * p.ng + grp) * 16 + f) * MP + m];
+    if (ksplit > 1) {
+      for (int ks = 0; ks < ksplit; ++ks)
+        v += __ldcg(p.partial + ((size_t)ks * MP + m) * p.N + n);
+    } else {
+      const int grp = ff / 16, f = ff % 16;
+      for (int k8 = 0; k8 < n_kg; ++k8) v += red[((k8 * p.ng + grp) * 16 + f) * MP + m];
+    }
     if (p.bias) v += p.bias[n];
     v = apply_act(v, p.act);
     if (p.residual) v += p.residual[(size_t)m * p.N + n];
     if (p.out_f32) ((float*)p.out)[(size_t)m * p.N + n] = v;
     else ((__nv_bfloat16*)p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
   }
+  if (ksplit > 1 && threadIdx.x == 0) p.counters[blockIdx.x] = 0;   // ready for the next launch
 }
 
 template <int MT>
-static int launch_skinny(const SkinnyParams& p, size_t smem, cudaStream_t st) {
+static int launch_skinny(const SkinnyParams& p, int ksplit, size_t smem, cudaStream_t st) {
   auto kern = linear_skinny_kernel<MT>;
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
@@ -195,62 +248,93 @@ static int launch_skinny(const SkinnyParams& p, size_t smem, cudaStream_t st) {
     configured = smem;
   }
   const int per_cta = SK_FEATS * p.ng;
-  kern<<<(p.N + per_cta - 1) / per_cta, SK_THREADS, smem, st>>>(p);
+  dim3 grid((p.N + per_cta - 1) / per_cta, ksplit);
+  kern<<<grid, SK_THREADS, smem, st>>>(p);
   HS_LAUNCH_CHECK();
   return HS_OK;
 }
 
+struct SkinnyPlan {
+  int mt, mp, ng, ksplit, kper, stride, blocks;
+  size_t smem;
+};
+
+// How a shape is cut: features per CTA, splits over k, shared memory.  Returns false for
+// shapes the kernel does not take.
+static bool plan_skinny(int M, int N, int K, SkinnyPlan& pl) {
+  if (M <= 0 || M > 64 || K <= 0 || K % 32) return false;
+  pl.mt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
+  pl.mp = pl.mt * 8;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+  // more features per CTA (the activations are staged less often) while the grid still fills
+  // the GPU twice
+  pl.ng = 1;
+  while (pl.ng < 8 && (N + 32 * pl.ng - 1) / (32 * pl.ng) >= 2 * sms) pl.ng *= 2;
+  pl.blocks = (N + 16 * pl.ng - 1) / (16 * pl.ng);
+  // k per CTA: at most what fits ~96 KB of shared memory, at least 1024 (four blocks a warp),
+  // and few enough splits that about two CTAs per SM are in flight
+  const size_t budget = 96 * 1024;
+  int kc = (int)(budget / (2 * (size_t)pl.mp)) - 64;
+  kc = kc / 32 * 32;
+  if (kc < 256) return false;
+  int want = (2 * sms + pl.blocks - 1) / pl.blocks;
+  int by_size = K / 1024 > 0 ? K / 1024 : 1;
+  int ksplit = want < by_size ? want : by_size;
+  const int need = (K + kc - 1) / kc;
+  if (ksplit < need) ksplit = need;
+  if (ksplit < 1) ksplit = 1;
+  pl.kper = ((K / 32 + ksplit - 1) / ksplit) * 32;
+  pl.ksplit = (K + pl.kper - 1) / pl.kper;
+  pl.stride = pl.kper + ((32 - pl.kper % 64) + 64) % 64;       // stride % 64 == 32
+  if (pl.stride % 64 != 32) pl.stride += 32;
+  pl.smem = (size_t)pl.mp * pl.stride * 2;
+  const size_t red = (size_t)SK_WARPS * 16 * pl.mp * 4;
+  if (red > pl.smem) pl.smem = red;
+  return true;
+}
+
 }  // namespace hs
+
+// Scratch a launch needs: floats for the partial sums and ints for the counters (both zero for
+// shapes that are not split over k).  Negative: the shape is not taken.
+HS_EXPORT int hs_linear_skinny_scratch(int M, int N, int K, long long* floats, int* counters) {
+  hs::SkinnyPlan pl;
+  if (!hs::plan_skinny(M, N, K, pl)) return HS_ERR_UNSUPPORTED;
+  *floats = pl.ksplit > 1 ? (long long)pl.ksplit * pl.mp * N : 0;
+  *counters = pl.ksplit > 1 ? pl.blocks : 0;
+  return HS_OK;
+}
 
 // Refuses (HS_ERR_UNSUPPORTED) M > 64, K not a multiple of 32, and unaligned pointers; the
 // caller then uses another kernel.
 HS_EXPORT int hs_linear_skinny(void* out, const void* a, const float* x, const float* gamma,
                                const float* beta, float eps, const void* w, const float* bias,
                                const float* residual, int M, int N, int K, int act, int out_dtype,
-                               void* stream) {
+                               float* scratch, int* counters, void* stream) {
   using namespace hs;
   if (!out || !w || (!a && !x)) return HS_ERR_ARGUMENT;
   if (x && (!gamma || !beta)) return HS_ERR_ARGUMENT;
   if (M <= 0 || N <= 0) return HS_OK;
-  if (M > 64 || K <= 0 || K % 32) return HS_ERR_UNSUPPORTED;
+  SkinnyPlan pl;
+  if (!plan_skinny(M, N, K, pl)) return HS_ERR_UNSUPPORTED;
   if (((uintptr_t)w & 15) || (a && ((uintptr_t)a & 15)) || (x && ((uintptr_t)x & 15)) ||
       (gamma && ((uintptr_t)gamma & 15)) || (beta && ((uintptr_t)beta & 15)))
     return HS_ERR_UNSUPPORTED;
   if (act < HS_ACT_NONE || act > HS_ACT_GELU_ERF) return HS_ERR_UNSUPPORTED;
   if (out_dtype != HS_DT_F32 && out_dtype != HS_DT_BF16) return HS_ERR_UNSUPPORTED;
-  const int mt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
-  const int mp = mt * 8;
-  // staging chunk: whole K if it fits ~96 KB, else the largest multiple of 256 that does
-  const size_t budget = 96 * 1024;
-  int kc = K;
-  if ((size_t)mp * (K + 64) * 2 > budget) {
-    kc = (int)(budget / (2 * (size_t)mp)) - 64;
-    kc = kc / 256 * 256;
-    if (kc < 256) return HS_ERR_UNSUPPORTED;
-  }
-  // row stride with (stride * 2) % 128 == 64: the fragment reads of two adjacent rows then
-  // fall into different halves of the 32 banks
-  int stride = kc + ((32 - kc % 64) + 64) % 64;
-  if (stride == kc) stride += 64;
-  size_t smem = (size_t)mp * stride * 2;
-  const size_t red = (size_t)SK_WARPS * 16 * mp * 4;
-  if (red > smem) smem = red;
+  if (pl.ksplit > 1 && (!scratch || !counters)) return HS_ERR_ARGUMENT;
   SkinnyParams p;
   p.a = (const __nv_bfloat16*)a; p.x = x; p.gamma = gamma; p.beta = beta;
   p.w = (const __nv_bfloat16*)w; p.bias = bias; p.residual = residual; p.out = out;
-  p.M = M; p.N = N; p.K = K; p.act = act; p.out_f32 = out_dtype == HS_DT_F32; p.kc = kc;
-  p.stride = stride; p.eps = eps;
-  // more features per CTA (fewer re-stagings of the activations) while the grid still fills
-  // the GPU twice
-  int sms = 148;
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
-  p.ng = 1;
-  while (p.ng < 8 && (N + 32 * p.ng - 1) / (32 * p.ng) >= 2 * sms) p.ng *= 2;
+  p.partial = scratch; p.counters = counters;
+  p.M = M; p.N = N; p.K = K; p.act = act; p.out_f32 = out_dtype == HS_DT_F32;
+  p.kper = pl.kper; p.stride = pl.stride; p.ng = pl.ng; p.eps = eps;
   cudaStream_t st = (cudaStream_t)stream;
-  switch (mt) {
-    case 1: return launch_skinny<1>(p, smem, st);
-    case 2: return launch_skinny<2>(p, smem, st);
-    case 4: return launch_skinny<4>(p, smem, st);
-    default: return launch_skinny<8>(p, smem, st);
+  switch (pl.mt) {
+    case 1: return launch_skinny<1>(p, pl.ksplit, pl.smem, st);
+    case 2: return launch_skinny<2>(p, pl.ksplit, pl.smem, st);
+    case 4: return launch_skinny<4>(p, pl.ksplit, pl.smem, st);
+    default: return launch_skinny<8>(p, pl.ksplit, pl.smem, st);
   }
 }

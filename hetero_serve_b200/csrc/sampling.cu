@@ -52,6 +52,7 @@ __device__ ArgMax block_argmax(const float* row, int vocab) {
   __shared__ ArgMax sh[SM_THREADS / 32];
   __shared__ ArgMax result;
   ArgMax best{-INFINITY, 0x7fffffff};
+#pragma unroll 8
   for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
     const float v = row[i];
     if (v > best.v || best.i == 0x7fffffff) best = ArgMax{v, i};  // first seen wins ties

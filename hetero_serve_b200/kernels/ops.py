@@ -53,9 +53,10 @@ class AttentionPlan:
     """Work lists of one step for the specialised attention kernels, in device memory.
 
     ``data`` (int32): ``[0]`` number of single-query tokens, ``[1]`` number of 64-query
-    tiles, ``[2]`` longest context among the single-query tokens, ``[3]`` unused; then the
-    flat indices of the single-query tokens (``n_rows`` entries), then for each tile the
-    flat index of its first query and its number of queries (``tile_slots`` entries each).
+    tiles, ``[2]`` longest context among the single-query tokens, ``[3]`` unused; then per
+    single-query token (``n_rows`` slots) its flat index, request row and position; then per
+    tile (``tile_slots`` slots) the flat index of its first query, its number of queries, its
+    request row and the position of its first query.
     ``decode_cap`` / ``tile_cap`` are the grid sizes the kernels are launched with (at
     least the counts; fixed per size class so that a captured graph stays valid)."""
 
@@ -73,15 +74,23 @@ DECODE_MAX_NEW = 4        # requests bringing at most this many tokens use the d
 PREFILL_TILE = 64
 
 
-def plan_tile_slots(n_rows: int) -> int:
-    return n_rows // PREFILL_TILE + n_rows // (DECODE_MAX_NEW + 1) + 1
-
-
 def _pow2(n: int) -> int:
     b = 1
     while b < n:
         b *= 2
     return b
+
+
+def plan_tile_slots(n_rows: int) -> int:
+    """Tile entries a plan holds: every tile a batch of n_rows tokens can have, rounded up to
+    a power of two (grids are sized in powers of two when steps are captured)."""
+    return _pow2(n_rows // PREFILL_TILE + n_rows // (DECODE_MAX_NEW + 1) + 1)
+
+
+def plan_decode_ints(n_rows: int) -> int:
+    """Ints of the single-query section: 3 per token, padded so that the tile section that
+    follows is 16-byte aligned."""
+    return (3 * n_rows + 3) // 4 * 4
 
 
 _ERRORS = {-1: "unsupported size, type or option", -2: "bad argument"}
@@ -109,12 +118,13 @@ def _declare(lib) -> None:
         "hs_layernorm": [P, P, P, P, P, I, I, F, I, P],
         "hs_linear_simt": [P, P, P, P, P, I, I, I, I, I, I, P],
         "hs_linear_tcgen05": [P, P, P, P, P, I, I, I, I, I, I, P, P],
-        "hs_linear_skinny": [P, P, P, P, P, F, P, P, P, I, I, I, I, I, P],
+        "hs_linear_skinny": [P, P, P, P, P, F, P, P, P, I, I, I, I, I, P, P, P],
+        "hs_linear_skinny_scratch": [I, I, I, P, P],
         "hs_kv_append": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "hs_attention_simt": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
         "hs_attention_decode": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P,
                                 P, P, P],
-        "hs_attention_prefill": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
+        "hs_attention_prefill": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
         "hs_argmax": [P, P, I, I, P],
         "hs_sample": [P, P, P, P, P, P, P, I, I, P],
     }
@@ -168,6 +178,8 @@ class CudaOps:
         self.tensor_cores = True   # bfloat16 linears on tcgen05 (False: CUDA cores, for tests)
         self.fast_attention = True  # bfloat16 attention on the split-context / tensor-core kernels
         self.sm_count = torch.cuda.get_device_properties(0).multi_processor_count
+        self.fuse_norm = True      # LayerNorm fused into the few-row linear kernel
+        self._skinny_need: dict = {}
         self._scratch: dict = {}
         self._retired: list = []
         self.tile_n = 0            # 0: chosen per shape; 64/128/256 force a tile width
@@ -254,13 +266,8 @@ class CudaOps:
         """bfloat16 goes to the tcgen05 kernel when TMA can address the operands (K a multiple
         of 8, 16-byte aligned pointers); everything else, and all of float32, to the CUDA cores."""
         self.launches += 1
-        if a.dtype == torch.bfloat16 and self.tensor_cores and (
-                M <= self.skinny_max_rows or (M <= 64 and N >= 16384)):
-            code = self.lib.hs_linear_skinny(
-                _ptr(out), _ptr(a), None, None, None, 0.0, _ptr(w), _ptr(bias), _ptr(residual),
-                M, N, K, act, _DT[out.dtype], self._stream())
-            if code != -1:
-                _check(code, f"linear_skinny(M={M},N={N},K={K})")
+        if a.dtype == torch.bfloat16 and self._skinny_ok(M, N, K):
+            if self._skinny(out, a, None, w, bias, act, residual, M, N, K):
                 return
         if a.dtype == torch.bfloat16 and self.tensor_cores and K % 8 == 0:
             code = self.lib.hs_linear_tcgen05(
@@ -272,6 +279,65 @@ class CudaOps:
         _check(self.lib.hs_linear_simt(_ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual),
                                        M, N, K, act, _DT[a.dtype], _DT[out.dtype],
                                        self._stream()), f"linear(M={M},N={N},K={K})")
+
+    def _skinny_ok(self, M, N, K) -> bool:
+        return self.tensor_cores and (M <= self.skinny_max_rows or (M <= 64 and N >= 16384))
+
+    def _skinny(self, out, a, norm, w, bias, act, residual, M, N, K) -> bool:
+        """The weight-streaming kernel; ``norm = (x, gamma, beta, eps)`` fuses a LayerNorm of
+        the float32 input.  False when the kernel does not take the shape."""
+        key = (M, N, K)
+        need = self._skinny_need.get(key)
+        if need is None:
+            floats, counters = ctypes.c_longlong(0), ctypes.c_int(0)
+            code = self.lib.hs_linear_skinny_scratch(M, N, K, ctypes.byref(floats),
+                                                     ctypes.byref(counters))
+            need = (floats.value, counters.value) if code == 0 else False
+            self._skinny_need[key] = need
+        if need is False:
+            return False
+        scratch = cnt = None
+        if need[0]:
+            scratch = self._scratch_buffer("skinny_partial", need[0], torch.float32)
+            cnt = self._scratch_buffer("skinny_counters", need[1], torch.int32)
+        x = g = b = None
+        eps = 0.0
+        if norm is not None:
+            x, g, b, eps = norm
+        code = self.lib.hs_linear_skinny(
+            _ptr(out), _ptr(a), _ptr(x), _ptr(g), _ptr(b), float(eps), _ptr(w), _ptr(bias),
+            _ptr(residual), M, N, K, act, _DT[out.dtype], _ptr(scratch), _ptr(cnt),
+            self._stream())
+        if code == -1:
+            return False
+        _check(code, f"linear_skinny(M={M},N={N},K={K})")
+        return True
+
+    def norm_linear(self, out, h, x, gamma, beta, eps, w, bias=None, act="none"):
+        """out = act(LayerNorm(x) @ w.T + bias).  For few rows the normalisation is fused into
+        the weight-streaming kernel; otherwise ``h`` receives LayerNorm(x) first."""
+        M, K = x.shape
+        N = w.shape[0]
+        if (w.dtype == torch.bfloat16 and self.fuse_norm and self._skinny_ok(M, N, K)):
+            _want(x, "x", torch.float32, 2)
+            _want(w, "w", torch.bfloat16, 2)
+            _want(out, "out", _FLOATS, 2)
+            _want(gamma, "gamma", torch.float32, 1)
+            _want(beta, "beta", torch.float32, 1)
+            if w.shape[1] != K or tuple(out.shape) != (M, N) or gamma.shape[0] != K \
+                    or beta.shape[0] != K:
+                raise KernelError("norm_linear: shapes do not fit")
+            if bias is not None:
+                _want(bias, "bias", torch.float32, 1)
+            if act not in ACTIVATIONS:
+                raise KernelError(f"norm_linear: unknown activation {act!r}")
+            self.launches += 1
+            if self._skinny(out, None, (x, gamma, beta, eps), w, bias, ACTIVATIONS[act], None,
+                            M, N, K):
+                return
+            self.launches -= 1
+        self.layernorm(h, x, gamma, beta, eps)
+        self.linear(out, h, w, bias, act=act)
 
     # -- cache and attention ------------------------------------------------------
     def _attn_common(self, qkv, pool, table, tok_pos, tok_req, g, n):
@@ -319,7 +385,7 @@ class CudaOps:
     # -- attention work lists ---------------------------------------------------------
     @staticmethod
     def attention_plan_ints(n_rows: int, n_requests: int) -> int:
-        return 4 + n_rows + 2 * plan_tile_slots(n_rows)
+        return 4 + plan_decode_ints(n_rows) + 4 * plan_tile_slots(n_rows)
 
     @staticmethod
     def plan_attention(view, host_batch, n_rows: int, n_requests: int, page_size: int,
@@ -328,22 +394,20 @@ class CudaOps:
         as ``[(request, slot, start, n_new)]`` in flat order; returns ``(decode_cap,
         tile_cap)``.  Requests bringing up to DECODE_MAX_NEW tokens go to the single-query
         list, the others are cut into tiles of 64 queries."""
-        slots = plan_tile_slots(n_rows)
-        tok_list = view[4:4 + n_rows]
-        tile_tok = view[4 + n_rows:4 + n_rows + slots]
-        tile_n = view[4 + n_rows + slots:4 + n_rows + 2 * slots]
+        dec = view[4:4 + 3 * n_rows]
+        tiles = view[4 + plan_decode_ints(n_rows):]
         n_dec = n_tiles = max_ctx = 0
         t = 0
-        for _req, _slot, start, n in host_batch:
+        for row, (_req, _slot, start, n) in enumerate(host_batch):
             if n <= DECODE_MAX_NEW:
                 for i in range(n):
-                    tok_list[n_dec] = t + i
+                    dec[3 * n_dec:3 * n_dec + 3] = (t + i, row, start + i)
                     n_dec += 1
                 max_ctx = max(max_ctx, start + n)
             else:
                 for q0 in range(0, n, PREFILL_TILE):
-                    tile_tok[n_tiles] = t + q0
-                    tile_n[n_tiles] = min(PREFILL_TILE, n - q0)
+                    tiles[4 * n_tiles:4 * n_tiles + 4] = (t + q0, min(PREFILL_TILE, n - q0), row,
+                                                          start + q0)
                     n_tiles += 1
             t += n
         view[0], view[1], view[2], view[3] = n_dec, n_tiles, max_ctx, 0
@@ -372,10 +436,11 @@ class CudaOps:
 
     def decode_splits(self, decode_cap: int, n_heads: int, max_context: int) -> int:
         """Slices the context of a single-query token is cut into: enough CTAs to fill the
-        GPU twice, slices of at least 64 keys (in the manner of the reference's
+        GPU four times, slices of at least 64 keys (in the manner of the reference's
         ``choose_num_splits``, heteroserve/model/paged_attn_v3.py:212-232)."""
-        want = -(-2 * self.sm_count // max(1, decode_cap * n_heads))
-        return max(1, min(want, max(1, max_context // 64), 32))
+        want = -(-4 * self.sm_count // max(1, decode_cap * n_heads))
+        need = -(-max_context // (128 * 16))     # a slice spans at most 32 pages per warp
+        return max(1, need, min(want, max(1, max_context // 64), 32))
 
     FAST_HEAD_DIMS = (16, 32, 64, 128)
 
@@ -394,11 +459,10 @@ class CudaOps:
 
     def _attention_fast(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan):
         d = plan.data
-        nr, slots = plan.n_rows, plan.tile_slots
+        nr = plan.n_rows
         head = d
-        tok_list = d[4:]
-        tile_tok = d[4 + nr:]
-        tile_n = d[4 + nr + slots:]
+        dec_info = d[4:]
+        tile_info = d[4 + plan_decode_ints(nr):]
         st = self._stream()
         if plan.decode_cap:
             max_ctx = g.max_pages * g.page_size
@@ -413,7 +477,7 @@ class CudaOps:
             self.launches += 1
             _check(self.lib.hs_attention_decode(
                 _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req),
-                _ptr(tok_list), _ptr(head), plan.decode_cap, g.n_heads, g.n_kv_heads, g.head_dim,
+                _ptr(dec_info), _ptr(head), plan.decode_cap, g.n_heads, g.n_kv_heads, g.head_dim,
                 g.page_size, g.num_pages, g.max_pages, g.q_off, g.qkv_stride, g.window, scale,
                 splits, _ptr(acc), _ptr(ml), _ptr(cnt), _ptr(status), st),
                 f"attention_decode(head_dim={g.head_dim})")
@@ -421,7 +485,7 @@ class CudaOps:
             self.launches += 1
             _check(self.lib.hs_attention_prefill(
                 _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req),
-                _ptr(tile_tok), _ptr(tile_n), _ptr(head), plan.tile_cap, g.n_heads, g.n_kv_heads,
+                _ptr(tile_info), _ptr(head), plan.tile_cap, g.n_heads, g.n_kv_heads,
                 g.head_dim, g.page_size, g.num_pages, g.max_pages, g.q_off, g.qkv_stride, scale,
                 _ptr(status), st), f"attention_prefill(head_dim={g.head_dim})")
 

@@ -66,6 +66,12 @@ class Part:
 
 
 class Mixer(Part):
+    # A part that sets ``takes_norm`` is handed the norm that precedes it (``norm=``) and an
+    # ``h`` that is NOT yet normalised; it must form its input projection with
+    # ``norm.linear(ctx, out, h, x, w, bias, act)``.  Parts that leave it False receive a
+    # normalised ``h``.
+    takes_norm = False
+
     def cache_request(self) -> CacheRequest | None:
         return None
 
@@ -78,6 +84,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_norm = False
+
     def forward(self, ctx, h, x) -> None:
         raise NotImplementedError
 
@@ -85,6 +93,13 @@ class FeedForward(Part):
 class Norm(Part):
     def forward(self, ctx, out, x, rows=None) -> None:
         raise NotImplementedError
+
+    def linear(self, ctx, out, h, x, w, bias=None, act="none") -> None:
+        """``out = act(norm(x) @ w.T + bias)``: the input projection of the part that follows
+        this norm.  The default normalises into ``h`` and projects; a norm whose kernel can be
+        fused into the projection overrides it."""
+        self.forward(ctx, h, x)
+        ctx.ops.linear(out, h, w, bias, act=act)
 
 
 class PositionEncoding(Part):

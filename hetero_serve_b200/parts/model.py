@@ -38,10 +38,16 @@ class PreNormBlock(Block):
 
     def forward(self, ctx, x, cache):
         h = ctx.buffer("normed", (x.shape[0], x.shape[1]), ctx.dtype)
-        self.norm1.forward(ctx, h, x)
-        self.mixer.forward(ctx, h, x, cache)
-        self.norm2.forward(ctx, h, x)
-        self.feed_forward.forward(ctx, h, x)
+        if self.mixer.takes_norm:           # the mixer forms norm + input projection itself
+            self.mixer.forward(ctx, h, x, cache, norm=self.norm1)
+        else:
+            self.norm1.forward(ctx, h, x)
+            self.mixer.forward(ctx, h, x, cache)
+        if self.feed_forward.takes_norm:
+            self.feed_forward.forward(ctx, h, x, norm=self.norm2)
+        else:
+            self.norm2.forward(ctx, h, x)
+            self.feed_forward.forward(ctx, h, x)
 
 
 _ARRANGEMENTS: dict[str, Callable[[LayerSpec], Block]] = {"pre_norm": PreNormBlock}

@@ -77,6 +77,9 @@ class LayerNorm(Norm):
     def forward(self, ctx, out, x, rows=None):
         ctx.ops.layernorm(out, x, self.weight, self.bias, self.eps, rows)
 
+    def linear(self, ctx, out, h, x, w, bias=None, act="none"):
+        ctx.ops.norm_linear(out, h, x, self.weight, self.bias, self.eps, w, bias, act)
+
 
 class CausalAttention(Mixer):
     """Multi-head (or grouped-query) causal attention over the paged cache.
@@ -136,10 +139,15 @@ class CausalAttention(Mixer):
             k_off=self.H * self.D, v_off=(self.H + self.HK) * self.D, qkv_stride=self.qkv_width,
             window=self.window)
 
-    def forward(self, ctx, h, x, cache):
+    takes_norm = True
+
+    def forward(self, ctx, h, x, cache, norm=None):
         T = h.shape[0]
         qkv = ctx.buffer("qkv", (T, self.qkv_width), ctx.dtype)
-        ctx.ops.linear(qkv, h, self.w_qkv, self.b_qkv)
+        if norm is not None:
+            norm.linear(ctx, qkv, h, x, self.w_qkv, self.b_qkv)
+        else:
+            ctx.ops.linear(qkv, h, self.w_qkv, self.b_qkv)
         g = self.geometry(cache)
         if cache.writes:
             ctx.ops.kv_append(cache.pool, qkv, cache.table, ctx.tok_pos, ctx.tok_req, g, ctx.status)
@@ -183,10 +191,15 @@ class DenseFeedForward(FeedForward):
         self.b_in = tensors[ib] if ib else None
         self.b_out = tensors[ob] if ob else None
 
-    def forward(self, ctx, h, x):
+    takes_norm = True
+
+    def forward(self, ctx, h, x, norm=None):
         T = h.shape[0]
         u = ctx.buffer("ff_inner", (T, self.inner), ctx.dtype)
-        ctx.ops.linear(u, h, self.w_in, self.b_in, act=self.act)
+        if norm is not None:
+            norm.linear(ctx, u, h, x, self.w_in, self.b_in, act=self.act)
+        else:
+            ctx.ops.linear(u, h, self.w_in, self.b_in, act=self.act)
         ctx.ops.linear(x, u, self.w_out, self.b_out, residual=x)
 
 

@@ -57,6 +57,10 @@ class PlainOps:
             v = v + residual.to(self.cd)
         out.copy_(v.to(out.dtype))
 
+    def norm_linear(self, out, h, x, gamma, beta, eps, w, bias=None, act="none"):
+        self.layernorm(h, x, gamma, beta, eps)
+        self.linear(out, h, w, bias, act=act)
+
     @staticmethod
     def _pool_view(pool, g):
         return pool.view(g.num_pages, 2, g.n_kv_heads, g.page_size, g.head_dim)
