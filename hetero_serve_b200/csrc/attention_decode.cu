@@ -20,6 +20,9 @@
 // Scratch layout (float32 unless noted), T = token capacity, H = heads, S = splits:
 //     acc  [T][H][S][D]      ml [T][H][S][2]      counters [T][H] (int32, zero between launches)
 #include "common.cuh"
+#include "no_alloc.h"
+
+#include <mutex>
 
 namespace hs {
 
@@ -307,4 +310,80 @@ HS_EXPORT int hs_attention_decode(void* out, const void* qkv, const void* pool, 
   }
   HS_LAUNCH_CHECK();
   return HS_OK;
+}
+
+
+// ------------------------------------------------------------------------------------------
+// The same kernel for callers that must not allocate (declared in no_alloc.h).
+//
+// The partial sums, their (max, sum) pairs and the arrival counters live in one file-scope
+// device array instead of caller-provided scratch.  Host code cannot use the array's name as
+// an address (on the host it is only a stand-in for the symbol), so the device address is
+// looked up with cudaGetSymbolAddress once per device, with that device current, and kept.
+namespace hs {
+
+static __device__ __align__(256) float noalloc_scratch[HS_NOALLOC_SCRATCH_FLOATS];
+
+static std::mutex noalloc_mutex;
+static float* noalloc_address[HS_NOALLOC_MAX_DEVICES];     // per device, null until looked up
+
+// Device address of the static scratch on the current device (first call per device does the
+// look-up; it is not a stream operation and should not happen inside a stream capture).
+static int noalloc_scratch_address(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= HS_NOALLOC_MAX_DEVICES) return HS_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(noalloc_mutex);
+  if (noalloc_address[dev] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (ptr == nullptr) return HS_ERR_ARGUMENT;
+    noalloc_address[dev] = ptr;
+  }
+  *out = noalloc_address[dev];
+  return HS_OK;
+}
+
+}  // namespace hs
+
+HS_EXPORT long long hs_attention_decode_noalloc_capacity(void) {
+  return (long long)HS_NOALLOC_SCRATCH_FLOATS;
+}
+
+HS_EXPORT int hs_attention_decode_noalloc(void* out, const void* qkv, const void* pool,
+                                          const int* table, const int* tok_pos,
+                                          const int* tok_req, const int* dec_info,
+                                          const int* plan_head, int token_cap, int n_heads,
+                                          int n_kv_heads, int head_dim, int page_size,
+                                          int num_pages, int max_pages, int q_off, int qkv_stride,
+                                          int window, float scale, int splits, int* status,
+                                          void* stream) {
+  using namespace hs;
+  if (token_cap <= 0) return HS_OK;
+  if (splits < 1 || n_heads <= 0 || head_dim <= 0) return HS_ERR_ARGUMENT;
+  if (splits == 1)      // one slice per (token, head): the kernel touches no scratch at all
+    return hs_attention_decode(out, qkv, pool, table, tok_pos, tok_req, dec_info, plan_head,
+                               token_cap, n_heads, n_kv_heads, head_dim, page_size, num_pages,
+                               max_pages, q_off, qkv_stride, window, scale, 1, nullptr, nullptr,
+                               nullptr, status, stream);
+  // layout inside the static array: acc [rows][D] | ml [rows][2] | counters [token_cap * heads]
+  const long long rows = (long long)token_cap * n_heads * splits;
+  const long long pairs = (long long)token_cap * n_heads;
+  const long long need = rows * head_dim + rows * 2 + pairs;
+  if (need > (long long)HS_NOALLOC_SCRATCH_FLOATS) return HS_ERR_TOO_LARGE;
+  float* base = nullptr;
+  if (int e = noalloc_scratch_address(&base)) return e;
+  float* acc = base;
+  float* ml = acc + rows * head_dim;
+  int* counters = (int*)(ml + rows * 2);
+  // The array keeps whatever the last call (or an aborted one) left.  Only the counters must
+  // start at zero; partial sums are fully written before they are read.
+  cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)pairs * sizeof(int), (cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  return hs_attention_decode(out, qkv, pool, table, tok_pos, tok_req, dec_info, plan_head,
+                             token_cap, n_heads, n_kv_heads, head_dim, page_size, num_pages,
+                             max_pages, q_off, qkv_stride, window, scale, splits, acc, ml, counters,
+                             status, stream);
 }

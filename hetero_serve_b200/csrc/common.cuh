@@ -18,6 +18,7 @@
 #define HS_OK 0
 #define HS_ERR_UNSUPPORTED (-1)   // a size or option this kernel does not take
 #define HS_ERR_ARGUMENT (-2)      // null pointer / inconsistent arguments
+#define HS_ERR_TOO_LARGE (-3)     // beyond a fixed capacity of the entry point
 
 #define HS_STATUS_BAD_TOKEN 1
 #define HS_STATUS_BAD_POSITION 2
