@@ -317,6 +317,52 @@ def run_ours(args):
     return 0
 
 
+def run_one_step(args):
+    """For profilers: build the model, warm up, then run ONE step (eager, no CUDA graph)
+    between cudaProfilerStart and cudaProfilerStop, so that
+    `ncu --profile-from-start off ... python bench.py --one-step decode` captures just it."""
+    import torch
+    from hetero_serve_b200.engine import Runner, StepEntry, load_model
+    from hetero_serve_b200.weights import write_model_dir
+    cfg, _ = model_config(args)
+    vocab = cfg["vocab_size"]
+    with tempfile.TemporaryDirectory(prefix="hsb200-bench-") as d:
+        write_model_dir(d, cfg, seed=0, dtype="bfloat16")
+        model, _ = load_model(d, "bfloat16", "cuda:0")
+        runner = Runner(model, num_pages=args.batch * 64 + 136, page_size=16, max_requests=64,
+                        dtype=torch.bfloat16, device="cuda:0", cuda_graphs=False)
+        g = torch.Generator().manual_seed(0)
+        if args.one_step == "decode":
+            ids = [f"r{i}" for i in range(args.batch)]
+            for r in ids:
+                runner.step([StepEntry(r, torch.randint(0, vocab, (args.prompt_len,), generator=g).tolist())])
+            entries = [StepEntry(r, [5], want=[0]) for r in ids]
+            for _ in range(3):
+                runner.step(entries, sample=True)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            runner.step(entries, sample=True)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        else:
+            prompts = torch.randint(0, vocab, (2, 1024), generator=g).tolist()
+            for it in range(3):
+                entries = [StepEntry(f"w{it}_{i}", p, want=[1023]) for i, p in enumerate(prompts)]
+                runner.step(entries, sample=True)
+                for e in entries:
+                    runner.close(e.req_id)
+            entries = [StepEntry(f"p{i}", p, want=[1023]) for i, p in enumerate(prompts)]
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            runner.step(entries, sample=True)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        runner.check_status()
+    print(json.dumps({"one_step": args.one_step, "n_layer": cfg["n_layer"], "batch": args.batch,
+                      "kernel_launches_total": runner.kernel_launches}))
+    return 0
+
+
 def run_reference(args):
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "heteroserve")):
@@ -341,6 +387,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0,
                     help="fewer layers than the configuration has (0: all); both numbers "
                          "are named in `config`")
+    ap.add_argument("--one-step", dest="one_step", default="", choices=["", "decode", "prefill"],
+                    help="for profilers: run a single eager step between cudaProfilerStart/Stop")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -349,6 +397,8 @@ def main() -> int:
         args.warmup = 3
     if args.impl == "reference":
         return run_reference(args)
+    if args.one_step:
+        return run_one_step(args)
     return run_ours(args)
 
 
