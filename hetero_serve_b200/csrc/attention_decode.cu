@@ -26,7 +26,7 @@
 
 namespace hs {
 
-constexpr int AD_WARPS = 4;
+constexpr int AD_WARPS = 4;          // warps per CTA of the narrow variant (the wide one has 16)
 
 struct DecodeParams {
   const __nv_bfloat16* qkv;
@@ -43,6 +43,7 @@ struct DecodeParams {
   int* status;
   int n_heads, n_kv_heads, page_size, num_pages, max_pages;
   int q_off, qkv_stride, splits, window;
+  int k_off, v_off, fuse_append;   // fuse_append: take and store the token's own key/value
   float scale;
 };
 
@@ -55,8 +56,8 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
   }
 }
 
-template <int D>
-__global__ void __launch_bounds__(AD_WARPS * 32)
+template <int D, int NW>
+__global__ void __launch_bounds__(NW * 32)
 attention_decode_kernel(const DecodeParams p) {
   constexpr int LPK = D / 8;          // lanes per key row
   constexpr int KPW = 32 / LPK;       // keys per warp-wide load
@@ -81,7 +82,10 @@ attention_decode_kernel(const DecodeParams p) {
   int chunk = (max_ctx + p.splits - 1) / p.splits;
   chunk = (chunk + PS - 1) / PS * PS;
   const int k_begin = max(split * chunk, lo_all);
-  const int k_end = min((split + 1) * chunk, pos + 1);       // exclusive
+  // With the append fused in, the token's own key (position pos) is not in the pages yet: the
+  // slice that contains pos takes it from the projection's output row and writes it to its page.
+  const bool own_here = p.fuse_append && pos >= split * chunk && pos < (split + 1) * chunk;
+  const int k_end = min((split + 1) * chunk, p.fuse_append ? pos : pos + 1);   // exclusive
 
   // the query, 8 elements per lane (the same 8 its key lanes read)
   const int part = lane % LPK, sub = lane / LPK;
@@ -101,12 +105,12 @@ attention_decode_kernel(const DecodeParams p) {
 
   if (k_begin < k_end) {
     const int pg_first = k_begin / PS, pg_last = (k_end - 1) / PS;
-    // This warp's pages: pg_first + warp, + AD_WARPS, ...  Their page numbers are fetched at
+    // This warp's pages: pg_first + warp, + NW, ...  Their page numbers are fetched at
     // once, one per lane (the host keeps a slice within 32 pages per warp), so that no key
     // load waits for a table lookup.
-    const int my_pg = pg_first + warp + AD_WARPS * lane;
+    const int my_pg = pg_first + warp + NW * lane;
     const int my_page = my_pg <= pg_last ? trow[my_pg] : -1;
-    const int n_pages = (pg_last - pg_first - warp + AD_WARPS) / AD_WARPS;   // may be <= 0
+    const int n_pages = (pg_last - pg_first - warp + NW) / NW;   // may be <= 0
     constexpr int UNIT = 4 * KPW;                        // keys per unit of work
     const int upp = (PS + UNIT - 1) / UNIT;              // units per page
     const int n_units = n_pages > 0 ? n_pages * upp : 0;
@@ -119,7 +123,7 @@ attention_decode_kernel(const DecodeParams p) {
     auto load_unit = [&](int u, Unit& un) {
       const int it = u / upp;
       un.g0 = (u - it * upp) * UNIT;
-      const int pg = pg_first + warp + AD_WARPS * it;
+      const int pg = pg_first + warp + NW * it;
       const int page = __shfl_sync(0xffffffffu, my_page, it & 31);
       un.j0 = pg * PS;
       const bool page_ok = page >= 0 && page < p.num_pages;
@@ -185,6 +189,43 @@ attention_decode_kernel(const DecodeParams p) {
       cur = nxt;
     }
   }
+  if (own_here && warp == NW - 1) {
+    // the new key and value: lanes of key group 0 hold 8 elements each
+    const __nv_bfloat16* row = p.qkv + (size_t)t * p.qkv_stride;
+    uint4 ku = make_uint4(0, 0, 0, 0), vu = make_uint4(0, 0, 0, 0);
+    if (sub == 0) {
+      ku = *(const uint4*)(row + p.k_off + (size_t)hk * D + part * 8);
+      vu = *(const uint4*)(row + p.v_off + (size_t)hk * D + part * 8);
+      if (h % (p.n_heads / p.n_kv_heads) == 0) {          // one writer per key/value head
+        const int page = trow[pos / PS];
+        if (page < 0 || page >= p.num_pages) {
+          if (part == 0) atomicOr(p.status, HS_STATUS_BAD_PAGE);
+        } else {
+          __nv_bfloat16* kdst = const_cast<__nv_bfloat16*>(p.pool) + (size_t)page * page_stride +
+                                (size_t)hk * tile + (size_t)(pos % PS) * D + part * 8;
+          *(uint4*)kdst = ku;
+          *(uint4*)(kdst + (size_t)p.n_kv_heads * tile) = vu;
+        }
+      }
+    }
+    float kf[8];
+    unpack8(ku, kf);
+    float dot = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dot = fmaf(q[e], kf[e], dot);
+#pragma unroll
+    for (int o = 1; o < LPK; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float sc = __shfl_sync(0xffffffffu, dot, 0) * p.scale;      // group 0's score, to all
+    const float m_new = fmaxf(m, sc);
+    const float corr = __expf(m - m_new);
+    const float pr = (sub == 0) ? __expf(sc - m_new) : 0.f;
+    l = l * corr + pr;
+    float vf[8];
+    unpack8(vu, vf);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = fmaf(pr, vf[e], acc[e] * corr);
+    m = m_new;
+  }
   // ---- combine the key groups of a warp, then the warps of the CTA (all share m per warp)
   // every lane of a warp holds the same m; l and acc are per key group: sum over groups
 #pragma unroll
@@ -194,7 +235,7 @@ attention_decode_kernel(const DecodeParams p) {
     for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
   }
   // l was added once per lane of a key group: every lane of a group holds the same l, fine
-  __shared__ float s_m[AD_WARPS], s_l[AD_WARPS], s_acc[AD_WARPS][D];
+  __shared__ float s_m[NW], s_l[NW], s_acc[NW][D];
   if (sub == 0) {
 #pragma unroll
     for (int e = 0; e < 8; ++e) s_acc[warp][part * 8 + e] = acc[e];
@@ -208,18 +249,18 @@ attention_decode_kernel(const DecodeParams p) {
   float* pacc = p.acc + pidx * D;
   float cm = -INFINITY;
 #pragma unroll
-  for (int w = 0; w < AD_WARPS; ++w) cm = fmaxf(cm, s_m[w]);
+  for (int w = 0; w < NW; ++w) cm = fmaxf(cm, s_m[w]);
   float cl = 0.f;
-  float wscale[AD_WARPS];
+  float wscale[NW];
 #pragma unroll
-  for (int w = 0; w < AD_WARPS; ++w) {
+  for (int w = 0; w < NW; ++w) {
     wscale[w] = (s_m[w] == -INFINITY) ? 0.f : __expf(s_m[w] - cm);
     cl += s_l[w] * wscale[w];
   }
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float a = 0.f;
 #pragma unroll
-    for (int w = 0; w < AD_WARPS; ++w) a += s_acc[w][d] * wscale[w];
+    for (int w = 0; w < NW; ++w) a += s_acc[w][d] * wscale[w];
     if (p.splits == 1) {
       orow[d] = __float2bfloat16_rn(cl > 0.f ? a / cl : 0.f);
     } else {
@@ -263,6 +304,62 @@ attention_decode_kernel(const DecodeParams p) {
 
 }  // namespace hs
 
+// fuse_append != 0: every served token is the only new token of its request; its key and value
+// (columns k_off / v_off of its row in `qkv`) are used from there and written to its page by the
+// kernel, so no separate append pass is needed.  wide != 0: 16 warps per CTA instead of 4 (for
+// batches whose token x head count alone does not fill the GPU).
+HS_EXPORT int hs_attention_decode_append(void* out, const void* qkv, void* pool, const int* table,
+                                         const int* tok_pos, const int* tok_req,
+                                         const int* dec_info, const int* plan_head, int token_cap,
+                                         int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                         int num_pages, int max_pages, int q_off, int k_off,
+                                         int v_off, int qkv_stride, int window, float scale,
+                                         int splits, int fuse_append, int wide, float* scratch_acc,
+                                         float* scratch_ml, int* counters, int* status,
+                                         void* stream) {
+  using namespace hs;
+  if (!out || !qkv || !pool || !table || !tok_pos || !tok_req || !dec_info || !plan_head ||
+      !status)
+    return HS_ERR_ARGUMENT;
+  if (token_cap <= 0) return HS_OK;
+  if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return HS_ERR_UNSUPPORTED;
+  if (page_size <= 0 || page_size % 16 || splits < 1 || splits > 65535) return HS_ERR_UNSUPPORTED;
+  if (n_heads > 65535) return HS_ERR_UNSUPPORTED;
+  if (splits > 1 && (!scratch_acc || !scratch_ml || !counters)) return HS_ERR_ARGUMENT;
+  if ((qkv_stride % 8) || (q_off % 8) || (k_off % 8) || (v_off % 8))
+    return HS_ERR_UNSUPPORTED;   // 16-byte loads of the query, key and value rows
+  const int nw = wide ? 16 : AD_WARPS;
+  // a slice may span at most 32 pages per warp
+  if ((long long)splits * 32 * nw < max_pages) return HS_ERR_UNSUPPORTED;
+  DecodeParams p;
+  p.qkv = (const __nv_bfloat16*)qkv;
+  p.pool = (const __nv_bfloat16*)pool;
+  p.out = (__nv_bfloat16*)out;
+  p.table = table; p.tok_pos = tok_pos; p.tok_req = tok_req; p.dec_info = dec_info;
+  p.plan_head = plan_head; p.acc = scratch_acc; p.ml = scratch_ml; p.counters = counters;
+  p.status = status;
+  p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
+  p.num_pages = num_pages; p.max_pages = max_pages; p.q_off = q_off; p.qkv_stride = qkv_stride;
+  p.splits = splits; p.window = window; p.scale = scale;
+  p.k_off = k_off; p.v_off = v_off; p.fuse_append = fuse_append;
+  dim3 grid(token_cap, n_heads, splits);
+  cudaStream_t st = (cudaStream_t)stream;
+#define HS_AD(DD)                                                                       \
+  if (wide) attention_decode_kernel<DD, 16><<<grid, 16 * 32, 0, st>>>(p);               \
+  else attention_decode_kernel<DD, AD_WARPS><<<grid, AD_WARPS * 32, 0, st>>>(p)
+  switch (head_dim) {
+    case 16: HS_AD(16); break;
+    case 32: HS_AD(32); break;
+    case 64: HS_AD(64); break;
+    case 128: HS_AD(128); break;
+    case 256: HS_AD(256); break;
+    default: return HS_ERR_UNSUPPORTED;
+  }
+#undef HS_AD
+  HS_LAUNCH_CHECK();
+  return HS_OK;
+}
+
 // Bytes of scratch one launch needs (acc + ml + counters), for a token capacity.
 HS_EXPORT long long hs_attention_decode_scratch_floats(int token_cap, int n_heads, int head_dim,
                                                        int splits) {
@@ -276,42 +373,12 @@ HS_EXPORT int hs_attention_decode(void* out, const void* qkv, const void* pool, 
                                   int max_pages, int q_off, int qkv_stride, int window,
                                   float scale, int splits, float* scratch_acc, float* scratch_ml,
                                   int* counters, int* status, void* stream) {
-  using namespace hs;
-  if (!out || !qkv || !pool || !table || !tok_pos || !tok_req || !dec_info || !plan_head ||
-      !status)
-    return HS_ERR_ARGUMENT;
-  if (token_cap <= 0) return HS_OK;
-  if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return HS_ERR_UNSUPPORTED;
-  if (page_size <= 0 || page_size % 16 || splits < 1 || splits > 65535) return HS_ERR_UNSUPPORTED;
-  if (n_heads > 65535) return HS_ERR_UNSUPPORTED;
-  if (splits > 1 && (!scratch_acc || !scratch_ml || !counters)) return HS_ERR_ARGUMENT;
-  if ((qkv_stride % 8) || (q_off % 8)) return HS_ERR_UNSUPPORTED;   // 16-byte query loads
-  // a slice may span at most 32 pages per warp
-  if ((long long)splits * 32 * hs::AD_WARPS < max_pages) return HS_ERR_UNSUPPORTED;
-  DecodeParams p;
-  p.qkv = (const __nv_bfloat16*)qkv;
-  p.pool = (const __nv_bfloat16*)pool;
-  p.out = (__nv_bfloat16*)out;
-  p.table = table; p.tok_pos = tok_pos; p.tok_req = tok_req; p.dec_info = dec_info;
-  p.plan_head = plan_head; p.acc = scratch_acc; p.ml = scratch_ml; p.counters = counters;
-  p.status = status;
-  p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
-  p.num_pages = num_pages; p.max_pages = max_pages; p.q_off = q_off; p.qkv_stride = qkv_stride;
-  p.splits = splits; p.window = window; p.scale = scale;
-  dim3 grid(token_cap, n_heads, splits);
-  cudaStream_t st = (cudaStream_t)stream;
-  switch (head_dim) {
-    case 16: attention_decode_kernel<16><<<grid, AD_WARPS * 32, 0, st>>>(p); break;
-    case 32: attention_decode_kernel<32><<<grid, AD_WARPS * 32, 0, st>>>(p); break;
-    case 64: attention_decode_kernel<64><<<grid, AD_WARPS * 32, 0, st>>>(p); break;
-    case 128: attention_decode_kernel<128><<<grid, AD_WARPS * 32, 0, st>>>(p); break;
-    case 256: attention_decode_kernel<256><<<grid, AD_WARPS * 32, 0, st>>>(p); break;
-    default: return HS_ERR_UNSUPPORTED;
-  }
-  HS_LAUNCH_CHECK();
-  return HS_OK;
+  return hs_attention_decode_append(out, qkv, const_cast<void*>(pool), table, tok_pos, tok_req, dec_info, plan_head,
+                                    token_cap, n_heads, n_kv_heads, head_dim, page_size,
+                                    num_pages, max_pages, q_off, 0, 0, qkv_stride, window, scale,
+                                    splits, 0, 0, scratch_acc, scratch_ml, counters, status,
+                                    stream);
 }
-
 
 // ------------------------------------------------------------------------------------------
 // The same kernel for callers that must not allocate (declared in no_alloc.h).

@@ -64,6 +64,7 @@ class AttentionPlan:
     n_rows: int
     decode_cap: int
     tile_cap: int
+    single_new: bool = False     # every single-query token is the only new token of its request
 
     @property
     def tile_slots(self) -> int:
@@ -122,8 +123,8 @@ def _declare(lib) -> None:
         "hs_linear_skinny_scratch": [I, I, I, P, P],
         "hs_kv_append": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "hs_attention_simt": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
-        "hs_attention_decode": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P,
-                                P, P, P],
+        "hs_attention_decode_append": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I,
+                                       F, I, I, I, P, P, P, P, P],
         "hs_attention_prefill": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
         "hs_argmax": [P, P, I, I, P],
         "hs_sample": [P, P, P, P, P, P, P, I, I, P],
@@ -179,6 +180,7 @@ class CudaOps:
         self.fast_attention = True  # bfloat16 attention on the split-context / tensor-core kernels
         self.sm_count = torch.cuda.get_device_properties(0).multi_processor_count
         self.fuse_norm = True      # LayerNorm fused into the few-row linear kernel
+        self.fuse_append = True    # key/value append fused into the decode attention
         self._skinny_need: dict = {}
         self._scratch: dict = {}
         self._retired: list = []
@@ -370,7 +372,8 @@ class CudaOps:
                                      self._stream()),
                f"kv_append(head_dim={g.head_dim})")
 
-    def attention(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan=None):
+    def attention(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan=None,
+                  _fuse_append=False):
         """out[t] = causal attention of token t's query over its request's pages.
 
         ``plan`` may carry a batch's work lists for the specialised kernels; the general
@@ -380,7 +383,8 @@ class CudaOps:
         if out.shape[1] != g.n_heads * g.head_dim:
             raise KernelError("attention: out width != n_heads * head_dim")
         self._attn_common(qkv, pool, table, tok_pos, tok_req, g, n)
-        self._attention(out, qkv, pool, table, tok_pos, tok_req, g, float(scale), status, plan, n)
+        self._attention(out, qkv, pool, table, tok_pos, tok_req, g, float(scale), status, plan, n,
+                        _fuse_append)
 
     # -- attention work lists ---------------------------------------------------------
     @staticmethod
@@ -392,14 +396,16 @@ class CudaOps:
                        bucketed: bool) -> tuple[int, int]:
         """Fill the plan section (a numpy int32 view of the step's metadata) for a batch given
         as ``[(request, slot, start, n_new)]`` in flat order; returns ``(decode_cap,
-        tile_cap)``.  Requests bringing up to DECODE_MAX_NEW tokens go to the single-query
+        tile_cap, single_new)``.  Requests bringing up to DECODE_MAX_NEW tokens go to the single-query
         list, the others are cut into tiles of 64 queries."""
         dec = view[4:4 + 3 * n_rows]
         tiles = view[4 + plan_decode_ints(n_rows):]
         n_dec = n_tiles = max_ctx = 0
         t = 0
+        single = True
         for row, (_req, _slot, start, n) in enumerate(host_batch):
             if n <= DECODE_MAX_NEW:
+                single = single and n == 1
                 for i in range(n):
                     dec[3 * n_dec:3 * n_dec + 3] = (t + i, row, start + i)
                     n_dec += 1
@@ -411,18 +417,19 @@ class CudaOps:
                     n_tiles += 1
             t += n
         view[0], view[1], view[2], view[3] = n_dec, n_tiles, max_ctx, 0
+        single = single and n_dec > 0
         if bucketed:
-            return (_pow2(n_dec) if n_dec else 0, _pow2(n_tiles) if n_tiles else 0)
-        return n_dec, n_tiles
+            return (_pow2(n_dec) if n_dec else 0, _pow2(n_tiles) if n_tiles else 0, single)
+        return n_dec, n_tiles, single
 
     def make_plan(self, host_batch, n_rows: int, page_size: int) -> AttentionPlan:
         """A plan built and uploaded on the spot (the runner packs it into the step's single
         upload instead)."""
         import numpy as np
         view = np.zeros(self.attention_plan_ints(n_rows, len(host_batch)), dtype=np.int32)
-        dec, tiles = self.plan_attention(view, host_batch, n_rows, len(host_batch), page_size,
-                                         False)
-        return AttentionPlan(torch.from_numpy(view).to("cuda"), n_rows, dec, tiles)
+        dec, tiles, single = self.plan_attention(view, host_batch, n_rows, len(host_batch),
+                                                 page_size, False)
+        return AttentionPlan(torch.from_numpy(view).to("cuda"), n_rows, dec, tiles, single)
 
     def _scratch_buffer(self, name, numel, dtype):
         key = (name, dtype)
@@ -434,21 +441,46 @@ class CudaOps:
             self._scratch[key] = buf
         return buf
 
+    def decode_wide(self, decode_cap: int, n_heads: int) -> bool:
+        """16 warps per CTA (instead of 4) while token x head count alone leaves SMs idle."""
+        return decode_cap * n_heads <= 2 * self.sm_count
+
     def decode_splits(self, decode_cap: int, n_heads: int, max_context: int) -> int:
-        """Slices the context of a single-query token is cut into: enough CTAs to fill the
-        GPU four times, slices of at least 64 keys (in the manner of the reference's
-        ``choose_num_splits``, heteroserve/model/paged_attn_v3.py:212-232)."""
-        want = -(-4 * self.sm_count // max(1, decode_cap * n_heads))
-        need = -(-max_context // (128 * 16))     # a slice spans at most 32 pages per warp
+        """Slices between CTAs the context of a single-query token is cut into: one wave of
+        CTAs over the SMs, slices of at least 64 keys (in the manner of the reference's
+        ``choose_num_splits``, heteroserve/model/paged_attn_v3.py:212-232).  Slices cost a
+        round trip through scratch memory, so they are used only when token x head count is
+        small."""
+        pairs = max(1, decode_cap * n_heads)
+        wide = self.decode_wide(decode_cap, n_heads)
+        want = max(1, round(self.sm_count / pairs)) if wide else 1
+        per_warp = 32 * 16 * (16 if wide else 4)     # keys a CTA can cover: 32 pages per warp
+        need = -(-max_context // per_warp)
         return max(1, need, min(want, max(1, max_context // 64), 32))
 
     FAST_HEAD_DIMS = (16, 32, 64, 128)
 
-    def _attention(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan, n):
-        if (plan is not None and self.fast_attention and qkv.dtype == torch.bfloat16
-                and g.window == 0 and g.head_dim in self.FAST_HEAD_DIMS
-                and plan.n_rows >= n):
-            self._attention_fast(out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan)
+    def _fast_ok(self, qkv, g, plan, n) -> bool:
+        return (plan is not None and self.fast_attention and qkv.dtype == torch.bfloat16
+                and g.window == 0 and g.head_dim in self.FAST_HEAD_DIMS and plan.n_rows >= n)
+
+    def attention_append(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status,
+                         plan=None, writes=True):
+        """Append the new keys/values to the pages (if ``writes``), then attention.  When the
+        step is made of single decoded tokens only, the decode kernel does both in one launch."""
+        n = out.shape[0]
+        fuse = (writes and self.fuse_append and self._fast_ok(qkv, g, plan, n)
+                and plan.tile_cap == 0 and plan.decode_cap > 0 and plan.single_new)
+        if writes and not fuse:
+            self.kv_append(pool, qkv, table, tok_pos, tok_req, g, status)
+        self.attention(out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan,
+                       _fuse_append=fuse)
+
+    def _attention(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan, n,
+                   fuse=False):
+        if self._fast_ok(qkv, g, plan, n):
+            self._attention_fast(out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan,
+                                 fuse)
             return
         self.launches += 1
         _check(self.lib.hs_attention_simt(
@@ -457,7 +489,8 @@ class CudaOps:
             g.k_off, g.v_off, g.qkv_stride, g.window, scale, _DT[qkv.dtype], _ptr(status),
             self._stream()), f"attention(head_dim={g.head_dim}, heads={g.n_heads})")
 
-    def _attention_fast(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan):
+    def _attention_fast(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan,
+                        fuse=False):
         d = plan.data
         nr = plan.n_rows
         head = d
@@ -475,12 +508,13 @@ class CudaOps:
                 cnt = self._scratch_buffer("decode_counters", plan.decode_cap * g.n_heads,
                                            torch.int32)
             self.launches += 1
-            _check(self.lib.hs_attention_decode(
+            _check(self.lib.hs_attention_decode_append(
                 _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req),
                 _ptr(dec_info), _ptr(head), plan.decode_cap, g.n_heads, g.n_kv_heads, g.head_dim,
-                g.page_size, g.num_pages, g.max_pages, g.q_off, g.qkv_stride, g.window, scale,
-                splits, _ptr(acc), _ptr(ml), _ptr(cnt), _ptr(status), st),
-                f"attention_decode(head_dim={g.head_dim})")
+                g.page_size, g.num_pages, g.max_pages, g.q_off, g.k_off, g.v_off, g.qkv_stride,
+                g.window, scale, splits, int(bool(fuse)),
+                int(self.decode_wide(plan.decode_cap, g.n_heads)), _ptr(acc), _ptr(ml), _ptr(cnt),
+                _ptr(status), st), f"attention_decode(head_dim={g.head_dim})")
         if plan.tile_cap:
             self.launches += 1
             _check(self.lib.hs_attention_prefill(

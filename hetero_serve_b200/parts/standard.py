@@ -149,11 +149,9 @@ class CausalAttention(Mixer):
         else:
             ctx.ops.linear(qkv, h, self.w_qkv, self.b_qkv)
         g = self.geometry(cache)
-        if cache.writes:
-            ctx.ops.kv_append(cache.pool, qkv, cache.table, ctx.tok_pos, ctx.tok_req, g, ctx.status)
         att = ctx.buffer("attn_out", (T, self.H * self.D), ctx.dtype)
-        ctx.ops.attention(att, qkv, cache.pool, cache.table, ctx.tok_pos, ctx.tok_req, g,
-                          self.scale, ctx.status, ctx.plan)
+        ctx.ops.attention_append(att, qkv, cache.pool, cache.table, ctx.tok_pos, ctx.tok_req, g,
+                                 self.scale, ctx.status, ctx.plan, cache.writes)
         ctx.ops.linear(x, att, self.w_out, self.b_out, residual=x)
 
 

@@ -103,6 +103,12 @@ class PlainOps:
                 pr = torch.softmax(s, 0)
                 out[t, h * D:(h + 1) * D] = (pr @ v[:, hk, :]).to(out.dtype)
 
+    def attention_append(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status,
+                         plan=None, writes=True):
+        if writes:
+            self.kv_append(pool, qkv, table, tok_pos, tok_req, g, status)
+        self.attention(out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan)
+
     def argmax(self, out, logits):
         rows = logits.shape[0]
         out[:rows] = torch.argmax(logits, dim=-1).to(torch.int32)

@@ -256,6 +256,43 @@ def test_specialised_attention_kernels(ops, plain, case):
     assert (out.float() - gen.float()).abs().max() < 2e-2
 
 
+DECODE_ONLY = [
+    # H, HK, D, PS, lens: every request brings one token -> append fused into the decode kernel
+    (16, 16, 64, 16, [1024, 700, 64, 65, 1, 16, 17, 513]),       # wide CTAs, one slice
+    (4, 2, 32, 16, [300]),                                         # few pairs: several slices
+    (8, 8, 128, 32, [90] * 40),                                    # many pairs: narrow CTAs
+    (2, 1, 16, 16, [33, 2]),
+]
+
+
+@pytest.mark.parametrize("case", DECODE_ONLY, ids=[f"H{c[0]}D{c[2]}n{len(c[4])}" for c in DECODE_ONLY])
+def test_decode_attention_with_the_append_fused_in(ops, plain, case):
+    H, HK, D, PS, lens = case
+    new = [1] * len(lens)
+    geom, qkv, pool, table, tok_pos, tok_req = _attention_case(H, HK, D, PS, lens, new, 0,
+                                                               torch.bfloat16, seed=7 * D + H)
+    st = _status()
+    T = qkv.shape[0]
+    plan = ops.make_plan(_host_batch(lens, new), T, PS)
+    assert plan.single_new and plan.tile_cap == 0
+    pool_ref = pool.clone()
+    out = torch.full((T, H * D), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ref = torch.empty(T, H * D, device=DEV, dtype=torch.float64)
+    before = ops.launches
+    ops.attention_append(out, qkv, pool, table, tok_pos, tok_req, geom, 0.11, st, plan, True)
+    assert ops.launches - before == 1                      # one kernel does both
+    plain.attention_append(ref, qkv, pool_ref, table, tok_pos, tok_req, geom, 0.11, st, None, True)
+    assert st.item() == 0
+    # the pages hold the new keys and values, bit for bit
+    assert torch.equal(torch.nan_to_num(pool, nan=9.0), torch.nan_to_num(pool_ref, nan=9.0))
+    assert torch.isfinite(out).all()
+    assert (out.double() - ref).abs().max() < 2e-2
+    # a reader of somebody else's cache entry does not write
+    pool2 = pool_ref.clone()
+    ops.attention_append(out, qkv, pool2, table, tok_pos, tok_req, geom, 0.11, st, plan, False)
+    assert torch.equal(torch.nan_to_num(pool2, nan=9.0), torch.nan_to_num(pool_ref, nan=9.0))
+
+
 @pytest.mark.parametrize("far", [0, 63, 64, 500, 1000])
 @pytest.mark.parametrize("new", [1, 100])
 def test_far_key_with_the_specialised_kernels(ops, far, new):
