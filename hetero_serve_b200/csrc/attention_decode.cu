@@ -87,8 +87,11 @@ attention_decode_kernel(const DecodeParams p) {
   const bool own_here = p.fuse_append && pos >= split * chunk && pos < (split + 1) * chunk;
   const int k_end = min((split + 1) * chunk, p.fuse_append ? pos : pos + 1);   // exclusive
 
-  // the query, 8 elements per lane (the same 8 its key lanes read)
+  // the query, 8 elements per lane (the same 8 its key lanes read).  Everything above came
+  // from the host's work lists; the query is the first thing the previous kernel wrote.
   const int part = lane % LPK, sub = lane / LPK;
+  pdl_trigger();
+  pdl_wait();
   float q[8];
   {
     const uint4 qu = *(const uint4*)(p.qkv + (size_t)t * p.qkv_stride + p.q_off + (size_t)h * D +
@@ -314,9 +317,9 @@ HS_EXPORT int hs_attention_decode_append(void* out, const void* qkv, void* pool,
                                          int n_heads, int n_kv_heads, int head_dim, int page_size,
                                          int num_pages, int max_pages, int q_off, int k_off,
                                          int v_off, int qkv_stride, int window, float scale,
-                                         int splits, int fuse_append, int wide, float* scratch_acc,
-                                         float* scratch_ml, int* counters, int* status,
-                                         void* stream) {
+                                         int splits, int fuse_append, int wide, int pdl,
+                                         float* scratch_acc, float* scratch_ml, int* counters,
+                                         int* status, void* stream) {
   using namespace hs;
   if (!out || !qkv || !pool || !table || !tok_pos || !tok_req || !dec_info || !plan_head ||
       !status)
@@ -344,9 +347,10 @@ HS_EXPORT int hs_attention_decode_append(void* out, const void* qkv, void* pool,
   p.k_off = k_off; p.v_off = v_off; p.fuse_append = fuse_append;
   dim3 grid(token_cap, n_heads, splits);
   cudaStream_t st = (cudaStream_t)stream;
-#define HS_AD(DD)                                                                       \
-  if (wide) attention_decode_kernel<DD, 16><<<grid, 16 * 32, 0, st>>>(p);               \
-  else attention_decode_kernel<DD, AD_WARPS><<<grid, AD_WARPS * 32, 0, st>>>(p)
+  cudaError_t le = cudaSuccess;
+#define HS_AD(DD)                                                                             \
+  if (wide) le = hs_launch(attention_decode_kernel<DD, 16>, grid, dim3(16 * 32), 0, st, pdl != 0, p); \
+  else le = hs_launch(attention_decode_kernel<DD, AD_WARPS>, grid, dim3(AD_WARPS * 32), 0, st, pdl != 0, p)
   switch (head_dim) {
     case 16: HS_AD(16); break;
     case 32: HS_AD(32); break;
@@ -356,6 +360,7 @@ HS_EXPORT int hs_attention_decode_append(void* out, const void* qkv, void* pool,
     default: return HS_ERR_UNSUPPORTED;
   }
 #undef HS_AD
+  if (le != cudaSuccess) return (int)le;
   HS_LAUNCH_CHECK();
   return HS_OK;
 }
@@ -376,7 +381,7 @@ HS_EXPORT int hs_attention_decode(void* out, const void* qkv, const void* pool, 
   return hs_attention_decode_append(out, qkv, const_cast<void*>(pool), table, tok_pos, tok_req, dec_info, plan_head,
                                     token_cap, n_heads, n_kv_heads, head_dim, page_size,
                                     num_pages, max_pages, q_off, 0, 0, qkv_stride, window, scale,
-                                    splits, 0, 0, scratch_acc, scratch_ml, counters, status,
+                                    splits, 0, 0, 0, scratch_acc, scratch_ml, counters, status,
                                     stream);
 }
 

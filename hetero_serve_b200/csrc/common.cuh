@@ -78,4 +78,31 @@ __device__ __forceinline__ float apply_act(float u, int act) {
   return u;
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization
+// attribute may start while its predecessor in the stream still runs.  `pdl_wait` blocks until
+// the predecessor has completed and its writes are visible (a no-op for a normal launch);
+// `pdl_trigger` lets the successor start.  What a kernel does before `pdl_wait` must not read
+// anything an earlier kernel of the step writes (weights, block tables and work lists are safe).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 }  // namespace hs
+
+// Launch with the programmatic-serialization attribute when `pdl` is set.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t hs_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}

@@ -12,6 +12,7 @@ __global__ void embed_kernel(float* __restrict__ x, const int* __restrict__ ids,
                              const int* __restrict__ pos, const int* __restrict__ req,
                              const T* __restrict__ wte, const T* __restrict__ wpe, int width,
                              int vocab, int n_pos, int* status) {
+  pdl_trigger();
   const int t = blockIdx.x;
   float* row = x + (size_t)t * width;
   const int r = req[t];
@@ -49,6 +50,7 @@ __global__ void layernorm_kernel(TO* __restrict__ out, const float* __restrict__
   extern __shared__ float srow[];
   __shared__ float red[THREADS / 32];
   __shared__ float bcast;
+  pdl_trigger();
   const int o = blockIdx.x;
   const int src = rows ? rows[o] : o;
   const float* xr = x + (size_t)src * width;

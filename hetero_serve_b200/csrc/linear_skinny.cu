@@ -100,6 +100,8 @@ linear_skinny_kernel(const SkinnyParams p) {
   // activations, so their latency overlaps the staging below
   WBatch cur;
   load_batch(kg, cur);
+  pdl_trigger();      // the next kernel may begin its own weight fetch
+  pdl_wait();         // from here on the activations of the previous kernel are read
 
   if (p.x) {        // LayerNorm statistics of every row, one warp per row
     for (int m = warp; m < MP; m += SK_WARPS) {
@@ -238,7 +240,8 @@ linear_skinny_kernel(const SkinnyParams p) {
 }
 
 template <int MT>
-static int launch_skinny(const SkinnyParams& p, int ksplit, size_t smem, cudaStream_t st) {
+static int launch_skinny(const SkinnyParams& p, int ksplit, size_t smem, cudaStream_t st,
+                         bool pdl) {
   auto kern = linear_skinny_kernel<MT>;
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
@@ -249,7 +252,8 @@ static int launch_skinny(const SkinnyParams& p, int ksplit, size_t smem, cudaStr
   }
   const int per_cta = SK_FEATS * p.ng;
   dim3 grid((p.N + per_cta - 1) / per_cta, ksplit);
-  kern<<<grid, SK_THREADS, smem, st>>>(p);
+  cudaError_t le = hs_launch(kern, grid, dim3(SK_THREADS), smem, st, pdl, p);
+  if (le != cudaSuccess) return (int)le;
   HS_LAUNCH_CHECK();
   return HS_OK;
 }
@@ -306,12 +310,14 @@ HS_EXPORT int hs_linear_skinny_scratch(int M, int N, int K, long long* floats, i
   return HS_OK;
 }
 
+// pdl != 0: launched with programmatic stream serialization (the weight fetch overlaps the
+// previous kernel of the stream).
 // Refuses (HS_ERR_UNSUPPORTED) M > 64, K not a multiple of 32, and unaligned pointers; the
 // caller then uses another kernel.
 HS_EXPORT int hs_linear_skinny(void* out, const void* a, const float* x, const float* gamma,
                                const float* beta, float eps, const void* w, const float* bias,
                                const float* residual, int M, int N, int K, int act, int out_dtype,
-                               float* scratch, int* counters, void* stream) {
+                               float* scratch, int* counters, int pdl, void* stream) {
   using namespace hs;
   if (!out || !w || (!a && !x)) return HS_ERR_ARGUMENT;
   if (x && (!gamma || !beta)) return HS_ERR_ARGUMENT;
@@ -332,9 +338,9 @@ HS_EXPORT int hs_linear_skinny(void* out, const void* a, const float* x, const f
   p.kper = pl.kper; p.stride = pl.stride; p.ng = pl.ng; p.eps = eps;
   cudaStream_t st = (cudaStream_t)stream;
   switch (pl.mt) {
-    case 1: return launch_skinny<1>(p, pl.ksplit, pl.smem, st);
-    case 2: return launch_skinny<2>(p, pl.ksplit, pl.smem, st);
-    case 4: return launch_skinny<4>(p, pl.ksplit, pl.smem, st);
-    default: return launch_skinny<8>(p, pl.ksplit, pl.smem, st);
+    case 1: return launch_skinny<1>(p, pl.ksplit, pl.smem, st, pdl != 0);
+    case 2: return launch_skinny<2>(p, pl.ksplit, pl.smem, st, pdl != 0);
+    case 4: return launch_skinny<4>(p, pl.ksplit, pl.smem, st, pdl != 0);
+    default: return launch_skinny<8>(p, pl.ksplit, pl.smem, st, pdl != 0);
   }
 }

@@ -119,12 +119,12 @@ def _declare(lib) -> None:
         "hs_layernorm": [P, P, P, P, P, I, I, F, I, P],
         "hs_linear_simt": [P, P, P, P, P, I, I, I, I, I, I, P],
         "hs_linear_tcgen05": [P, P, P, P, P, I, I, I, I, I, I, P, P],
-        "hs_linear_skinny": [P, P, P, P, P, F, P, P, P, I, I, I, I, I, P, P, P],
+        "hs_linear_skinny": [P, P, P, P, P, F, P, P, P, I, I, I, I, I, P, P, I, P],
         "hs_linear_skinny_scratch": [I, I, I, P, P],
         "hs_kv_append": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "hs_attention_simt": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
         "hs_attention_decode_append": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I,
-                                       F, I, I, I, P, P, P, P, P],
+                                       F, I, I, I, I, P, P, P, P, P],
         "hs_attention_prefill": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
         "hs_argmax": [P, P, I, I, P],
         "hs_sample": [P, P, P, P, P, P, P, I, I, P],
@@ -181,6 +181,7 @@ class CudaOps:
         self.sm_count = torch.cuda.get_device_properties(0).multi_processor_count
         self.fuse_norm = True      # LayerNorm fused into the few-row linear kernel
         self.fuse_append = True    # key/value append fused into the decode attention
+        self.pdl = True            # programmatic dependent launch of the decode kernels
         self._skinny_need: dict = {}
         self._scratch: dict = {}
         self._retired: list = []
@@ -309,7 +310,7 @@ class CudaOps:
         code = self.lib.hs_linear_skinny(
             _ptr(out), _ptr(a), _ptr(x), _ptr(g), _ptr(b), float(eps), _ptr(w), _ptr(bias),
             _ptr(residual), M, N, K, act, _DT[out.dtype], _ptr(scratch), _ptr(cnt),
-            self._stream())
+            int(self.pdl), self._stream())
         if code == -1:
             return False
         _check(code, f"linear_skinny(M={M},N={N},K={K})")
@@ -513,7 +514,8 @@ class CudaOps:
                 _ptr(dec_info), _ptr(head), plan.decode_cap, g.n_heads, g.n_kv_heads, g.head_dim,
                 g.page_size, g.num_pages, g.max_pages, g.q_off, g.k_off, g.v_off, g.qkv_stride,
                 g.window, scale, splits, int(bool(fuse)),
-                int(self.decode_wide(plan.decode_cap, g.n_heads)), _ptr(acc), _ptr(ml), _ptr(cnt),
+                int(self.decode_wide(plan.decode_cap, g.n_heads)), int(self.pdl), _ptr(acc),
+                _ptr(ml), _ptr(cnt),
                 _ptr(status), st), f"attention_decode(head_dim={g.head_dim})")
         if plan.tile_cap:
             self.launches += 1
