@@ -25,7 +25,7 @@
 
 namespace hs {
 
-constexpr int SK_WARPS = 8, SK_THREADS = SK_WARPS * 32, SK_FEATS = 16;
+constexpr int SK_FEATS = 16;
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   uint4 v;
@@ -64,24 +64,30 @@ struct WBatch {
   uint4 a[4], b[4];
 };
 
-template <int MT>
-__global__ void __launch_bounds__(SK_THREADS)
+constexpr int SK_LN_ROW_F4 = 16;      // a row of up to 16 * 128 = 2048 floats is normalised from registers
+
+// NW warps per CTA: 8, or 16 for deep layers (more 32-wide k blocks in flight per feature group).
+template <int MT, int NW>
+__global__ void __launch_bounds__(NW * 32)
 linear_skinny_kernel(const SkinnyParams p) {
   constexpr int MP = MT * 8;
+  constexpr int THREADS = NW * 32;
   extern __shared__ __align__(16) uint8_t sk_smem[];
   __nv_bfloat16* sx = (__nv_bfloat16*)sk_smem;             // [MP][stride]
+  float* sgb = (float*)(sk_smem + (size_t)MP * p.stride * 2);   // gamma | beta of the k range
   __shared__ float s_mu[MP], s_rs[MP];
   __shared__ int s_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  // warp -> (feature group, k group): ng groups of 16 features, 8 / ng warps share each
-  const int fg = warp % p.ng, kg = warp / p.ng, n_kg = SK_WARPS / p.ng;
+  // warp -> (feature group, k group): ng groups of 16 features, NW / ng warps share each
+  const int fg = warp % p.ng, kg = warp / p.ng, n_kg = NW / p.ng;
   const int n0 = (blockIdx.x * p.ng + fg) * SK_FEATS;
   const int K = p.K, M = p.M;
   const int ksplit = gridDim.y;
   const int k0 = blockIdx.y * p.kper;
   const int kn = min(p.kper, K - k0);                       // may be <= 0 for the last splits
   const int nblk = kn > 0 ? kn / 32 : 0;
+  const int feats = 16 * p.ng;
 
   const int row_a = min(n0 + g, p.N - 1), row_b = min(n0 + g + 8, p.N - 1);   // clamped: never stored
   const __nv_bfloat16* wa = p.w + (size_t)row_a * K + k0 + t * 8;
@@ -96,69 +102,129 @@ linear_skinny_kernel(const SkinnyParams p) {
       }
     }
   };
-  // the first weight fragments are requested before anything else: they do not depend on the
-  // activations, so their latency overlaps the staging below
+  // ---- before the previous kernel is waited for: everything that only reads parameters.
+  // The first weight fragments, the bias of this thread's output element, the norm's scale and
+  // shift for this CTA's k range.
   WBatch cur;
   load_batch(kg, cur);
-  pdl_trigger();      // the next kernel may begin its own weight fetch
-  pdl_wait();         // from here on the activations of the previous kernel are read
+  const int my_e = threadIdx.x;                              // first epilogue element of this thread
+  const int my_n = blockIdx.x * feats + (my_e % feats);
+  float my_bias = 0.f;
+  if (p.bias && my_e < feats * MP && my_n < p.N) my_bias = p.bias[my_n];
+  if (p.x && kn > 0) {
+    for (int i = threadIdx.x; i < kn / 4; i += THREADS) {
+      ((float4*)sgb)[i] = ((const float4*)(p.gamma + k0))[i];
+      ((float4*)(sgb + kn))[i] = ((const float4*)(p.beta + k0))[i];
+    }
+  }
+  pdl_trigger();      // the next kernel may begin its own parameter fetch
+  pdl_wait();         // from here on what the previous kernels wrote is read
 
-  if (p.x) {        // LayerNorm statistics of every row, one warp per row
-    for (int m = warp; m < MP; m += SK_WARPS) {
-      float mu = 0.f, rs = 0.f;
-      if (m < M) {
-        const float4* xr = (const float4*)(p.x + (size_t)m * K);
-        float s = 0.f;
-#pragma unroll 8
-        for (int k = lane; k < K / 4; k += 32) {
-          const float4 v = xr[k];
-          s += (v.x + v.y) + (v.z + v.w);
+  // the residual element of this thread, requested early so that the epilogue does not wait
+  float my_res = 0.f;
+  const int my_m = my_e / feats;
+  if (p.residual && my_e < feats * MP && my_m < M && my_n < p.N && ksplit == 1)
+    my_res = p.residual[(size_t)my_m * p.N + my_n];
+
+  if (p.x) {
+    if (K <= SK_LN_ROW_F4 * 128) {
+      // LayerNorm from registers: a warp reads a whole row once, forms the mean and the centred
+      // variance, and writes the normalised k range of this CTA to shared memory
+      __syncthreads();                                       // gamma/beta are in shared memory
+      for (int m = warp; m < MP; m += NW) {
+        float4 xr[SK_LN_ROW_F4];
+        const float4* src = (const float4*)(p.x + (size_t)m * K);
+        const int nf4 = K / 4;
+        if (m < M) {
+#pragma unroll
+          for (int i = 0; i < SK_LN_ROW_F4; ++i)
+            xr[i] = (lane + 32 * i < nf4) ? src[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+          float sum = 0.f;
+#pragma unroll
+          for (int i = 0; i < SK_LN_ROW_F4; ++i) sum += (xr[i].x + xr[i].y) + (xr[i].z + xr[i].w);
+          const float mu = warp_sum(sum) / (float)K;
+          float q = 0.f;
+#pragma unroll
+          for (int i = 0; i < SK_LN_ROW_F4; ++i) {
+            if (lane + 32 * i < nf4) {
+              const float c0 = xr[i].x - mu, c1 = xr[i].y - mu, c2 = xr[i].z - mu, c3 = xr[i].w - mu;
+              q += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+            }
+          }
+          const float rs = 1.0f / sqrtf(warp_sum(q) / (float)K + p.eps);
+#pragma unroll
+          for (int i = 0; i < SK_LN_ROW_F4; ++i) {
+            const int kk = (lane + 32 * i) * 4 - k0;          // column inside this CTA's k range
+            if (lane + 32 * i < nf4 && kk >= 0 && kk < kn) {
+              const float4 ga = *(const float4*)(sgb + kk), be = *(const float4*)(sgb + kn + kk);
+              __nv_bfloat162 o0 = __floats2bfloat162_rn((xr[i].x - mu) * rs * ga.x + be.x,
+                                                        (xr[i].y - mu) * rs * ga.y + be.y);
+              __nv_bfloat162 o1 = __floats2bfloat162_rn((xr[i].z - mu) * rs * ga.z + be.z,
+                                                        (xr[i].w - mu) * rs * ga.w + be.w);
+              uint2 v;
+              v.x = *(uint32_t*)&o0; v.y = *(uint32_t*)&o1;
+              *(uint2*)(sx + (size_t)m * p.stride + kk) = v;
+            }
+          }
+        } else {
+          for (int kk = lane * 4; kk < kn; kk += 128)
+            *(uint2*)(sx + (size_t)m * p.stride + kk) = make_uint2(0, 0);
         }
-        mu = warp_sum(s) / (float)K;
-        float q = 0.f;
-#pragma unroll 8
-        for (int k = lane; k < K / 4; k += 32) {
-          const float4 v = xr[k];
-          const float c0 = v.x - mu, c1 = v.y - mu, c2 = v.z - mu, c3 = v.w - mu;
-          q += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
-        }
-        rs = 1.0f / sqrtf(warp_sum(q) / (float)K + p.eps);
       }
-      if (lane == 0) {
-        s_mu[m] = mu;
-        s_rs[m] = rs;
+    } else {
+      // long rows: statistics in two passes over global memory, then staging
+      for (int m = warp; m < MP; m += NW) {
+        float mu = 0.f, rs = 0.f;
+        if (m < M) {
+          const float4* xr = (const float4*)(p.x + (size_t)m * K);
+          float sum = 0.f;
+#pragma unroll 8
+          for (int k = lane; k < K / 4; k += 32) {
+            const float4 v = xr[k];
+            sum += (v.x + v.y) + (v.z + v.w);
+          }
+          mu = warp_sum(sum) / (float)K;
+          float q = 0.f;
+#pragma unroll 8
+          for (int k = lane; k < K / 4; k += 32) {
+            const float4 v = xr[k];
+            const float c0 = v.x - mu, c1 = v.y - mu, c2 = v.z - mu, c3 = v.w - mu;
+            q += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+          }
+          rs = 1.0f / sqrtf(warp_sum(q) / (float)K + p.eps);
+        }
+        if (lane == 0) {
+          s_mu[m] = mu;
+          s_rs[m] = rs;
+        }
+      }
+      __syncthreads();
+      if (kn > 0) {
+#pragma unroll 4
+        for (int i = threadIdx.x; i < MP * (kn / 4); i += THREADS) {
+          const int m = i / (kn / 4), kk = (i % (kn / 4)) * 4;
+          uint2 v = make_uint2(0, 0);
+          if (m < M) {
+            const float4 x0 = *(const float4*)(p.x + (size_t)m * K + k0 + kk);
+            const float4 ga = *(const float4*)(sgb + kk), be = *(const float4*)(sgb + kn + kk);
+            const float mu = s_mu[m], rs = s_rs[m];
+            __nv_bfloat162 o0 = __floats2bfloat162_rn((x0.x - mu) * rs * ga.x + be.x,
+                                                      (x0.y - mu) * rs * ga.y + be.y);
+            __nv_bfloat162 o1 = __floats2bfloat162_rn((x0.z - mu) * rs * ga.z + be.z,
+                                                      (x0.w - mu) * rs * ga.w + be.w);
+            v.x = *(uint32_t*)&o0; v.y = *(uint32_t*)&o1;
+          }
+          *(uint2*)(sx + (size_t)m * p.stride + kk) = v;
+        }
       }
     }
-    __syncthreads();
-  }
-
-  // ---- stage this CTA's k range of the activations [MP][kn] (rows past M are zero)
-  if (kn > 0) {
+  } else if (kn > 0) {
+    // ---- stage this CTA's k range of the bfloat16 activations [MP][kn] (rows past M are zero)
 #pragma unroll 4
-    for (int i = threadIdx.x; i < MP * (kn / 8); i += SK_THREADS) {
+    for (int i = threadIdx.x; i < MP * (kn / 8); i += THREADS) {
       const int m = i / (kn / 8), kk = (i % (kn / 8)) * 8;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (m < M) {
-        if (p.x) {
-          const float4* xr = (const float4*)(p.x + (size_t)m * K + k0 + kk);
-          const float4 x0 = xr[0], x1 = xr[1];
-          const float4* gp = (const float4*)(p.gamma + k0 + kk);
-          const float4* bp = (const float4*)(p.beta + k0 + kk);
-          const float4 g0 = gp[0], g1 = gp[1], b0 = bp[0], b1 = bp[1];
-          const float mu = s_mu[m], rs = s_rs[m];
-          __nv_bfloat162 o0 = __floats2bfloat162_rn((x0.x - mu) * rs * g0.x + b0.x,
-                                                    (x0.y - mu) * rs * g0.y + b0.y);
-          __nv_bfloat162 o1 = __floats2bfloat162_rn((x0.z - mu) * rs * g0.z + b0.z,
-                                                    (x0.w - mu) * rs * g0.w + b0.w);
-          __nv_bfloat162 o2 = __floats2bfloat162_rn((x1.x - mu) * rs * g1.x + b1.x,
-                                                    (x1.y - mu) * rs * g1.y + b1.y);
-          __nv_bfloat162 o3 = __floats2bfloat162_rn((x1.z - mu) * rs * g1.z + b1.z,
-                                                    (x1.w - mu) * rs * g1.w + b1.w);
-          v.x = *(uint32_t*)&o0; v.y = *(uint32_t*)&o1; v.z = *(uint32_t*)&o2; v.w = *(uint32_t*)&o3;
-        } else {
-          v = *(const uint4*)(p.a + (size_t)m * K + k0 + kk);
-        }
-      }
+      if (m < M) v = *(const uint4*)(p.a + (size_t)m * K + k0 + kk);
       *(uint4*)(sx + (size_t)m * p.stride + kk) = v;
     }
   }
@@ -187,7 +253,7 @@ linear_skinny_kernel(const SkinnyParams p) {
   }
   // ---- add the warps' partial tiles in warp order
   __syncthreads();
-  float* red = (float*)sk_smem;                          // [SK_WARPS][16][MP]
+  float* red = (float*)sk_smem;                          // [NW][16][MP]
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
     const int m = mt * 8 + t * 2;
@@ -197,12 +263,11 @@ linear_skinny_kernel(const SkinnyParams p) {
     red[(warp * 16 + g + 8) * MP + m + 1] = c[mt][3];
   }
   __syncthreads();
-  const int feats = 16 * p.ng;
   if (ksplit > 1) {
     // this CTA's share goes to scratch; the last CTA of the feature block to arrive adds the
     // shares in split order
     float* mine = p.partial + (size_t)blockIdx.y * MP * p.N;
-    for (int i = threadIdx.x; i < feats * MP; i += SK_THREADS) {
+    for (int i = threadIdx.x; i < feats * MP; i += THREADS) {
       const int m = i / feats, ff = i % feats;
       const int n = blockIdx.x * feats + ff;
       if (n >= p.N) continue;
@@ -218,7 +283,7 @@ linear_skinny_kernel(const SkinnyParams p) {
     if (!s_last) return;
     __threadfence();
   }
-  for (int i = threadIdx.x; i < feats * MP; i += SK_THREADS) {
+  for (int i = threadIdx.x; i < feats * MP; i += THREADS) {
     const int m = i / feats, ff = i % feats;             // consecutive threads -> consecutive n
     const int n = blockIdx.x * feats + ff;
     if (m >= M || n >= p.N) continue;
@@ -230,19 +295,20 @@ linear_skinny_kernel(const SkinnyParams p) {
       const int grp = ff / 16, f = ff % 16;
       for (int k8 = 0; k8 < n_kg; ++k8) v += red[((k8 * p.ng + grp) * 16 + f) * MP + m];
     }
-    if (p.bias) v += p.bias[n];
+    const bool first = i == my_e;                        // bias (and residual) already in registers
+    if (p.bias) v += first ? my_bias : p.bias[n];
     v = apply_act(v, p.act);
-    if (p.residual) v += p.residual[(size_t)m * p.N + n];
+    if (p.residual) v += (first && ksplit == 1) ? my_res : p.residual[(size_t)m * p.N + n];
     if (p.out_f32) ((float*)p.out)[(size_t)m * p.N + n] = v;
     else ((__nv_bfloat16*)p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
   }
   if (ksplit > 1 && threadIdx.x == 0) p.counters[blockIdx.x] = 0;   // ready for the next launch
 }
 
-template <int MT>
+template <int MT, int NW>
 static int launch_skinny(const SkinnyParams& p, int ksplit, size_t smem, cudaStream_t st,
                          bool pdl) {
-  auto kern = linear_skinny_kernel<MT>;
+  auto kern = linear_skinny_kernel<MT, NW>;
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -252,20 +318,20 @@ static int launch_skinny(const SkinnyParams& p, int ksplit, size_t smem, cudaStr
   }
   const int per_cta = SK_FEATS * p.ng;
   dim3 grid((p.N + per_cta - 1) / per_cta, ksplit);
-  cudaError_t le = hs_launch(kern, grid, dim3(SK_THREADS), smem, st, pdl, p);
+  cudaError_t le = hs_launch(kern, grid, dim3(NW * 32), smem, st, pdl, p);
   if (le != cudaSuccess) return (int)le;
   HS_LAUNCH_CHECK();
   return HS_OK;
 }
 
 struct SkinnyPlan {
-  int mt, mp, ng, ksplit, kper, stride, blocks;
+  int mt, mp, ng, nw, ksplit, kper, stride, blocks;
   size_t smem;
 };
 
-// How a shape is cut: features per CTA, splits over k, shared memory.  Returns false for
-// shapes the kernel does not take.
-static bool plan_skinny(int M, int N, int K, SkinnyPlan& pl) {
+// How a shape is cut: features per CTA, warps per CTA, splits over k, shared memory.  Returns
+// false for shapes the kernel does not take.
+static bool plan_skinny(int M, int N, int K, bool with_norm, SkinnyPlan& pl) {
   if (M <= 0 || M > 64 || K <= 0 || K % 32) return false;
   pl.mt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
   pl.mp = pl.mt * 8;
@@ -276,10 +342,29 @@ static bool plan_skinny(int M, int N, int K, SkinnyPlan& pl) {
   pl.ng = 1;
   while (pl.ng < 8 && (N + 32 * pl.ng - 1) / (32 * pl.ng) >= 2 * sms) pl.ng *= 2;
   pl.blocks = (N + 16 * pl.ng - 1) / (16 * pl.ng);
-  // k per CTA: at most what fits ~96 KB of shared memory, at least 1024 (four blocks a warp),
-  // and few enough splits that about two CTAs per SM are in flight
+  auto smem_for = [&](int kper, int& stride) {
+    stride = kper + ((32 - kper % 64) + 64) % 64;             // stride % 64 == 32
+    if (stride % 64 != 32) stride += 32;
+    size_t sm = (size_t)pl.mp * stride * 2 + (with_norm ? (size_t)kper * 8 : 0);
+    const size_t red = (size_t)16 * 16 * pl.mp * 4;
+    return sm > red ? sm : red;
+  };
+  // Deep layers (k >= 2048) whose feature blocks alone leave SMs idle: 16 warps per CTA and
+  // the whole k range in one CTA if its activations fit shared memory - no scratch round trip.
+  pl.nw = 8;
+  int stride = 0;
+  if (K >= 2048 && pl.ng == 1 && pl.mt <= 2 && smem_for(K, stride) <= 200 * 1024) {
+    pl.nw = 16;
+    pl.ksplit = 1;
+    pl.kper = K;
+    pl.stride = stride;
+    pl.smem = smem_for(K, stride);
+    return true;
+  }
+  // otherwise: k per CTA at most what fits ~96 KB of shared memory, at least 1024 (four blocks
+  // a warp), and few enough splits that about two CTAs per SM are in flight
   const size_t budget = 96 * 1024;
-  int kc = (int)(budget / (2 * (size_t)pl.mp)) - 64;
+  int kc = (int)(budget / (2 * (size_t)pl.mp + (with_norm ? 8 : 0))) - 64;
   kc = kc / 32 * 32;
   if (kc < 256) return false;
   int want = (2 * sms + pl.blocks - 1) / pl.blocks;
@@ -290,11 +375,7 @@ static bool plan_skinny(int M, int N, int K, SkinnyPlan& pl) {
   if (ksplit < 1) ksplit = 1;
   pl.kper = ((K / 32 + ksplit - 1) / ksplit) * 32;
   pl.ksplit = (K + pl.kper - 1) / pl.kper;
-  pl.stride = pl.kper + ((32 - pl.kper % 64) + 64) % 64;       // stride % 64 == 32
-  if (pl.stride % 64 != 32) pl.stride += 32;
-  pl.smem = (size_t)pl.mp * pl.stride * 2;
-  const size_t red = (size_t)SK_WARPS * 16 * pl.mp * 4;
-  if (red > pl.smem) pl.smem = red;
+  pl.smem = smem_for(pl.kper, pl.stride);
   return true;
 }
 
@@ -302,9 +383,10 @@ static bool plan_skinny(int M, int N, int K, SkinnyPlan& pl) {
 
 // Scratch a launch needs: floats for the partial sums and ints for the counters (both zero for
 // shapes that are not split over k).  Negative: the shape is not taken.
-HS_EXPORT int hs_linear_skinny_scratch(int M, int N, int K, long long* floats, int* counters) {
+HS_EXPORT int hs_linear_skinny_scratch(int M, int N, int K, int with_norm, long long* floats,
+                                       int* counters) {
   hs::SkinnyPlan pl;
-  if (!hs::plan_skinny(M, N, K, pl)) return HS_ERR_UNSUPPORTED;
+  if (!hs::plan_skinny(M, N, K, with_norm != 0, pl)) return HS_ERR_UNSUPPORTED;
   *floats = pl.ksplit > 1 ? (long long)pl.ksplit * pl.mp * N : 0;
   *counters = pl.ksplit > 1 ? pl.blocks : 0;
   return HS_OK;
@@ -323,7 +405,7 @@ HS_EXPORT int hs_linear_skinny(void* out, const void* a, const float* x, const f
   if (x && (!gamma || !beta)) return HS_ERR_ARGUMENT;
   if (M <= 0 || N <= 0) return HS_OK;
   SkinnyPlan pl;
-  if (!plan_skinny(M, N, K, pl)) return HS_ERR_UNSUPPORTED;
+  if (!plan_skinny(M, N, K, x != nullptr, pl)) return HS_ERR_UNSUPPORTED;
   if (((uintptr_t)w & 15) || (a && ((uintptr_t)a & 15)) || (x && ((uintptr_t)x & 15)) ||
       (gamma && ((uintptr_t)gamma & 15)) || (beta && ((uintptr_t)beta & 15)))
     return HS_ERR_UNSUPPORTED;
@@ -337,10 +419,14 @@ HS_EXPORT int hs_linear_skinny(void* out, const void* a, const float* x, const f
   p.M = M; p.N = N; p.K = K; p.act = act; p.out_f32 = out_dtype == HS_DT_F32;
   p.kper = pl.kper; p.stride = pl.stride; p.ng = pl.ng; p.eps = eps;
   cudaStream_t st = (cudaStream_t)stream;
+  if (pl.nw == 16) {
+    if (pl.mt == 1) return launch_skinny<1, 16>(p, pl.ksplit, pl.smem, st, pdl != 0);
+    return launch_skinny<2, 16>(p, pl.ksplit, pl.smem, st, pdl != 0);
+  }
   switch (pl.mt) {
-    case 1: return launch_skinny<1>(p, pl.ksplit, pl.smem, st, pdl != 0);
-    case 2: return launch_skinny<2>(p, pl.ksplit, pl.smem, st, pdl != 0);
-    case 4: return launch_skinny<4>(p, pl.ksplit, pl.smem, st, pdl != 0);
-    default: return launch_skinny<8>(p, pl.ksplit, pl.smem, st, pdl != 0);
+    case 1: return launch_skinny<1, 8>(p, pl.ksplit, pl.smem, st, pdl != 0);
+    case 2: return launch_skinny<2, 8>(p, pl.ksplit, pl.smem, st, pdl != 0);
+    case 4: return launch_skinny<4, 8>(p, pl.ksplit, pl.smem, st, pdl != 0);
+    default: return launch_skinny<8, 8>(p, pl.ksplit, pl.smem, st, pdl != 0);
   }
 }

@@ -120,7 +120,7 @@ def _declare(lib) -> None:
         "hs_linear_simt": [P, P, P, P, P, I, I, I, I, I, I, P],
         "hs_linear_tcgen05": [P, P, P, P, P, I, I, I, I, I, I, P, P],
         "hs_linear_skinny": [P, P, P, P, P, F, P, P, P, I, I, I, I, I, P, P, I, P],
-        "hs_linear_skinny_scratch": [I, I, I, P, P],
+        "hs_linear_skinny_scratch": [I, I, I, I, P, P],
         "hs_kv_append": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "hs_attention_simt": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
         "hs_attention_decode_append": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I,
@@ -289,12 +289,12 @@ class CudaOps:
     def _skinny(self, out, a, norm, w, bias, act, residual, M, N, K) -> bool:
         """The weight-streaming kernel; ``norm = (x, gamma, beta, eps)`` fuses a LayerNorm of
         the float32 input.  False when the kernel does not take the shape."""
-        key = (M, N, K)
+        key = (M, N, K, norm is not None)
         need = self._skinny_need.get(key)
         if need is None:
             floats, counters = ctypes.c_longlong(0), ctypes.c_int(0)
-            code = self.lib.hs_linear_skinny_scratch(M, N, K, ctypes.byref(floats),
-                                                     ctypes.byref(counters))
+            code = self.lib.hs_linear_skinny_scratch(M, N, K, int(norm is not None),
+                                                     ctypes.byref(floats), ctypes.byref(counters))
             need = (floats.value, counters.value) if code == 0 else False
             self._skinny_need[key] = need
         if need is False:
