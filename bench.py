@@ -220,7 +220,7 @@ def time_e2e(model_dir, torch, batch, prompt_len, steps, warmup, vocab, seed, nu
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     assert all(len(s.output_ids) == 1 + warmup + steps for s in seqs)
-    lay = eng.runner._layout(16 if batch <= 16 else batch, batch, batch)
+    lay = eng.runner._layout(max(8, batch), batch, batch)
     h2d = lay.total * 4
     d2h = (batch + 1) * 4
     eng.run_until_done()

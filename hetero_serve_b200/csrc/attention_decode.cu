@@ -87,17 +87,18 @@ attention_decode_kernel(const DecodeParams p) {
   const bool own_here = p.fuse_append && pos >= split * chunk && pos < (split + 1) * chunk;
   const int k_end = min((split + 1) * chunk, p.fuse_append ? pos : pos + 1);   // exclusive
 
-  // the query, 8 elements per lane (the same 8 its key lanes read).  Everything above came
-  // from the host's work lists; the query is the first thing the previous kernel wrote.
+  // the query, 8 elements per lane (the same 8 its key lanes read).  It is the first thing the
+  // previous kernel wrote that this one needs: the work lists, the block table and the keys and
+  // values of earlier positions are fetched before the dependency wait.
   const int part = lane % LPK, sub = lane / LPK;
-  pdl_trigger();
-  pdl_wait();
   float q[8];
-  {
+  auto wait_and_load_query = [&]() {
+    pdl_trigger();
+    pdl_wait();
     const uint4 qu = *(const uint4*)(p.qkv + (size_t)t * p.qkv_stride + p.q_off + (size_t)h * D +
                                      part * 8);
     unpack8(qu, q);
-  }
+  };
   float m = -INFINITY, l = 0.f, acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -149,7 +150,13 @@ attention_decode_kernel(const DecodeParams p) {
       }
     };
     Unit cur, nxt;
+    // Keys and values of earlier positions were written by earlier steps, so with the append
+    // fused in (nothing else writes this layer's pages during the step) the first group is
+    // requested before the dependency wait.  Without fusion the previous kernel may be the one
+    // that appends this step's keys: wait first.
+    if (!p.fuse_append) wait_and_load_query();
     if (n_units > 0) load_unit(0, cur);
+    if (p.fuse_append) wait_and_load_query();
     for (int u = 0; u < n_units; ++u) {
       if (u + 1 < n_units) load_unit(u + 1, nxt);        // in flight while `cur` is used
       float s[4];
@@ -191,6 +198,8 @@ attention_decode_kernel(const DecodeParams p) {
       }
       cur = nxt;
     }
+  } else {
+    wait_and_load_query();
   }
   if (own_here && warp == NW - 1) {
     // the new key and value: lanes of key group 0 hold 8 elements each

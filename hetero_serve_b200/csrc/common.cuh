@@ -34,6 +34,8 @@
 
 #define HS_EXPORT extern "C" __attribute__((visibility("default")))
 
+unsigned long long* hs_timing_buffer();   // embed_norm.cu
+
 #define HS_LAUNCH_CHECK()                      \
   do {                                         \
     cudaError_t e__ = cudaGetLastError();      \
@@ -76,6 +78,17 @@ __device__ __forceinline__ float apply_act(float u, int act) {
   if (act == HS_ACT_GELU_TANH) return gelu_tanh(u);
   if (act == HS_ACT_GELU_ERF) return gelu_erf(u);
   return u;
+}
+
+// Optional phase timing for tuning: when a buffer has been set with hs_set_timing_buffer, thread
+// 0 of every CTA of the instrumented kernels stores the global nanosecond timer at a few
+// marks: buffer[(cta * 8) + mark].  Null (the default) costs one predictable branch.
+__device__ __forceinline__ void mark_time(unsigned long long* buf, int cta, int mark) {
+  if (buf != nullptr && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    buf[(size_t)cta * 8 + mark] = t;
+  }
 }
 
 // Programmatic dependent launch: a kernel launched with the programmatic-serialization

@@ -138,3 +138,9 @@ HS_EXPORT int hs_layernorm(void* out, const float* x, const float* gamma, const 
   HS_LAUNCH_CHECK();
   return HS_OK;
 }
+
+// Tuning aid: a device buffer of 8 x uint64 per CTA that instrumented kernels fill with
+// nanosecond timestamps (see mark_time in common.cuh); null switches it off.
+static unsigned long long* g_timing_buffer = nullptr;
+HS_EXPORT void hs_set_timing_buffer(unsigned long long* buf) { g_timing_buffer = buf; }
+unsigned long long* hs_timing_buffer() { return g_timing_buffer; }

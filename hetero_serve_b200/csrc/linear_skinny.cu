@@ -58,13 +58,15 @@ struct SkinnyParams {
   int kper, stride;            // k per CTA (multiple of 32); smem row stride in elements
   int ng;                      // feature groups (of 16) per CTA: 1, 2, 4 or 8
   float eps;
+  unsigned long long* timing;  // null, or the tuning buffer (see mark_time)
 };
 
 struct WBatch {
   uint4 a[4], b[4];
 };
 
-constexpr int SK_LN_ROW_F4 = 16;      // a row of up to 16 * 128 = 2048 floats is normalised from registers
+constexpr int SK_LN_ROW_F4 = 8;       // a row of up to 8 * 128 = 1024 floats is normalised from registers
+                                      // (two rows at a time); longer rows take the three-pass route
 
 // NW warps per CTA: 8, or 16 for deep layers (more 32-wide k blocks in flight per feature group).
 template <int MT, int NW>
@@ -105,6 +107,8 @@ linear_skinny_kernel(const SkinnyParams p) {
   // ---- before the previous kernel is waited for: everything that only reads parameters.
   // The first weight fragments, the bias of this thread's output element, the norm's scale and
   // shift for this CTA's k range.
+  const int cta_id = blockIdx.y * gridDim.x + blockIdx.x;
+  mark_time(p.timing, cta_id, 0);
   WBatch cur;
   load_batch(kg, cur);
   const int my_e = threadIdx.x;                              // first epilogue element of this thread
@@ -119,6 +123,7 @@ linear_skinny_kernel(const SkinnyParams p) {
   }
   pdl_trigger();      // the next kernel may begin its own parameter fetch
   pdl_wait();         // from here on what the previous kernels wrote is read
+  mark_time(p.timing, cta_id, 1);
 
   // the residual element of this thread, requested early so that the epilogue does not wait
   float my_res = 0.f;
@@ -131,44 +136,61 @@ linear_skinny_kernel(const SkinnyParams p) {
       // LayerNorm from registers: a warp reads a whole row once, forms the mean and the centred
       // variance, and writes the normalised k range of this CTA to shared memory
       __syncthreads();                                       // gamma/beta are in shared memory
-      for (int m = warp; m < MP; m += NW) {
-        float4 xr[SK_LN_ROW_F4];
-        const float4* src = (const float4*)(p.x + (size_t)m * K);
-        const int nf4 = K / 4;
-        if (m < M) {
+      // a warp takes rows warp, warp + NW, ...; the loads of two rows are in flight together
+      constexpr int RPW = (MP + NW - 1) / NW;                // rows per warp
+      const int nf4 = K / 4;
+#pragma unroll
+      for (int r0 = 0; r0 < RPW; r0 += 2) {
+        float4 xr[2][SK_LN_ROW_F4 / 2 * 2];
+        int rows[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          rows[j] = warp + (r0 + j) * NW;
+          const bool live = (r0 + j) < RPW && rows[j] < M;
+          const float4* src = (const float4*)(p.x + (size_t)(live ? rows[j] : 0) * K);
 #pragma unroll
           for (int i = 0; i < SK_LN_ROW_F4; ++i)
-            xr[i] = (lane + 32 * i < nf4) ? src[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
-          float sum = 0.f;
+            xr[j][i] = (live && lane + 32 * i < nf4) ? src[lane + 32 * i]
+                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
 #pragma unroll
-          for (int i = 0; i < SK_LN_ROW_F4; ++i) sum += (xr[i].x + xr[i].y) + (xr[i].z + xr[i].w);
-          const float mu = warp_sum(sum) / (float)K;
-          float q = 0.f;
+        for (int j = 0; j < 2; ++j) {
+          const int m = rows[j];
+          if ((r0 + j) >= RPW || m >= MP) continue;
+          if (m < M) {
+            float sum = 0.f;
 #pragma unroll
-          for (int i = 0; i < SK_LN_ROW_F4; ++i) {
-            if (lane + 32 * i < nf4) {
-              const float c0 = xr[i].x - mu, c1 = xr[i].y - mu, c2 = xr[i].z - mu, c3 = xr[i].w - mu;
-              q += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+            for (int i = 0; i < SK_LN_ROW_F4; ++i)
+              sum += (xr[j][i].x + xr[j][i].y) + (xr[j][i].z + xr[j][i].w);
+            const float mu = warp_sum(sum) / (float)K;
+            float q = 0.f;
+#pragma unroll
+            for (int i = 0; i < SK_LN_ROW_F4; ++i) {
+              if (lane + 32 * i < nf4) {
+                const float c0 = xr[j][i].x - mu, c1 = xr[j][i].y - mu, c2 = xr[j][i].z - mu,
+                            c3 = xr[j][i].w - mu;
+                q += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+              }
             }
-          }
-          const float rs = 1.0f / sqrtf(warp_sum(q) / (float)K + p.eps);
+            const float rs = 1.0f / sqrtf(warp_sum(q) / (float)K + p.eps);
 #pragma unroll
-          for (int i = 0; i < SK_LN_ROW_F4; ++i) {
-            const int kk = (lane + 32 * i) * 4 - k0;          // column inside this CTA's k range
-            if (lane + 32 * i < nf4 && kk >= 0 && kk < kn) {
-              const float4 ga = *(const float4*)(sgb + kk), be = *(const float4*)(sgb + kn + kk);
-              __nv_bfloat162 o0 = __floats2bfloat162_rn((xr[i].x - mu) * rs * ga.x + be.x,
-                                                        (xr[i].y - mu) * rs * ga.y + be.y);
-              __nv_bfloat162 o1 = __floats2bfloat162_rn((xr[i].z - mu) * rs * ga.z + be.z,
-                                                        (xr[i].w - mu) * rs * ga.w + be.w);
-              uint2 v;
-              v.x = *(uint32_t*)&o0; v.y = *(uint32_t*)&o1;
-              *(uint2*)(sx + (size_t)m * p.stride + kk) = v;
+            for (int i = 0; i < SK_LN_ROW_F4; ++i) {
+              const int kk = (lane + 32 * i) * 4 - k0;        // column inside this CTA's k range
+              if (lane + 32 * i < nf4 && kk >= 0 && kk < kn) {
+                const float4 ga = *(const float4*)(sgb + kk), be = *(const float4*)(sgb + kn + kk);
+                __nv_bfloat162 o0 = __floats2bfloat162_rn((xr[j][i].x - mu) * rs * ga.x + be.x,
+                                                          (xr[j][i].y - mu) * rs * ga.y + be.y);
+                __nv_bfloat162 o1 = __floats2bfloat162_rn((xr[j][i].z - mu) * rs * ga.z + be.z,
+                                                          (xr[j][i].w - mu) * rs * ga.w + be.w);
+                uint2 v;
+                v.x = *(uint32_t*)&o0; v.y = *(uint32_t*)&o1;
+                *(uint2*)(sx + (size_t)m * p.stride + kk) = v;
+              }
             }
+          } else {
+            for (int kk = lane * 4; kk < kn; kk += 128)
+              *(uint2*)(sx + (size_t)m * p.stride + kk) = make_uint2(0, 0);
           }
-        } else {
-          for (int kk = lane * 4; kk < kn; kk += 128)
-            *(uint2*)(sx + (size_t)m * p.stride + kk) = make_uint2(0, 0);
         }
       }
     } else {
@@ -229,6 +251,7 @@ linear_skinny_kernel(const SkinnyParams p) {
     }
   }
   __syncthreads();
+  mark_time(p.timing, cta_id, 2);
 
   float c[MT][4];
 #pragma unroll
@@ -253,6 +276,7 @@ linear_skinny_kernel(const SkinnyParams p) {
   }
   // ---- add the warps' partial tiles in warp order
   __syncthreads();
+  mark_time(p.timing, cta_id, 3);
   float* red = (float*)sk_smem;                          // [NW][16][MP]
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
@@ -303,6 +327,7 @@ linear_skinny_kernel(const SkinnyParams p) {
     else ((__nv_bfloat16*)p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
   }
   if (ksplit > 1 && threadIdx.x == 0) p.counters[blockIdx.x] = 0;   // ready for the next launch
+  mark_time(p.timing, cta_id, 4);
 }
 
 template <int MT, int NW>
@@ -418,6 +443,7 @@ HS_EXPORT int hs_linear_skinny(void* out, const void* a, const float* x, const f
   p.partial = scratch; p.counters = counters;
   p.M = M; p.N = N; p.K = K; p.act = act; p.out_f32 = out_dtype == HS_DT_F32;
   p.kper = pl.kper; p.stride = pl.stride; p.ng = pl.ng; p.eps = eps;
+  p.timing = hs_timing_buffer();
   cudaStream_t st = (cudaStream_t)stream;
   if (pl.nw == 16) {
     if (pl.mt == 1) return launch_skinny<1, 16>(p, pl.ksplit, pl.smem, st, pdl != 0);

@@ -298,7 +298,7 @@ class Runner:
             mgr.reserve(e.req_id, start + len(e.tokens))      # OutOfPages: nothing ran
 
         if self.use_graphs:
-            T, R = _bucket(n_tok, 16), _bucket(len(entries), 1)
+            T, R = _bucket(n_tok, 8), _bucket(len(entries), 1)
             W = _bucket(n_want, 1) if n_want else 0
         else:
             T, R, W = n_tok, len(entries), n_want
