@@ -156,9 +156,9 @@ attention_decode_kernel(const DecodeParams p) {
     // that appends this step's keys: wait first.
     if (!p.fuse_append) wait_and_load_query();
     if (n_units > 0) load_unit(0, cur);
+    if (n_units > 1) load_unit(1, nxt);
     if (p.fuse_append) wait_and_load_query();
     for (int u = 0; u < n_units; ++u) {
-      if (u + 1 < n_units) load_unit(u + 1, nxt);        // in flight while `cur` is used
       float s[4];
       float bm = -INFINITY;
 #pragma unroll
@@ -197,6 +197,7 @@ attention_decode_kernel(const DecodeParams p) {
         m = m_new;
       }
       cur = nxt;
+      if (u + 2 < n_units) load_unit(u + 2, nxt);        // two groups ahead of the one in use
     }
   } else {
     wait_and_load_query();

@@ -52,10 +52,19 @@ __device__ ArgMax block_argmax(const float* row, int vocab) {
   __shared__ ArgMax sh[SM_THREADS / 32];
   __shared__ ArgMax result;
   ArgMax best{-INFINITY, 0x7fffffff};
-#pragma unroll 8
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = row[i];
-    if (v > best.v || best.i == 0x7fffffff) best = ArgMax{v, i};  // first seen wins ties
+  // eight loads in flight per thread; within a thread indices rise, so the first seen wins ties
+  for (int base = threadIdx.x; base < vocab; base += 8 * blockDim.x) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = base + j * blockDim.x;
+      v[j] = i < vocab ? row[i] : -INFINITY;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = base + j * blockDim.x;
+      if (i < vocab && (v[j] > best.v || best.i == 0x7fffffff)) best = ArgMax{v[j], i};
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
