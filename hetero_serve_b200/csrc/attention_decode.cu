@@ -319,7 +319,7 @@ attention_decode_kernel(const DecodeParams p) {
 
 // fuse_append != 0: every served token is the only new token of its request; its key and value
 // (columns k_off / v_off of its row in `qkv`) are used from there and written to its page by the
-// kernel, so no separate append pass is needed.  wide != 0: 16 warps per CTA instead of 4 (for
+// kernel, so no separate append pass is needed.  wide: 0 = 4 warps per CTA, 1 = 8, 2 = 16 (for
 // batches whose token x head count alone does not fill the GPU).
 HS_EXPORT int hs_attention_decode_append(void* out, const void* qkv, void* pool, const int* table,
                                          const int* tok_pos, const int* tok_req,
@@ -341,7 +341,7 @@ HS_EXPORT int hs_attention_decode_append(void* out, const void* qkv, void* pool,
   if (splits > 1 && (!scratch_acc || !scratch_ml || !counters)) return HS_ERR_ARGUMENT;
   if ((qkv_stride % 8) || (q_off % 8) || (k_off % 8) || (v_off % 8))
     return HS_ERR_UNSUPPORTED;   // 16-byte loads of the query, key and value rows
-  const int nw = wide ? 16 : AD_WARPS;
+  const int nw = wide == 2 ? 16 : (wide == 1 ? 8 : AD_WARPS);
   // a slice may span at most 32 pages per warp
   if ((long long)splits * 32 * nw < max_pages) return HS_ERR_UNSUPPORTED;
   DecodeParams p;
@@ -359,7 +359,8 @@ HS_EXPORT int hs_attention_decode_append(void* out, const void* qkv, void* pool,
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t le = cudaSuccess;
 #define HS_AD(DD)                                                                             \
-  if (wide) le = hs_launch(attention_decode_kernel<DD, 16>, grid, dim3(16 * 32), 0, st, pdl != 0, p); \
+  if (wide == 2) le = hs_launch(attention_decode_kernel<DD, 16>, grid, dim3(16 * 32), 0, st, pdl != 0, p); \
+  else if (wide == 1) le = hs_launch(attention_decode_kernel<DD, 8>, grid, dim3(8 * 32), 0, st, pdl != 0, p); \
   else le = hs_launch(attention_decode_kernel<DD, AD_WARPS>, grid, dim3(AD_WARPS * 32), 0, st, pdl != 0, p)
   switch (head_dim) {
     case 16: HS_AD(16); break;

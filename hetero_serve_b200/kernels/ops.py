@@ -186,7 +186,7 @@ class CudaOps:
         self._scratch: dict = {}
         self._retired: list = []
         self.tile_n = 0            # 0: chosen per shape; 64/128/256 force a tile width
-        self.skinny_max_rows = 16  # up to this many rows the weight-streaming kernel is used
+        self.skinny_max_rows = 32  # up to this many rows the weight-streaming kernel is used
         # pipeline time-outs of the TMA/tcgen05 kernels are ORed into this word; the runner
         # replaces it with its own so that they surface with the step's results
         self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -284,7 +284,7 @@ class CudaOps:
                                        self._stream()), f"linear(M={M},N={N},K={K})")
 
     def _skinny_ok(self, M, N, K) -> bool:
-        return self.tensor_cores and (M <= self.skinny_max_rows or (M <= 64 and N >= 16384))
+        return self.tensor_cores and M <= self.skinny_max_rows
 
     def _skinny(self, out, a, norm, w, bias, act, residual, M, N, K) -> bool:
         """The weight-streaming kernel; ``norm = (x, gamma, beta, eps)`` fuses a LayerNorm of
@@ -442,9 +442,11 @@ class CudaOps:
             self._scratch[key] = buf
         return buf
 
-    def decode_wide(self, decode_cap: int, n_heads: int) -> bool:
-        """16 warps per CTA (instead of 4) while token x head count alone leaves SMs idle."""
-        return decode_cap * n_heads <= 2 * self.sm_count
+    def decode_wide(self, decode_cap: int, n_heads: int) -> int:
+        """Warps per CTA of the decode attention: 16 (code 2) while token x head count is below
+        the SM count, 8 (code 1) up to twice that, else 4 (code 0)."""
+        pairs = decode_cap * n_heads
+        return 2 if pairs <= self.sm_count else (1 if pairs <= 2 * self.sm_count else 0)
 
     def decode_splits(self, decode_cap: int, n_heads: int, max_context: int) -> int:
         """Slices between CTAs the context of a single-query token is cut into: one wave of
@@ -454,8 +456,8 @@ class CudaOps:
         small."""
         pairs = max(1, decode_cap * n_heads)
         wide = self.decode_wide(decode_cap, n_heads)
-        want = max(1, round(self.sm_count / pairs)) if wide else 1
-        per_warp = 32 * 16 * (16 if wide else 4)     # keys a CTA can cover: 32 pages per warp
+        want = max(1, round(self.sm_count / pairs)) if wide == 2 else 1
+        per_warp = 32 * 16 * (4, 8, 16)[wide]        # keys a CTA can cover: 32 pages per warp
         need = -(-max_context // per_warp)
         return max(1, need, min(want, max(1, max_context // 64), 32))
 
