@@ -8,15 +8,20 @@
 // `x + (... @ proj_w + proj_b)`, `ln_f(x) @ wte.T`: heteroserve/model/torch_engine.py:77-87,122,139)
 // with the bias, the activation and the float32 residual sum fused into the epilogue.
 //
-// One CTA computes one 128 x BN tile of `out`:
-//   warp 0      TMA producer: cp.async.bulk.tensor loads of a [128 x 64] tile of `a` and a
-//               [BN x 64] tile of `w` per stage, 128-byte swizzle, completion on an mbarrier;
-//   warp 1      allocates TMEM, then one elected thread issues tcgen05.mma (M=128, N=BN, K=16,
-//               kind::f16, bf16 inputs, f32 accumulate), four per stage, and commits each
-//               stage's completion to the stage's "empty" barrier;
-//   warps 2..5  epilogue: tcgen05.ld of the accumulator (lane = row, 32 columns at a time),
-//               bias / activation / residual in float32, stores.
-// Rows and columns beyond M, N and K are zero-filled by TMA and never stored.
+// A persistent CTA (one per SM) walks over 128 x BN output tiles (n fastest, so that CTAs running
+// together share rows of `a`):
+//   warp 0       TMA producer: cp.async.bulk.tensor loads of a [128 x 64] tile of `a` and a
+//                [BN x 64] tile of `w` per stage, 128-byte swizzle, completion on an mbarrier;
+//   warp 1       allocates TMEM (two accumulators), then one elected thread issues tcgen05.mma
+//                (M=128, N=BN, K=16, kind::f16, bf16 inputs, f32 accumulate), four per stage, and
+//                commits each stage's completion to the stage's "empty" barrier and each tile's
+//                to its accumulator's "full" barrier;
+//   warps 4..11  epilogue: tcgen05.ld of the accumulator (lane = row, 32 columns at a time, two
+//                warps per lane quarter), bias / activation / residual in float32, stores; it
+//                runs while the MMAs of the next tile fill the other accumulator.
+// Rows and columns beyond M, N and K are zero-filled by TMA and never stored.  With few rows
+// (one row tile and few column tiles) the k range is also split between CTAs: each writes its
+// share to scratch memory and the last to arrive (a counter per tile) adds them in split order.
 //
 // Every wait on an mbarrier is bounded: after HS_SPIN_LIMIT failed polls the thread sets
 // HS_STATUS_PIPELINE_TIMEOUT in the status word and leaves the loop; the kernel then runs to
@@ -164,35 +169,106 @@ struct TcSmem {
   static constexpr int B_BYTES = BN * TC_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;  // + alignment slack
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024;  // + alignment slack
 };
 
+constexpr int TC_THREADS = 384;       // warp 0 TMA, warp 1 MMA, warps 4..11 epilogue
+constexpr int TC_EPI_WARPS = 8;
+
+struct TcParams {
+  void* out;
+  const float* bias;
+  const float* residual;
+  float* partial;        // [splits][M][N] float32 (splits > 1)
+  int* counters;         // one per output tile, zero between launches (splits > 1)
+  int* status;
+  int M, N, K, act;
+  int tiles_m, tiles_n;
+  int splits, kb_per_split;   // k blocks (of 64) per split
+};
+
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// The activation of the bfloat16 tensor-core path: the hardware tanh (relative error 2^-11,
+// below bfloat16's 2^-9) for the tanh GELU; erff for the exact one.
+__device__ __forceinline__ float act_tc(float u, int act) {
+  if (act == HS_ACT_GELU_TANH) {
+    const float inner = 0.7978845608028654f * (u + 0.044715f * u * u * u);
+    return 0.5f * u * (1.0f + tanh_fast(inner));
+  }
+  if (act == HS_ACT_GELU_ERF) return gelu_erf(u);
+  return u;
+}
+__device__ __forceinline__ void epi_bar_sync() {   // the 8 epilogue warps only
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+}
+
+// Stores 32 consecutive columns of one row: v[j] final values.
+template <typename TO>
+__device__ __forceinline__ void store_row32(TO* out, size_t off, const float (&f)[32], int nvalid,
+                                            bool vec) {
+  if (vec && nvalid == 32) {
+    if constexpr (sizeof(TO) == 4) {
+      float4* o4 = (float4*)((float*)out + off);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        o4[j] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+    } else {
+      uint4* o4 = (uint4*)((__nv_bfloat16*)out + off);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(f[8 * j], f[8 * j + 1]);
+        __nv_bfloat162 p1 = __floats2bfloat162_rn(f[8 * j + 2], f[8 * j + 3]);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(f[8 * j + 4], f[8 * j + 5]);
+        __nv_bfloat162 p3 = __floats2bfloat162_rn(f[8 * j + 6], f[8 * j + 7]);
+        uint4 u;
+        u.x = *(uint32_t*)&p0; u.y = *(uint32_t*)&p1; u.z = *(uint32_t*)&p2; u.w = *(uint32_t*)&p3;
+        o4[j] = u;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < nvalid) out[off + j] = from_f<TO>(f[j]);
+  }
+}
+
+// Persistent: each CTA takes work items (output tile x k split) blockIdx.x, + gridDim.x, ...
+// Tiles are numbered with n fastest, so CTAs running together share the rows of `a`.
+// Two accumulators in TMEM: the epilogue of one work item overlaps the MMAs of the next.
 template <int BN, int STAGES, typename TO>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(TC_THREADS, 1)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
-                      const __grid_constant__ CUtensorMap map_w, TO* out,
-                      const float* __restrict__ bias, const float* residual, int M, int N, int K,
-                      int act, int* status) {
+                      const __grid_constant__ CUtensorMap map_w, const TcParams p) {
   using S = TcSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles need 1024-byte alignment
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full_bar = (uint64_t*)(smem + S::BAR_OFFSET);
   uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* accum_bar = empty_bar + STAGES;
-  uint32_t* tmem_slot = (uint32_t*)(accum_bar + 1);
+  uint64_t* acc_full = empty_bar + STAGES;       // [2] MMA -> epilogue
+  uint64_t* acc_empty = acc_full + 2;            // [2] epilogue -> MMA
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  __shared__ int s_last;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
-  const int num_kb = (K + TC_BK - 1) / TC_BK;
-  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;     // power of two >= 32
+  const int num_kb = (p.K + TC_BK - 1) / TC_BK;
+  const int n_items = p.tiles_m * p.tiles_n * p.splits;
+  constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;          // 64 .. 512, a power of two
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(accum_bar, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], TC_EPI_WARPS);
+    }
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -207,103 +283,188 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == 0) {
     if (lane == 0) {
       // ---------------- TMA producer
+      uint32_t it = 0;                          // k blocks issued so far (over all work items)
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t round = kb / STAGES;
-        if (round > 0) ok = mbar_wait(&empty_bar[s], (round - 1) & 1, status);
-        if (!ok) break;
-        uint8_t* a_dst = smem + s * S::STAGE_BYTES;
-        uint8_t* b_dst = a_dst + S::A_BYTES;
-        mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
-        tma_load_2d(a_dst, &map_a, &full_bar[s], kb * TC_BK, m0);
-        tma_load_2d(b_dst, &map_w, &full_bar[s], kb * TC_BK, n0);
+      for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+        const int tile = w / p.splits, split = w - tile * p.splits;
+        const int m0 = (tile / p.tiles_n) * TC_BM, n0 = (tile % p.tiles_n) * BN;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, num_kb);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t round = it / STAGES;
+          if (round > 0) ok = mbar_wait(&empty_bar[s], (round - 1) & 1, p.status);
+          if (!ok) break;
+          uint8_t* a_dst = smem + s * S::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + S::A_BYTES;
+          mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, &full_bar[s], kb * TC_BK, m0);
+          tma_load_2d(b_dst, &map_w, &full_bar[s], kb * TC_BK, n0);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // ---------------- MMA issuer
       constexpr uint32_t idesc = make_idesc(TC_BM, BN);
+      uint32_t it = 0, wi = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t round = kb / STAGES;
-        ok = mbar_wait(&full_bar[s], round & 1, status);
+      for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++wi) {
+        const int split = w % p.splits;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, num_kb);
+        const uint32_t acc = wi & 1, acc_round = wi >> 1;
+        if (acc_round > 0) ok = mbar_wait(&acc_empty[acc], (acc_round - 1) & 1, p.status);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
-        const uint32_t b_addr = a_addr + S::A_BYTES;
-        const uint64_t adesc = make_smem_desc(a_addr);
-        const uint64_t bdesc = make_smem_desc(b_addr);
+        const uint32_t tmem_d = tmem_base + acc * ACC_COLS;
+        for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t round = it / STAGES;
+          ok = mbar_wait(&full_bar[s], round & 1, p.status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + S::A_BYTES;
+          const uint64_t adesc = make_smem_desc(a_addr);
+          const uint64_t bdesc = make_smem_desc(b_addr);
 #pragma unroll
-        for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
-          // advance 16 elements = 32 bytes along K inside the swizzled row: +2 in 16-byte units
-          umma_bf16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
-                    (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
+            // advance 16 elements = 32 bytes along K inside the swizzled row: +2 in 16-byte units
+            umma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
+                      (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);     // the stage may be refilled once these MMAs are done
         }
-        umma_commit(&empty_bar[s]);     // the stage may be refilled once these MMAs are done
+        umma_commit(&acc_full[acc]);      // this accumulator is complete (or the pipeline gave up)
       }
-      umma_commit(accum_bar);           // the accumulator is complete (or the pipeline gave up)
     }
-  } else {
-    // ---------------- epilogue: 4 warps, warp (w % 4) owns TMEM lanes 32*(w%4) .. +31
-    const int q = warp & 3;
-    const bool ok = mbar_wait(accum_bar, 0, status);
-    tc_fence_after();
-    const int row = m0 + q * 32 + lane;
-    if (ok) {
+  } else if (warp >= 4) {
+    // ---------------- epilogue: 8 warps; warp (w % 4) owns TMEM lanes 32*(w%4) .. +31, the two
+    // groups of four take the two halves of the columns
+    const int q = warp & 3, half = (warp - 4) >> 2;
+    constexpr int HALF_COLS = BN / 2;
+    TO* out = (TO*)p.out;
+    const bool vec = (p.N % 8 == 0);
+    uint32_t wi = 0;
+    for (int w = blockIdx.x; w < n_items; w += gridDim.x, ++wi) {
+      const int tile = w / p.splits, split = w - tile * p.splits;
+      const int m0 = (tile / p.tiles_n) * TC_BM, n0 = (tile % p.tiles_n) * BN;
+      const uint32_t acc = wi & 1, acc_round = wi >> 1;
+      const bool ok = mbar_wait(&acc_full[acc], acc_round & 1, p.status);
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t t_addr = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
+      if (ok) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
-        tmem_ld_wait();
-        if (row < M) {
+        for (int c0 = half * HALF_COLS; c0 < (half + 1) * HALF_COLS; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(t_addr + (uint32_t)c0, v);
+          tmem_ld_wait();
           const int nbase = n0 + c0;
-          if (nbase + 32 <= N && (N % 8 == 0)) {
-            float f[32];
+          if (row >= p.M || nbase >= p.N) continue;
+          const int nvalid = min(32, p.N - nbase);
+          float f[32];
+          if (p.splits > 1) {
+            // raw partial sums to scratch; the last split to arrive finishes the tile below
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float x = __uint_as_float(v[j]);
-              if (bias) x += __ldg(bias + nbase + j);
-              f[j] = apply_act(x, act);
-            }
-            if (residual) {
-              const float4* r4 = (const float4*)(residual + (size_t)row * N + nbase);
+            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+            store_row32<float>(p.partial, ((size_t)split * p.M + row) * p.N + nbase, f, nvalid,
+                               p.N % 4 == 0);
+            continue;
+          }
+          if (p.bias != nullptr && nvalid == 32 && (p.N % 4 == 0)) {
+            const float4* b4 = (const float4*)(p.bias + nbase);
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 r = r4[j];
-                f[4 * j] += r.x; f[4 * j + 1] += r.y; f[4 * j + 2] += r.z; f[4 * j + 3] += r.w;
-              }
-            }
-            if constexpr (sizeof(TO) == 4) {
-              float4* o4 = (float4*)((float*)out + (size_t)row * N + nbase);
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                o4[j] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
-            } else {
-              uint4* o4 = (uint4*)((__nv_bfloat16*)out + (size_t)row * N + nbase);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                __nv_bfloat162 p0 = __floats2bfloat162_rn(f[8 * j], f[8 * j + 1]);
-                __nv_bfloat162 p1 = __floats2bfloat162_rn(f[8 * j + 2], f[8 * j + 3]);
-                __nv_bfloat162 p2 = __floats2bfloat162_rn(f[8 * j + 4], f[8 * j + 5]);
-                __nv_bfloat162 p3 = __floats2bfloat162_rn(f[8 * j + 6], f[8 * j + 7]);
-                uint4 u;
-                u.x = *(uint32_t*)&p0; u.y = *(uint32_t*)&p1; u.z = *(uint32_t*)&p2; u.w = *(uint32_t*)&p3;
-                o4[j] = u;
-              }
+            for (int j = 0; j < 8; ++j) {
+              const float4 b = __ldg(b4 + j);
+              f[4 * j] = __uint_as_float(v[4 * j]) + b.x;
+              f[4 * j + 1] = __uint_as_float(v[4 * j + 1]) + b.y;
+              f[4 * j + 2] = __uint_as_float(v[4 * j + 2]) + b.z;
+              f[4 * j + 3] = __uint_as_float(v[4 * j + 3]) + b.w;
             }
           } else {
-            for (int j = 0; j < 32; ++j) {
-              const int n = nbase + j;
-              if (n >= N) break;
-              float x = __uint_as_float(v[j]);
-              if (bias) x += bias[n];
-              x = apply_act(x, act);
-              if (residual) x += residual[(size_t)row * N + n];
-              out[(size_t)row * N + n] = from_f<TO>(x);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              f[j] = __uint_as_float(v[j]) + ((p.bias && j < nvalid) ? p.bias[nbase + j] : 0.f);
+          }
+          if (p.act != HS_ACT_NONE) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], p.act);
+          }
+          const size_t off = (size_t)row * p.N + nbase;
+          if (p.residual) {
+            if (nvalid == 32 && (p.N % 4 == 0)) {
+              const float4* r4 = (const float4*)(p.residual + off);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 r = r4[j];
+                f[4 * j] += r.x; f[4 * j + 1] += r.y; f[4 * j + 2] += r.z; f[4 * j + 3] += r.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < nvalid) f[j] += p.residual[off + j];
             }
           }
+          store_row32<TO>(out, off, f, nvalid, vec);
+        }
+      }
+      // the accumulator may be overwritten by the MMAs of the work item after next
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+
+      if (p.splits > 1) {
+        // ---- the last split of this tile to arrive adds the shares in split order
+        __threadfence();
+        epi_bar_sync();
+        if (threadIdx.x == 4 * 32) s_last = atomicAdd(&p.counters[tile], 1) == p.splits - 1;
+        epi_bar_sync();
+        if (s_last) {
+          __threadfence();
+          // 256 threads sweep the tile in float4 pieces, rows of the tile x BN/4 pieces a row;
+          // the loads of all shares of a piece are issued together, then added in split order
+          const int et = threadIdx.x - 4 * 32;                   // 0..255
+          constexpr int PIECES = BN / 4;
+          const int rows_here = min(TC_BM, p.M - m0);
+          const bool vec4 = (p.N % 4 == 0);
+          for (int e = et; e < rows_here * PIECES; e += TC_EPI_WARPS * 32) {
+            const int r = e / PIECES, c = (e % PIECES) * 4;
+            const int n = n0 + c;
+            if (n >= p.N) continue;
+            const size_t off = (size_t)(m0 + r) * p.N + n;
+            float4 acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (vec4) {
+              float4 sh[16];
+#pragma unroll
+              for (int sp = 0; sp < 16; ++sp)
+                if (sp < p.splits)
+                  sh[sp] = __ldcg((const float4*)(p.partial + (size_t)sp * p.M * p.N + off));
+#pragma unroll
+              for (int sp = 0; sp < 16; ++sp)
+                if (sp < p.splits) {
+                  acc4.x += sh[sp].x; acc4.y += sh[sp].y; acc4.z += sh[sp].z; acc4.w += sh[sp].w;
+                }
+            } else {
+              float* a = (float*)&acc4;
+              for (int sp = 0; sp < p.splits; ++sp)
+                for (int j = 0; j < 4; ++j)
+                  if (n + j < p.N) a[j] += __ldcg(p.partial + (size_t)sp * p.M * p.N + off + j);
+            }
+            float vals[4] = {acc4.x, acc4.y, acc4.z, acc4.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (n + j < p.N) {
+                float x = vals[j] + (p.bias ? p.bias[n + j] : 0.f);
+                x = act_tc(x, p.act);
+                if (p.residual) x += p.residual[off + j];
+                out[off + j] = from_f<TO>(x);
+              }
+            }
+          }
+          epi_bar_sync();
+          if (threadIdx.x == 4 * 32) p.counters[tile] = 0;       // ready for the next launch
         }
       }
     }
@@ -352,8 +513,7 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
 }
 
 template <int BN, int STAGES, typename TO>
-static int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, const float* bias,
-                  const float* residual, int M, int N, int K, int act, int* status,
+static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const TcParams& p, int grid,
                   cudaStream_t st) {
   auto kern = linear_tcgen05_kernel<BN, STAGES, TO>;
   constexpr int smem = TcSmem<BN, STAGES>::TOTAL;
@@ -363,37 +523,25 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, const
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
-  kern<<<grid, 192, smem, st>>>(ma, mw, (TO*)out, bias, residual, M, N, K, act, status);
+  kern<<<grid, TC_THREADS, smem, st>>>(ma, mw, p);
   HS_LAUNCH_CHECK();
   return HS_OK;
 }
 
-}  // namespace hs
+struct TcPlan {
+  int bn, splits, kb_per_split, tiles_m, tiles_n, grid;
+};
 
-// Returns HS_ERR_UNSUPPORTED for shapes the TMA path cannot take (K not a multiple of 8:
-// row strides must be multiples of 16 bytes; pointers not 16-byte aligned); the caller falls
-// back to the CUDA-core kernel.
-HS_EXPORT int hs_linear_tcgen05(void* out, const void* a, const void* w, const float* bias,
-                                const float* residual, int M, int N, int K, int act,
-                                int out_dtype, int tile_n, int* status, void* stream) {
-  using namespace hs;
-  if (!out || !a || !w || !status) return HS_ERR_ARGUMENT;
-  if (M <= 0 || N <= 0) return HS_OK;
-  if (K <= 0) return HS_ERR_ARGUMENT;
-  if (K % 8 != 0) return HS_ERR_UNSUPPORTED;
-  if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15)) return HS_ERR_UNSUPPORTED;
-  if (residual && ((uintptr_t)residual & 15)) return HS_ERR_UNSUPPORTED;
-  if (act < HS_ACT_NONE || act > HS_ACT_GELU_ERF) return HS_ERR_UNSUPPORTED;
-  if ((M + TC_BM - 1) / TC_BM > 65535) return HS_ERR_UNSUPPORTED;
+static bool plan_tc(int M, int N, int K, int tile_n, TcPlan& pl) {
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+  const int mt = (M + TC_BM - 1) / TC_BM;
+  const int num_kb = (K + TC_BK - 1) / TC_BK;
   int bn = tile_n;
   if (bn == 0) {
     // A tile's time grows with the bytes it loads per k-block (128 + width rows) plus a fixed
-    // part; pick the width for which waves x that is smallest.
-    int sms = 148;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    // part; pick the width for which rounds over the SMs x that is smallest.
     long best = -1;
-    const int mt = (M + TC_BM - 1) / TC_BM;
     for (int cand : {256, 128, 64}) {
       if (cand > 64 && cand / 2 >= N) continue;
       const long tiles = (long)mt * ((N + cand - 1) / cand);
@@ -403,22 +551,79 @@ HS_EXPORT int hs_linear_tcgen05(void* out, const void* a, const void* w, const f
         bn = cand;
       }
     }
+    if (mt == 1) bn = 64;     // few rows: narrow tiles (more CTAs stream the weights) and splits
   }
+  if (bn != 64 && bn != 128 && bn != 256) return false;
+  pl.bn = bn;
+  pl.tiles_m = mt;
+  pl.tiles_n = (N + bn - 1) / bn;
+  const int tiles = pl.tiles_m * pl.tiles_n;
+  // splits over k only while the tiles alone leave most SMs idle (few rows), each split at
+  // least 2 k blocks deep
+  int splits = 1;
+  if (tiles * 2 <= sms) {
+    splits = sms / tiles;
+    if (splits > num_kb / 2) splits = num_kb / 2;
+    if (splits < 1) splits = 1;
+    if (splits > 16) splits = 16;
+  }
+  pl.kb_per_split = (num_kb + splits - 1) / splits;
+  pl.splits = (num_kb + pl.kb_per_split - 1) / pl.kb_per_split;
+  const int items = tiles * pl.splits;
+  pl.grid = items < sms ? items : sms;
+  return true;
+}
+
+}  // namespace hs
+
+// Scratch a launch needs when it is split over k: floats for the shares, ints for the counters
+// (both zero when it is not split).
+HS_EXPORT int hs_linear_tcgen05_scratch(int M, int N, int K, int tile_n, long long* floats,
+                                        int* counters) {
+  hs::TcPlan pl;
+  if (M <= 0 || N <= 0 || K <= 0 || !hs::plan_tc(M, N, K, tile_n, pl)) return HS_ERR_UNSUPPORTED;
+  *floats = pl.splits > 1 ? (long long)pl.splits * M * N : 0;
+  *counters = pl.splits > 1 ? pl.tiles_m * pl.tiles_n : 0;
+  return HS_OK;
+}
+
+// Returns HS_ERR_UNSUPPORTED for shapes the TMA path cannot take (K not a multiple of 8:
+// row strides must be multiples of 16 bytes; pointers not 16-byte aligned); the caller falls
+// back to the CUDA-core kernel.
+HS_EXPORT int hs_linear_tcgen05(void* out, const void* a, const void* w, const float* bias,
+                                const float* residual, int M, int N, int K, int act,
+                                int out_dtype, int tile_n, float* scratch, int* counters,
+                                int* status, void* stream) {
+  using namespace hs;
+  if (!out || !a || !w || !status) return HS_ERR_ARGUMENT;
+  if (M <= 0 || N <= 0) return HS_OK;
+  if (K <= 0) return HS_ERR_ARGUMENT;
+  if (K % 8 != 0) return HS_ERR_UNSUPPORTED;
+  if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15)) return HS_ERR_UNSUPPORTED;
+  if (residual && ((uintptr_t)residual & 15)) return HS_ERR_UNSUPPORTED;
+  if (bias && ((uintptr_t)bias & 15)) return HS_ERR_UNSUPPORTED;
+  if (act < HS_ACT_NONE || act > HS_ACT_GELU_ERF) return HS_ERR_UNSUPPORTED;
+  if (out_dtype != HS_DT_F32 && out_dtype != HS_DT_BF16) return HS_ERR_UNSUPPORTED;
+  TcPlan pl;
+  if (!plan_tc(M, N, K, tile_n, pl)) return HS_ERR_UNSUPPORTED;
+  if (pl.splits > 1 && (!scratch || !counters)) return HS_ERR_ARGUMENT;
   CUtensorMap ma, mw;
   if (int e = make_map(&ma, a, M, K, TC_BM)) return e;
-  if (int e = make_map(&mw, w, N, K, bn)) return e;
+  if (int e = make_map(&mw, w, N, K, pl.bn)) return e;
+  TcParams p;
+  p.out = out; p.bias = bias; p.residual = residual; p.partial = scratch; p.counters = counters;
+  p.status = status; p.M = M; p.N = N; p.K = K; p.act = act;
+  p.tiles_m = pl.tiles_m; p.tiles_n = pl.tiles_n; p.splits = pl.splits;
+  p.kb_per_split = pl.kb_per_split;
   cudaStream_t st = (cudaStream_t)stream;
   using bf16 = __nv_bfloat16;
-#define HS_TC(BN, ST)                                                                          \
-  (out_dtype == HS_DT_F32                                                                      \
-       ? launch<BN, ST, float>(ma, mw, out, bias, residual, M, N, K, act, status, st)          \
-       : launch<BN, ST, bf16>(ma, mw, out, bias, residual, M, N, K, act, status, st))
-  if (out_dtype != HS_DT_F32 && out_dtype != HS_DT_BF16) return HS_ERR_UNSUPPORTED;
-  switch (bn) {
+#define HS_TC(BN, ST)                                                        \
+  (out_dtype == HS_DT_F32 ? launch<BN, ST, float>(ma, mw, p, pl.grid, st)    \
+                          : launch<BN, ST, bf16>(ma, mw, p, pl.grid, st))
+  switch (pl.bn) {
     case 256: return HS_TC(256, 4);
     case 128: return HS_TC(128, 6);
-    case 64: return HS_TC(64, 8);
-    default: return HS_ERR_UNSUPPORTED;
+    default: return HS_TC(64, 8);
   }
 #undef HS_TC
 }

@@ -115,6 +115,70 @@ def test_linear(ops, plain, M, N, K, dtype, act):
     assert (acc.double() - ref).abs().max() < (2e-5 if dtype == torch.float32 else 2e-3 * K ** 0.5)
 
 
+TC_SHAPES = [(1, 1000, 96), (5, 50257, 64), (16, 192, 320), (17, 1024, 1024), (40, 288, 96),
+             (64, 1024, 4096), (100, 3072, 1024), (128, 64, 64), (129, 257, 520), (300, 1000, 1600)]
+
+
+@pytest.mark.parametrize("M,N,K", TC_SHAPES)
+@pytest.mark.parametrize("path", ["few_rows", "tcgen05"])
+def test_bfloat16_linear_kernels_each_on_its_own(ops, plain, M, N, K, path):
+    """The weight-streaming kernel (up to 64 rows, k a multiple of 32) and the tcgen05 kernel
+    (any rows; few rows take its split over k) forced one at a time, all epilogues."""
+    if path == "few_rows" and (M > 64 or K % 32):
+        pytest.skip("the few-row kernel takes up to 64 rows and k in multiples of 32")
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(N, K, device=DEV) / K ** 0.5).bfloat16()
+    bias = torch.randn(N, device=DEV)
+    saved = ops.skinny_max_rows
+    ops.skinny_max_rows = 64 if path == "few_rows" else 0
+    try:
+        for act, out_dtype, with_res in (("none", torch.bfloat16, False), ("gelu_tanh", torch.bfloat16, False),
+                                         ("gelu_erf", torch.bfloat16, False), ("none", torch.float32, False),
+                                         ("none", torch.float32, True)):
+            ref = torch.empty(M, N, device=DEV, dtype=torch.float64)
+            if with_res:
+                res = torch.randn(M, N, device=DEV)
+                out = res.clone()
+                ops.linear(out, a, w, bias, act=act, residual=out)
+                plain.linear(ref, a, w, bias, act=act, residual=res)
+            else:
+                out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
+                ops.linear(out, a, w, bias, act=act)
+                plain.linear(ref, a, w, bias, act=act)
+            tol = 3e-2 if out_dtype == torch.bfloat16 else 2e-3      # hardware tanh: 2^-11
+            assert (out.double() - ref).abs().max() < tol, (act, out_dtype, with_res)
+            # launched twice: scratch and counters of a split launch are left ready
+            if with_res:
+                out2 = res.clone()
+                ops.linear(out2, a, w, bias, act=act, residual=out2)
+                assert torch.equal(out, out2)
+        assert ops.status.item() == 0
+    finally:
+        ops.skinny_max_rows = saved
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 192, 64), (8, 3072, 1024), (16, 4096, 1024), (5, 288, 96),
+                                   (16, 4800, 1600), (9, 1024, 4096), (30, 320, 2048),
+                                   (200, 1000, 96)])
+def test_layernorm_fused_into_the_linear(ops, plain, M, N, K):
+    torch.manual_seed(M * K + N)
+    x = torch.randn(M, K, device=DEV) * 4 + 2
+    g, b = torch.randn(K, device=DEV), torch.randn(K, device=DEV)
+    w = (torch.randn(N, K, device=DEV) / K ** 0.5).bfloat16()
+    bias = torch.randn(N, device=DEV)
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    h = torch.empty(M, K, device=DEV, dtype=torch.bfloat16)
+    ref = torch.empty(M, N, device=DEV, dtype=torch.float64)
+    href = torch.empty(M, K, device=DEV, dtype=torch.bfloat16)
+    before = ops.launches
+    ops.norm_linear(out, h, x, g, b, 1e-6, w, bias, act="gelu_tanh")
+    fused = ops.launches - before == 1
+    assert fused == (M <= ops.skinny_max_rows and K % 32 == 0)
+    plain.norm_linear(ref, href, x, g, b, 1e-6, w, bias, act="gelu_tanh")
+    assert (out.double() - ref).abs().max() < 3e-2
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_linear_rows_do_not_depend_on_the_batch(ops, dtype):
     torch.manual_seed(5)
