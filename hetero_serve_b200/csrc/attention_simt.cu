@@ -48,6 +48,17 @@ __global__ void kv_append_kernel(T* __restrict__ pool, const T* __restrict__ qkv
   const T* src = qkv + (size_t)t * g.qkv_stride;
   T* pk = pool + (size_t)page * 2 * g.n_kv_heads * tile;
   T* pv = pk + (size_t)g.n_kv_heads * tile;
+  // 16 bytes at a time (head sizes are multiples of 16 elements) when the columns are aligned
+  constexpr int VEC = 16 / sizeof(T);
+  if ((g.k_off % VEC == 0) && (g.v_off % VEC == 0) && (g.qkv_stride % VEC == 0)) {
+    for (int e = threadIdx.x * VEC; e < kvw; e += blockDim.x * VEC) {
+      const int hk = e / g.head_dim, d = e - hk * g.head_dim;
+      const size_t dst = (size_t)hk * tile + (size_t)slot * g.head_dim + d;
+      *(uint4*)(pk + dst) = *(const uint4*)(src + g.k_off + e);
+      *(uint4*)(pv + dst) = *(const uint4*)(src + g.v_off + e);
+    }
+    return;
+  }
   for (int e = threadIdx.x; e < kvw; e += blockDim.x) {
     const int hk = e / g.head_dim, d = e - hk * g.head_dim;
     const size_t dst = (size_t)hk * tile + (size_t)slot * g.head_dim + d;
@@ -164,7 +175,7 @@ HS_EXPORT int hs_kv_append(void* pool, const void* qkv, const int* table, const 
   if (int e = check_geom(g)) return e;
   if (n_tokens <= 0) return HS_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  int threads = n_kv_heads * head_dim >= 256 ? 256 : 128;
+  int threads = n_kv_heads * head_dim >= 1024 ? 128 : 64;
   if (dtype == HS_DT_F32)
     hs::kv_append_kernel<float><<<n_tokens, threads, 0, st>>>(
         (float*)pool, (const float*)qkv, table, tok_pos, tok_req, g, status);

@@ -91,6 +91,61 @@ __global__ void layernorm_kernel(TO* __restrict__ out, const float* __restrict__
     orow[e] = from_f<TO>((srow[e] - mu) * rstd * gamma[e] + beta[e]);
 }
 
+// One warp per row, the row held in registers (up to 32 * 4 * LN_F4 floats): no shared memory,
+// no block barrier.  The mean and the centred variance are two warp reductions (a fixed
+// butterfly), so a row's result does not depend on the batch here either.
+constexpr int LN_F4 = 16;           // rows of up to 2048 floats
+constexpr int LN_ROWS_PER_CTA = 8;
+
+template <typename TO>
+__global__ void __launch_bounds__(LN_ROWS_PER_CTA * 32)
+layernorm_warp_kernel(TO* __restrict__ out, const float* __restrict__ x,
+                      const float* __restrict__ gamma, const float* __restrict__ beta,
+                      const int* __restrict__ rows, int n_rows, int width, float eps) {
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int o = blockIdx.x * LN_ROWS_PER_CTA + warp;
+  if (o >= n_rows) return;
+  const int src = rows ? rows[o] : o;
+  const float4* xr = (const float4*)(x + (size_t)src * width);
+  const int nf4 = width / 4;
+  float4 v[LN_F4];
+#pragma unroll
+  for (int i = 0; i < LN_F4; ++i)
+    v[i] = (lane + 32 * i < nf4) ? xr[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < LN_F4; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  const float mu = warp_sum(s) / (float)width;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < LN_F4; ++i) {
+    if (lane + 32 * i < nf4) {
+      const float c0 = v[i].x - mu, c1 = v[i].y - mu, c2 = v[i].z - mu, c3 = v[i].w - mu;
+      q += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+    }
+  }
+  const float rstd = 1.0f / sqrtf(warp_sum(q) / (float)width + eps);
+  TO* orow = out + (size_t)o * width;
+#pragma unroll
+  for (int i = 0; i < LN_F4; ++i) {
+    const int e = (lane + 32 * i) * 4;
+    if (lane + 32 * i < nf4) {
+      const float4 g = *(const float4*)(gamma + e), b = *(const float4*)(beta + e);
+      const float y0 = (v[i].x - mu) * rstd * g.x + b.x, y1 = (v[i].y - mu) * rstd * g.y + b.y;
+      const float y2 = (v[i].z - mu) * rstd * g.z + b.z, y3 = (v[i].w - mu) * rstd * g.w + b.w;
+      if constexpr (sizeof(TO) == 4) {
+        *(float4*)((float*)orow + e) = make_float4(y0, y1, y2, y3);
+      } else {
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(y0, y1), p1 = __floats2bfloat162_rn(y2, y3);
+        uint2 u;
+        u.x = *(uint32_t*)&p0; u.y = *(uint32_t*)&p1;
+        *(uint2*)((__nv_bfloat16*)orow + e) = u;
+      }
+    }
+  }
+}
+
 }  // namespace hs
 
 HS_EXPORT int hs_embed(float* x, const int* ids, const int* pos, const int* req, const void* wte,
@@ -118,6 +173,22 @@ HS_EXPORT int hs_layernorm(void* out, const float* x, const float* gamma, const 
                            void* stream) {
   if (!out || !x || !gamma || !beta) return HS_ERR_ARGUMENT;
   if (n_rows <= 0) return HS_OK;
+  cudaStream_t st0 = (cudaStream_t)stream;
+  // rows of up to 2048 floats (a multiple of 4, 16-byte aligned): one warp per row
+  if (width % 4 == 0 && width <= hs::LN_F4 * 128 && !((uintptr_t)x & 15) && !((uintptr_t)out & 15) &&
+      !((uintptr_t)gamma & 15) && !((uintptr_t)beta & 15)) {
+    const int grid = (n_rows + hs::LN_ROWS_PER_CTA - 1) / hs::LN_ROWS_PER_CTA;
+    if (out_dtype == HS_DT_F32)
+      hs::layernorm_warp_kernel<float><<<grid, hs::LN_ROWS_PER_CTA * 32, 0, st0>>>(
+          (float*)out, x, gamma, beta, rows, n_rows, width, eps);
+    else if (out_dtype == HS_DT_BF16)
+      hs::layernorm_warp_kernel<__nv_bfloat16><<<grid, hs::LN_ROWS_PER_CTA * 32, 0, st0>>>(
+          (__nv_bfloat16*)out, x, gamma, beta, rows, n_rows, width, eps);
+    else
+      return HS_ERR_UNSUPPORTED;
+    HS_LAUNCH_CHECK();
+    return HS_OK;
+  }
   constexpr int THREADS = 256;
   size_t smem = (size_t)width * sizeof(float);
   if (smem > 200 * 1024) return HS_ERR_UNSUPPORTED;  // a row must fit shared memory
