@@ -5,10 +5,13 @@
 // scalar one (heteroserve/model/paged_attn_prefill.py:72-157: query s of a portion sits at
 // absolute position ctx_len - S + s and sees keys 0..that position; the mask is the loop bound).
 //
-// One CTA = 64 consecutive queries of one request x one head, 4 warps of 16 queries.  Keys and
+// A work item = up to 64 consecutive queries of one request x one head, 4 warps of 16 queries.
+// CTAs are persistent: each takes the next item from a counter in device memory, and the host
+// lists the items with the most keys first, so the causal triangle's uneven tiles spread evenly
+// over the SMs.  Keys and
 // values are taken 64 positions at a time: each 16-position block of a tile lies inside one page
 // (page sizes are multiples of 16), is found through the block table and copied to shared memory
-// with cp.async (two tiles in flight).  S = Q K^T and O += P V run on mma.sync m16n8k16
+// with cp.async (a ring of three tiles: two in flight while one is used).  S = Q K^T and O += P V run on mma.sync m16n8k16
 // (bf16 in, f32 accumulate), fragments fetched with ldmatrix from XOR-swizzled tiles; the scores
 // are multiplied by `scale` after the dot product (heteroserve/model/torch_engine.py:135); the
 // running maximum, the running sum and O are float32 (online softmax).  The new tokens' own keys
@@ -22,7 +25,7 @@
 
 namespace hs {
 
-constexpr int AP_BQ = 64, AP_BKV = 64, AP_WARPS = 4;
+constexpr int AP_BQ = 64, AP_BKV = 64, AP_WARPS = 4, AP_STAGES = 3;
 
 struct PrefillParams {
   const __nv_bfloat16* qkv;
@@ -34,8 +37,10 @@ struct PrefillParams {
   const int* tile_info;    // per tile: first query's flat index, queries, request row, first position
   const int* plan_head;
   int* status;
+  int* work_counter;       // next work item; zero at launch
   int n_heads, n_kv_heads, page_size, num_pages, max_pages;
   int q_off, qkv_stride;
+  int ps_log2;             // log2(page_size) when it is a power of two, else -1
   float scale;
 };
 
@@ -82,28 +87,34 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(AP_WARPS * 32)
+__global__ void __launch_bounds__(AP_WARPS * 32, (D <= 64 ? 4 : 2))
 attention_prefill_kernel(const PrefillParams p) {
   constexpr int CPR = D / 8;
   constexpr int KSTEPS = D / 16;       // k-steps of Q K^T
   constexpr int DT = D / 8;            // n-tiles of the output
   extern __shared__ __align__(128) uint8_t smem_raw[];
   uint4* sQ = (uint4*)smem_raw;                          // [64][CPR]
-  uint4* sK = sQ + AP_BQ * CPR;                          // [2][64][CPR]
-  uint4* sV = sK + 2 * AP_BKV * CPR;                     // [2][64][CPR]
+  uint4* sK = sQ + AP_BQ * CPR;                          // [AP_STAGES][64][CPR]
+  uint4* sV = sK + AP_STAGES * AP_BKV * CPR;             // [AP_STAGES][64][CPR]
 
-  const int tile = blockIdx.x, h = blockIdx.y;
-  const int n_tiles_served = p.plan_head[1];
-  const int4 ti = *(const int4*)(p.tile_info + 4 * tile);
-  if (tile >= n_tiles_served) return;
-  const int tok0 = ti.x, nq = ti.y, r = ti.z, pos0 = ti.w;
+  __shared__ int s_item;
+  const int n_items = p.plan_head[1] * p.n_heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  if (r < 0 || nq <= 0 || pos0 < 0) return;
+  while (true) {
+  __syncthreads();            // the previous item's shared memory has been consumed
+  if (threadIdx.x == 0) s_item = atomicAdd(p.work_counter, 1);
+  __syncthreads();
+  const int item = s_item;
+  if (item >= n_items) break;
+  const int tile = item / p.n_heads, h = item - tile * p.n_heads;
+  const int4 ti = *(const int4*)(p.tile_info + 4 * tile);
+  const int tok0 = ti.x, nq = ti.y, r = ti.z, pos0 = ti.w;
+  if (r < 0 || nq <= 0 || pos0 < 0) continue;
   const int pos_last = pos0 + nq - 1;
   if (pos_last / p.page_size >= p.max_pages) {
     if (threadIdx.x == 0) atomicOr(p.status, HS_STATUS_BAD_POSITION);
-    return;
+    continue;
   }
   const int hk = h / (p.n_heads / p.n_kv_heads);
   const int PS = p.page_size;
@@ -132,8 +143,11 @@ attention_prefill_kernel(const PrefillParams p) {
       const int dst = swz<D>(row, ch);
       bool ok = j <= pos_last;
       int page = 0;
+      int slot_in_page = 0;
       if (ok) {
-        page = trow[j / PS];
+        const int pg = p.ps_log2 >= 0 ? (j >> p.ps_log2) : (j / PS);
+        slot_in_page = j - pg * PS;
+        page = trow[pg];
         if (page < 0 || page >= p.num_pages) {
           atomicOr(p.status, HS_STATUS_BAD_PAGE);
           ok = false;
@@ -141,7 +155,7 @@ attention_prefill_kernel(const PrefillParams p) {
       }
       if (ok) {
         const __nv_bfloat16* kp = p.pool + (size_t)page * page_stride + (size_t)hk * ptile +
-                                  (size_t)(j % PS) * D + ch * 8;
+                                  (size_t)slot_in_page * D + ch * 8;
         cp_async16(&dK[dst], kp);
         cp_async16(&dV[dst], kp + (size_t)p.n_kv_heads * ptile);
       } else {
@@ -151,8 +165,12 @@ attention_prefill_kernel(const PrefillParams p) {
     }
   };
 
-  load_tile(0, 0);
-  cp_async_commit();
+  // tiles 0 .. AP_STAGES-2 are requested up front; one commit group per tile (empty ones too)
+#pragma unroll
+  for (int st = 0; st < AP_STAGES - 1; ++st) {
+    if (st < n_tiles) load_tile(st, st);
+    cp_async_commit();
+  }
   __syncthreads();          // Q is in shared memory
 
   // ---- Q fragments stay in registers
@@ -167,14 +185,18 @@ attention_prefill_kernel(const PrefillParams p) {
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
   const int row_a = warp * 16 + g, row_b = row_a + 8;
   const int pos_a = min(pos0 + row_a, pos_last), pos_b = min(pos0 + row_b, pos_last);
-  const int warp_last = min(pos0 + warp * 16 + 15, pos_last);
+  // last position any query of this warp sees; a warp whose rows are all past nq sees nothing
+  const int warp_last = (warp * 16 < nq) ? min(pos0 + warp * 16 + 15, pos_last) : -1;
+  const int warp_first = pos0 + warp * 16;               // position of the warp's first query
+  const float sl2 = p.scale * 1.4426950408889634f;       // scores in units of log2(e)
 
   for (int kt = 0; kt < n_tiles; ++kt) {
-    const int stage = kt & 1;
-    if (kt + 1 < n_tiles) load_tile(kt + 1, stage ^ 1);
+    const int stage = kt % AP_STAGES;
+    cp_async_wait<AP_STAGES - 2>();     // tile kt has landed (for this thread's copies)
+    __syncthreads();                    // ... for everyone's; and tile kt-1 has been consumed
+    if (kt + AP_STAGES - 1 < n_tiles)
+      load_tile(kt + AP_STAGES - 1, (kt + AP_STAGES - 1) % AP_STAGES);
     cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
     if (kt * AP_BKV <= warp_last) {
       const uint4* tK = sK + stage * AP_BKV * CPR;
       const uint4* tV = sV + stage * AP_BKV * CPR;
@@ -193,15 +215,19 @@ attention_prefill_kernel(const PrefillParams p) {
           mma_bf16(s[np * 2 + 1], qf[ks], b[2], b[3]);
         }
       }
-      // scale, mask, running maximum
+      // scale (folded into the exponent: p = 2^(s * scale * log2 e - m)), mask, running maximum.
+      // Only tiles that reach past the warp's first query need the mask.
+      const bool diagonal = kt * AP_BKV + AP_BKV - 1 > warp_first;
       float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
-        const int j = kt * AP_BKV + nt * 8 + t * 2;
-        s[nt][0] = (j <= pos_a) ? s[nt][0] * p.scale : -INFINITY;
-        s[nt][1] = (j + 1 <= pos_a) ? s[nt][1] * p.scale : -INFINITY;
-        s[nt][2] = (j <= pos_b) ? s[nt][2] * p.scale : -INFINITY;
-        s[nt][3] = (j + 1 <= pos_b) ? s[nt][3] * p.scale : -INFINITY;
+        if (diagonal) {
+          const int j = kt * AP_BKV + nt * 8 + t * 2;
+          if (j > pos_a) s[nt][0] = -INFINITY;
+          if (j + 1 > pos_a) s[nt][1] = -INFINITY;
+          if (j > pos_b) s[nt][2] = -INFINITY;
+          if (j + 1 > pos_b) s[nt][3] = -INFINITY;
+        }
         mx_a = fmaxf(mx_a, fmaxf(s[nt][0], s[nt][1]));
         mx_b = fmaxf(mx_b, fmaxf(s[nt][2], s[nt][3]));
       }
@@ -209,20 +235,21 @@ attention_prefill_kernel(const PrefillParams p) {
       mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
       mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
       mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-      const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+      // running maxima are kept in scaled units (m = max(s) * sl2; the scale is positive)
+      const float mn_a = fmaxf(m_a, mx_a * sl2), mn_b = fmaxf(m_b, mx_b * sl2);
       // a row whose keys of this tile are all masked keeps its state (mn == m); a row with
       // no key at all yet (mn == -inf) contributes zeros
-      const float ca = (mn_a == -INFINITY) ? 1.f : __expf(m_a - mn_a);
-      const float cb = (mn_b == -INFINITY) ? 1.f : __expf(m_b - mn_b);
+      const float ca = (mn_a == -INFINITY) ? 1.f : exp2f(m_a - mn_a);
+      const float cb = (mn_b == -INFINITY) ? 1.f : exp2f(m_b - mn_b);
       const float base_a = (mn_a == -INFINITY) ? 0.f : mn_a;
       const float base_b = (mn_b == -INFINITY) ? 0.f : mn_b;
       float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
-        s[nt][0] = __expf(s[nt][0] - base_a);
-        s[nt][1] = __expf(s[nt][1] - base_a);
-        s[nt][2] = __expf(s[nt][2] - base_b);
-        s[nt][3] = __expf(s[nt][3] - base_b);
+        s[nt][0] = exp2f(fmaf(s[nt][0], sl2, -base_a));
+        s[nt][1] = exp2f(fmaf(s[nt][1], sl2, -base_a));
+        s[nt][2] = exp2f(fmaf(s[nt][2], sl2, -base_b));
+        s[nt][3] = exp2f(fmaf(s[nt][3], sl2, -base_b));
         sum_a += s[nt][0] + s[nt][1];
         sum_b += s[nt][2] + s[nt][3];
       }
@@ -253,7 +280,6 @@ attention_prefill_kernel(const PrefillParams p) {
         }
       }
     }
-    __syncthreads();         // the stage may be overwritten by the next prefetch
   }
   cp_async_wait<0>();
   // ---- finish: the per-thread sums cover 2 of a row's 8 columns per tile; add the quad
@@ -270,20 +296,31 @@ attention_prefill_kernel(const PrefillParams p) {
     if (row_a < nq) *(uint32_t*)(oa + d) = pack_bf16(o[i][0] * ia, o[i][1] * ia);
     if (row_b < nq) *(uint32_t*)(ob + d) = pack_bf16(o[i][2] * ib, o[i][3] * ib);
   }
+  }   // next work item
 }
 
 template <int D>
-static int launch_prefill(const PrefillParams& p, int tile_cap, cudaStream_t st) {
+static int launch_prefill(const PrefillParams& p, cudaStream_t st) {
   auto kern = attention_prefill_kernel<D>;
-  constexpr int smem = (AP_BQ + 4 * AP_BKV) * D * 2;
-  static bool configured = false;
-  if (!configured && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  constexpr int smem = (AP_BQ + 2 * AP_STAGES * AP_BKV) * D * 2;
+  static int ctas = 0;                 // persistent CTAs: as many as are resident at once
+  if (ctas == 0) {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    int per_sm = 0, sms = 148;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, AP_WARPS * 32,
+                                                                  smem);
     if (e != cudaSuccess) return (int)e;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    if (per_sm < 1) per_sm = 1;
+    if (per_sm > 3) per_sm = 3;        // three per SM leave items over to be handed out late
+    ctas = per_sm * sms;
   }
-  configured = true;
-  dim3 grid(tile_cap, p.n_heads);
-  kern<<<grid, AP_WARPS * 32, smem, st>>>(p);
+  cudaError_t e = cudaMemsetAsync(p.work_counter, 0, sizeof(int), st);
+  if (e != cudaSuccess) return (int)e;
+  kern<<<ctas, AP_WARPS * 32, smem, st>>>(p);
   HS_LAUNCH_CHECK();
   return HS_OK;
 }
@@ -293,31 +330,34 @@ static int launch_prefill(const PrefillParams& p, int tile_cap, cudaStream_t st)
 HS_EXPORT int hs_attention_prefill(void* out, const void* qkv, const void* pool, const int* table,
                                    const int* tok_pos, const int* tok_req, const int* tile_info,
                                    const int* plan_head, int tile_cap,
-                                   int n_heads, int n_kv_heads, int head_dim, int page_size,
+                                   int* work_counter, int n_heads, int n_kv_heads, int head_dim, int page_size,
                                    int num_pages, int max_pages, int q_off, int qkv_stride,
                                    float scale, int* status, void* stream) {
   using namespace hs;
   if (!out || !qkv || !pool || !table || !tok_pos || !tok_req || !tile_info ||
-      !plan_head || !status)
+      !plan_head || !status || !work_counter)
     return HS_ERR_ARGUMENT;
   if (tile_cap <= 0) return HS_OK;
   if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || n_heads > 65535)
     return HS_ERR_UNSUPPORTED;
   if (page_size <= 0 || page_size % 16) return HS_ERR_UNSUPPORTED;
   if ((qkv_stride % 8) || (q_off % 8)) return HS_ERR_UNSUPPORTED;
+  if (!(scale > 0.f)) return HS_ERR_UNSUPPORTED;     // maxima are tracked in scaled units
   PrefillParams p;
   p.qkv = (const __nv_bfloat16*)qkv; p.pool = (const __nv_bfloat16*)pool;
   p.out = (__nv_bfloat16*)out; p.table = table; p.tok_pos = tok_pos; p.tok_req = tok_req;
   p.tile_info = tile_info; p.plan_head = plan_head; p.status = status;
+  p.work_counter = work_counter;
+  p.ps_log2 = (page_size & (page_size - 1)) == 0 ? __builtin_ctz(page_size) : -1;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
   p.num_pages = num_pages; p.max_pages = max_pages; p.q_off = q_off; p.qkv_stride = qkv_stride;
   p.scale = scale;
   cudaStream_t st = (cudaStream_t)stream;
   switch (head_dim) {
-    case 16: return launch_prefill<16>(p, tile_cap, st);
-    case 32: return launch_prefill<32>(p, tile_cap, st);
-    case 64: return launch_prefill<64>(p, tile_cap, st);
-    case 128: return launch_prefill<128>(p, tile_cap, st);
+    case 16: return launch_prefill<16>(p, st);
+    case 32: return launch_prefill<32>(p, st);
+    case 64: return launch_prefill<64>(p, st);
+    case 128: return launch_prefill<128>(p, st);
     default: return HS_ERR_UNSUPPORTED;
   }
 }

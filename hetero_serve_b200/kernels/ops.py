@@ -126,7 +126,7 @@ def _declare(lib) -> None:
         "hs_attention_simt": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
         "hs_attention_decode_append": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I,
                                        F, I, I, I, I, P, P, P, P, P],
-        "hs_attention_prefill": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
+        "hs_attention_prefill": [P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P, P],
         "hs_argmax": [P, P, I, I, P],
         "hs_sample": [P, P, P, P, P, P, P, I, I, P],
     }
@@ -413,12 +413,13 @@ class CudaOps:
         """Fill the plan section (a numpy int32 view of the step's metadata) for a batch given
         as ``[(request, slot, start, n_new)]`` in flat order; returns ``(decode_cap,
         tile_cap, single_new)``.  Requests bringing up to DECODE_MAX_NEW tokens go to the single-query
-        list, the others are cut into tiles of 64 queries."""
+        list, the others are cut into tiles of 64 queries, longest context first."""
         dec = view[4:4 + 3 * n_rows]
         tiles = view[4 + plan_decode_ints(n_rows):]
         n_dec = n_tiles = max_ctx = 0
         t = 0
         single = True
+        tile_list = []
         for row, (_req, _slot, start, n) in enumerate(host_batch):
             if n <= DECODE_MAX_NEW:
                 single = single and n == 1
@@ -428,10 +429,13 @@ class CudaOps:
                 max_ctx = max(max_ctx, start + n)
             else:
                 for q0 in range(0, n, PREFILL_TILE):
-                    tiles[4 * n_tiles:4 * n_tiles + 4] = (t + q0, min(PREFILL_TILE, n - q0), row,
-                                                          start + q0)
+                    tile_list.append((t + q0, min(PREFILL_TILE, n - q0), row, start + q0))
                     n_tiles += 1
             t += n
+        # tiles with the most keys first, so that the long ones do not form the tail
+        tile_list.sort(key=lambda ti: -(ti[3] + ti[1]))
+        for i, ti in enumerate(tile_list):
+            tiles[4 * i:4 * i + 4] = ti
         view[0], view[1], view[2], view[3] = n_dec, n_tiles, max_ctx, 0
         single = single and n_dec > 0
         if bucketed:
@@ -478,16 +482,17 @@ class CudaOps:
 
     FAST_HEAD_DIMS = (16, 32, 64, 128)
 
-    def _fast_ok(self, qkv, g, plan, n) -> bool:
+    def _fast_ok(self, qkv, g, plan, n, scale=1.0) -> bool:
         return (plan is not None and self.fast_attention and qkv.dtype == torch.bfloat16
-                and g.window == 0 and g.head_dim in self.FAST_HEAD_DIMS and plan.n_rows >= n)
+                and g.window == 0 and g.head_dim in self.FAST_HEAD_DIMS and plan.n_rows >= n
+                and scale > 0)
 
     def attention_append(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status,
                          plan=None, writes=True):
         """Append the new keys/values to the pages (if ``writes``), then attention.  When the
         step is made of single decoded tokens only, the decode kernel does both in one launch."""
         n = out.shape[0]
-        fuse = (writes and self.fuse_append and self._fast_ok(qkv, g, plan, n)
+        fuse = (writes and self.fuse_append and self._fast_ok(qkv, g, plan, n, scale)
                 and plan.tile_cap == 0 and plan.decode_cap > 0 and plan.single_new)
         if writes and not fuse:
             self.kv_append(pool, qkv, table, tok_pos, tok_req, g, status)
@@ -496,7 +501,7 @@ class CudaOps:
 
     def _attention(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan, n,
                    fuse=False):
-        if self._fast_ok(qkv, g, plan, n):
+        if self._fast_ok(qkv, g, plan, n, scale):
             self._attention_fast(out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan,
                                  fuse)
             return
@@ -538,7 +543,8 @@ class CudaOps:
             self.launches += 1
             _check(self.lib.hs_attention_prefill(
                 _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req),
-                _ptr(tile_info), _ptr(head), plan.tile_cap, g.n_heads, g.n_kv_heads,
+                _ptr(tile_info), _ptr(head), plan.tile_cap,
+                _ptr(self._scratch_buffer("prefill_counter", 1, torch.int32)), g.n_heads, g.n_kv_heads,
                 g.head_dim, g.page_size, g.num_pages, g.max_pages, g.q_off, g.qkv_stride, scale,
                 _ptr(status), st), f"attention_prefill(head_dim={g.head_dim})")
 

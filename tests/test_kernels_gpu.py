@@ -284,7 +284,7 @@ FAST_CASES = [
     (6, 2, 64, 16, [150, 23, 90, 77], [70, 23, 3, 1]),           # grouped heads; both kernels
     (2, 1, 128, 32, [300, 64, 129], [130, 1, 129]),              # pages of 32, head size 128
     (5, 5, 32, 48, [100, 130], [100, 2]),                        # pages of 48
-    (2, 2, 64, 16, [64, 63, 65, 128, 1], [64, 63, 65, 64, 1]),   # tile edges
+    (2, 2, 64, 16, [64, 63, 65, 128, 1, 300], [64, 63, 65, 64, 1, 129]),   # tile edges
 ]
 
 
