@@ -1,0 +1,76 @@
+"""The engine at the real widths of GPT-2 medium, large and XL (a few layers of each, random
+weights): widths 1024 / 1280 / 1600, 16 / 20 / 25 heads of 64, inner 4x, the real vocabulary
+of 50,257 (odd, no power of two).  In 32-bit and in bfloat16, whole prompts against decoding
+and portions, compared with the plain implementation on the last positions."""
+
+import json
+
+import pytest
+import torch
+
+import plain_gpt2
+from hetero_serve_b200.engine.loading import load_model
+from hetero_serve_b200.engine.step import Runner, StepEntry
+from hetero_serve_b200.weights import read_safetensors, write_model_dir
+
+pytestmark = pytest.mark.gpu
+
+SIZES = {
+    "medium": dict(n_layer=3, n_embd=1024, n_head=16),
+    "large": dict(n_layer=2, n_embd=1280, n_head=20),
+    "xl": dict(n_layer=2, n_embd=1600, n_head=25),
+}
+
+
+@pytest.fixture(scope="module", params=list(SIZES))
+def real_model(request, tmp_path_factory):
+    sz = SIZES[request.param]
+    cfg = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", vocab_size=50257,
+               n_positions=1024, n_inner=None, layer_norm_epsilon=1e-5,
+               activation_function="gelu_new", scale_attn_by_inverse_layer_idx=False,
+               tie_word_embeddings=True, **sz)
+    d = tmp_path_factory.mktemp("real_" + request.param)
+    write_model_dir(d, cfg, 3, "float32")
+    raw = read_safetensors(d / "model.safetensors")
+    return request.param, str(d), json.loads((d / "config.json").read_text()), raw
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_real_widths_every_cut_agrees_with_the_plain_model(real_model, dtype):
+    name, d, cfg, raw = real_model
+    g = torch.Generator().manual_seed(11)
+    a = torch.randint(0, 50257, (150,), generator=g).tolist()
+    b = torch.randint(0, 50257, (41,), generator=g).tolist()
+    w = plain_gpt2.prepare_weights(raw, dtype=torch.float32,
+                                   round_to=torch.bfloat16 if dtype == "bfloat16" else None)
+    # float32 plain arithmetic is enough here: the comparison is at 1e-3 of a logit
+    ref_a = plain_gpt2.forward(cfg, w, a, dtype=torch.float32)
+    ref_b = plain_gpt2.forward(cfg, w, b, dtype=torch.float32)
+    model, _ = load_model(d, dtype, "cuda:0")
+    rn = Runner(model, num_pages=24, page_size=16, max_requests=4, dtype=model.dtype,
+                device="cuda:0", cuda_graphs=(dtype == "bfloat16"))
+    tol = 2e-3 if dtype == "float32" else 6e-2
+    got = {}
+    # a whole; b as a portion beside a's decoded tokens; then both decode together
+    # (the logits of a step live in a buffer the next step reuses: copy what is kept)
+    r = rn.step([StepEntry("a", a[:140], want=[0, 139])]).logits.clone()
+    got[("a", 0)], got[("a", 139)] = r[0], r[1]
+    r = rn.step([StepEntry("a", a[140:141], want=[0]),
+                 StepEntry("b", b[:30], want=[29])]).logits.clone()
+    got[("a", 140)], got[("b", 29)] = r[0], r[1]
+    r = rn.step([StepEntry("b", b[30:33], want=[2]),
+                 StepEntry("a", a[141:149], want=[7])]).logits.clone()
+    got[("b", 32)], got[("a", 148)] = r[0], r[1]
+    for i in range(33, 41):
+        r = rn.step([StepEntry("a", a[149:150], want=[0])] * (i == 33) +
+                    [StepEntry("b", b[i:i + 1], want=[0])]).logits.clone()
+        if i == 33:
+            got[("a", 149)] = r[0]
+        got[("b", i)] = r[-1]
+    worst = 0.0
+    for (rid, pos), row in got.items():
+        ref = (ref_a if rid == "a" else ref_b)[pos]
+        assert torch.isfinite(row).all()
+        worst = max(worst, float((row.float().cpu() - ref).abs().max()))
+    assert worst < tol, (name, dtype, worst)
+    rn.manager.check()
