@@ -5,13 +5,14 @@
 // scalar one (heteroserve/model/paged_attn_prefill.py:72-157: query s of a portion sits at
 // absolute position ctx_len - S + s and sees keys 0..that position; the mask is the loop bound).
 //
-// A work item = up to 64 consecutive queries of one request x one head, 4 warps of 16 queries.
+// A work item = up to 128 consecutive queries of one request x one head, 8 warps of 16 queries.
 // CTAs are persistent: each takes the next item from a counter in device memory, and the host
 // lists the items with the most keys first, so the causal triangle's uneven tiles spread evenly
 // over the SMs.  Keys and
 // values are taken 64 positions at a time: each 16-position block of a tile lies inside one page
 // (page sizes are multiples of 16), is found through the block table and copied to shared memory
-// with cp.async (a ring of three tiles: two in flight while one is used).  S = Q K^T and O += P V run on mma.sync m16n8k16
+// with cp.async (a ring of three tiles: two in flight while one is used).  S = Q K^T and O += P V run on mma.sync m16n8k16 (this is the kernel for head sizes 16, 32 and 128; head size 64 runs on
+// tcgen05, attention_prefill_tc.cu)
 // (bf16 in, f32 accumulate), fragments fetched with ldmatrix from XOR-swizzled tiles; the scores
 // are multiplied by `scale` after the dot product (heteroserve/model/torch_engine.py:135); the
 // running maximum, the running sum and O are float32 (online softmax).  The new tokens' own keys
@@ -19,13 +20,13 @@
 // no special case.  Tiles past a warp's last query are skipped.
 //
 // Work list (device memory, written by the host per step): plan_head[1] = number of tiles;
-// tile_info[4 i ..] = flat index of the tile's first query, its number of queries (<= 64), its
+// tile_info[4 i ..] = flat index of the tile's first query, its number of queries (<= 128), its
 // request's row in the block table, the position of its first query.
 #include "common.cuh"
 
 namespace hs {
 
-constexpr int AP_BQ = 64, AP_BKV = 64, AP_WARPS = 4, AP_STAGES = 3;
+constexpr int AP_BQ = 128, AP_BKV = 64, AP_WARPS = 8, AP_STAGES = 3;
 
 struct PrefillParams {
   const __nv_bfloat16* qkv;
@@ -87,7 +88,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(AP_WARPS * 32, (D <= 64 ? 4 : 2))
+__global__ void __launch_bounds__(AP_WARPS * 32, (D <= 64 ? 2 : 1))
 attention_prefill_kernel(const PrefillParams p) {
   constexpr int CPR = D / 8;
   constexpr int KSTEPS = D / 16;       // k-steps of Q K^T
@@ -315,7 +316,7 @@ static int launch_prefill(const PrefillParams& p, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
     if (per_sm < 1) per_sm = 1;
-    if (per_sm > 3) per_sm = 3;        // three per SM leave items over to be handed out late
+    if (per_sm > 2) per_sm = 2;
     ctas = per_sm * sms;
   }
   cudaError_t e = cudaMemsetAsync(p.work_counter, 0, sizeof(int), st);

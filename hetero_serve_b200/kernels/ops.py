@@ -52,7 +52,7 @@ class AttentionGeometry:
 class AttentionPlan:
     """Work lists of one step for the specialised attention kernels, in device memory.
 
-    ``data`` (int32): ``[0]`` number of single-query tokens, ``[1]`` number of 64-query
+    ``data`` (int32): ``[0]`` number of single-query tokens, ``[1]`` number of 128-query
     tiles, ``[2]`` longest context among the single-query tokens, ``[3]`` unused; then per
     single-query token (``n_rows`` slots) its flat index, request row and position; then per
     tile (``tile_slots`` slots) the flat index of its first query, its number of queries, its
@@ -72,7 +72,7 @@ class AttentionPlan:
 
 
 DECODE_MAX_NEW = 4        # requests bringing at most this many tokens use the decode kernel
-PREFILL_TILE = 64
+PREFILL_TILE = 128
 
 
 def _pow2(n: int) -> int:
@@ -127,6 +127,7 @@ def _declare(lib) -> None:
         "hs_attention_decode_append": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I,
                                        F, I, I, I, I, P, P, P, P, P],
         "hs_attention_prefill": [P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P, P],
+        "hs_attention_prefill_tc": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, P, P],
         "hs_argmax": [P, P, I, I, P],
         "hs_sample": [P, P, P, P, P, P, P, I, I, P],
     }
@@ -179,6 +180,7 @@ class CudaOps:
         self.launches = 0          # kernels launched through this object (graph captures count once)
         self.tensor_cores = True   # bfloat16 linears on tcgen05 (False: CUDA cores, for tests)
         self.fast_attention = True  # bfloat16 attention on the split-context / tensor-core kernels
+        self.tc_attention = True    # head size 64: prompt portions on the tcgen05 attention kernel
         self.sm_count = torch.cuda.get_device_properties(0).multi_processor_count
         self.fuse_norm = True      # LayerNorm fused into the few-row linear kernel
         self.fuse_append = True    # key/value append fused into the decode attention
@@ -413,7 +415,7 @@ class CudaOps:
         """Fill the plan section (a numpy int32 view of the step's metadata) for a batch given
         as ``[(request, slot, start, n_new)]`` in flat order; returns ``(decode_cap,
         tile_cap, single_new)``.  Requests bringing up to DECODE_MAX_NEW tokens go to the single-query
-        list, the others are cut into tiles of 64 queries, longest context first."""
+        list, the others are cut into tiles of 128 queries, longest context first."""
         dec = view[4:4 + 3 * n_rows]
         tiles = view[4 + plan_decode_ints(n_rows):]
         n_dec = n_tiles = max_ctx = 0
@@ -541,6 +543,16 @@ class CudaOps:
                 _ptr(status), st), f"attention_decode(head_dim={g.head_dim})")
         if plan.tile_cap:
             self.launches += 1
+            counter = self._scratch_buffer("prefill_counter", 1, torch.int32)
+            if self.tc_attention and g.head_dim == 64:
+                code = self.lib.hs_attention_prefill_tc(
+                    _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tile_info), _ptr(head),
+                    plan.tile_cap, _ptr(counter), qkv.shape[0], g.n_heads, g.n_kv_heads,
+                    g.head_dim, g.page_size, g.num_pages, g.max_pages, g.q_off, g.qkv_stride,
+                    scale, _ptr(status), st)
+                if code != -1:
+                    _check(code, "attention_prefill_tc")
+                    return
             _check(self.lib.hs_attention_prefill(
                 _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req),
                 _ptr(tile_info), _ptr(head), plan.tile_cap,

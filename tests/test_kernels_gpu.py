@@ -299,7 +299,7 @@ def test_specialised_attention_kernels(ops, plain, case):
     T = qkv.shape[0]
     plan = ops.make_plan(_host_batch(lens, new), T, PS)
     assert plan.decode_cap == sum(k for k in new if k <= 4)
-    assert plan.tile_cap == sum(-(-k // 64) for k in new if k > 4)
+    assert plan.tile_cap == sum(-(-k // 128) for k in new if k > 4)
     out = torch.full((T, H * D), float("nan"), device=DEV, dtype=torch.bfloat16)
     ref = torch.empty(T, H * D, device=DEV, dtype=torch.float64)
     scale = 0.9 / D ** 0.5
