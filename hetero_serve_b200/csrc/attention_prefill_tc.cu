@@ -8,15 +8,17 @@
 // tensor memory, the operands are staged by TMA, and the softmax runs with ONE THREAD PER QUERY
 // ROW (a TMEM lane is a row), so row maxima and sums need no shuffles.
 //
-// A work item is up to 128 consecutive queries of one request x one head.  CTAs are persistent
-// and take items from a counter in device memory; the host lists them with the most keys first.
+// A work item is up to 128 consecutive queries of one request x one head.  CTAs are persistent;
+// the host lists the items with the most keys first and CTA b walks b, 2G-1-b, 2G+b, ... (a snake
+// over the sorted list, G CTAs), so every role knows its sequence and runs ahead on its own.
 //   warp 0      TMA producer: the Q tile [128 x 64] once per item; per 128-key tile, one
 //               [16 x 64] box of K and of V per 16-position block, found through the block table
-//               (a page holds whole blocks), into a two-stage ring;
+//               (a page holds whole blocks), into a four-stage ring;
 //   warp 1      one thread issues  S[b] = Q K^T  (M=128, N=128, 4 k-steps) into one of two TMEM
 //               buffers, and  O_tile = P V  (M=128, N=64, 8 k-steps, V as the N-contiguous
 //               operand) once the softmax warps have written P;
-//   warps 2..5  softmax: tcgen05.ld of a row of S (two passes: maximum, then exponentials),
+//   warps 2..9  softmax, two threads per query row (one per 64-key half; the halves exchange
+//               their maxima through shared memory): tcgen05.ld of the row, maximum, exponentials,
 //               scores * scale folded into the exponent (2^(s*scale*log2e - m)), causal mask by
 //               position, P written to shared memory as bfloat16 in the swizzled operand layout,
 //               O_tile added into the row's float32 accumulator in registers with the usual
@@ -31,8 +33,9 @@
 namespace hs {
 
 constexpr int TA_BQ = 128, TA_BKV = 128, TA_D = 64;
-constexpr int TA_THREADS = 192;
-constexpr int TA_KV_STAGES = 2;
+constexpr int TA_THREADS = 320;          // warp 0 TMA, warp 1 MMA, warps 2..9 softmax
+constexpr int TA_SOFTMAX_WARPS = 8;
+constexpr int TA_KV_STAGES = 4;
 constexpr int TA_Q_BYTES = TA_BQ * TA_D * 2;             // 16 KB
 constexpr int TA_KV_BYTES = TA_BKV * TA_D * 2;           // 16 KB per K or V tile
 constexpr int TA_P_BYTES = TA_BQ * TA_BKV * 2;           // 32 KB: two 64-key k-blocks
@@ -49,11 +52,14 @@ struct PrefillTcParams {
   int* work_counter;
   int n_heads, n_kv_heads, page_size, num_pages, max_pages, q_off, ps_log2;
   float scale;
+  unsigned long long* timing;   // null, or 8 x uint64 per CTA: cycles per softmax phase
 };
 
 // barriers, in this order in shared memory
-enum { B_Q_FULL = 0, B_KV_FULL = 1, B_KV_EMPTY = 3, B_S_FULL = 5, B_S_EMPTY = 7, B_P_FULL = 9,
-       B_P_EMPTY = 10, B_O_FULL = 11, B_O_EMPTY = 12, B_Q_EMPTY = 13, B_COUNT = 14 };
+enum { B_Q_FULL = 0, B_KV_FULL = 1, B_KV_EMPTY = 1 + TA_KV_STAGES, B_S_FULL = 1 + 2 * TA_KV_STAGES,
+       B_S_EMPTY = B_S_FULL + 2, B_P_FULL = B_S_EMPTY + 2, B_P_EMPTY = B_P_FULL + 1,
+       B_O_FULL = B_P_EMPTY + 1, B_O_EMPTY = B_O_FULL + 1, B_Q_EMPTY = B_O_EMPTY + 1,
+       B_COUNT = B_Q_EMPTY + 1 };
 
 __device__ __forceinline__ float ex2_fast(float x) {
   float y;
@@ -73,7 +79,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   uint8_t* sP = sV + TA_KV_STAGES * TA_KV_BYTES;          // [2 k-blocks][128 rows][128 B]
   uint64_t* bars = (uint64_t*)(sP + TA_P_BYTES);
   uint32_t* tmem_slot = (uint32_t*)(bars + B_COUNT);
-  __shared__ int s_item;
+  __shared__ float s_max2[2][2][TA_BQ];  // [tile parity][half][row]: row maxima of the halves
+  __shared__ float s_l[2][TA_BQ];        // [half][row]: the halves' shares of the row sum
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_items = p.plan_head[1] * p.n_heads;
@@ -84,17 +91,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 
   if (threadIdx.x == 0) {
     mbar_init(&bars[B_Q_FULL], 1);
-    mbar_init(&bars[B_Q_EMPTY], 4);
-    for (int i = 0; i < 2; ++i) {
+    mbar_init(&bars[B_Q_EMPTY], 1);
+    for (int i = 0; i < TA_KV_STAGES; ++i) {
       mbar_init(&bars[B_KV_FULL + i], 1);
       mbar_init(&bars[B_KV_EMPTY + i], 1);
-      mbar_init(&bars[B_S_FULL + i], 1);
-      mbar_init(&bars[B_S_EMPTY + i], 4);
     }
-    mbar_init(&bars[B_P_FULL], 4);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[B_S_FULL + i], 1);
+      mbar_init(&bars[B_S_EMPTY + i], TA_SOFTMAX_WARPS);
+    }
+    mbar_init(&bars[B_P_FULL], TA_SOFTMAX_WARPS);
     mbar_init(&bars[B_P_EMPTY], 1);
     mbar_init(&bars[B_O_FULL], 1);
-    mbar_init(&bars[B_O_EMPTY], 4);
+    mbar_init(&bars[B_O_EMPTY], TA_SOFTMAX_WARPS);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -111,12 +120,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   uint32_t n_tile = 0;        // key tiles processed by this CTA (over all items)
   bool ok = true;
 
-  while (ok) {
-    __syncthreads();
-    if (threadIdx.x == 0) s_item = atomicAdd(p.work_counter, 1);
-    __syncthreads();
-    const int item = s_item;
-    if (item >= n_items) break;
+  // Items are listed heaviest first; CTA b takes b, 2G-1-b, 2G+b, 4G-1-b, ... (G CTAs): a
+  // snake over the sorted list, so heavy and light items alternate per CTA.  Every role walks
+  // the same sequence on its own: no CTA-wide synchronisation between items.
+  const int G = gridDim.x;
+  for (int round = 0; ok; ++round) {
+    const int item = round * G + ((round & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    if (round * G >= n_items) break;
+    if (item >= n_items) continue;
     const int tile = item / p.n_heads, h = item - tile * p.n_heads;
     const int4 ti = *(const int4*)(p.tile_info + 4 * tile);
     const int tok0 = ti.x, nq = ti.y, r = ti.z, pos0 = ti.w;
@@ -140,8 +151,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         for (int kt = 0; kt < n_kv && ok; ++kt) {
           const uint32_t it = n_tile + kt;
-          const int st = it & 1;
-          if (it >= 2) ok = mbar_wait(&bars[B_KV_EMPTY + st], ((it >> 1) - 1) & 1, p.status);
+          const int st = it % TA_KV_STAGES;
+          if (it >= TA_KV_STAGES)
+            ok = mbar_wait(&bars[B_KV_EMPTY + st], ((it / TA_KV_STAGES) - 1) & 1, p.status);
           if (!ok) break;
           // blocks of 16 positions up to the item's last one
           const int first = kt * TA_BKV;
@@ -186,8 +198,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         ok = mbar_wait(&bars[B_Q_FULL], n_item & 1, p.status);
         auto issue_s = [&](int kt) -> bool {
           const uint32_t it = n_tile + kt;
-          const int st = it & 1, sb = it & 1;
-          if (!mbar_wait(&bars[B_KV_FULL + st], (it >> 1) & 1, p.status)) return false;
+          const int st = it % TA_KV_STAGES, sb = it & 1;
+          if (!mbar_wait(&bars[B_KV_FULL + st], (it / TA_KV_STAGES) & 1, p.status)) return false;
           if (it >= 2 && !mbar_wait(&bars[B_S_EMPTY + sb], ((it >> 1) - 1) & 1, p.status))
             return false;
           tc_fence_after();
@@ -198,12 +210,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             umma_bf16(tmem_base + sb * S_COLS, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2),
                       idesc_s, k > 0 ? 1u : 0u);
           umma_commit(&bars[B_S_FULL + sb]);
+          // the item's last S: once it has completed, Q may be replaced by the next item's
+          if (kt == n_kv - 1) umma_commit(&bars[B_Q_EMPTY]);
           return true;
         };
         if (ok) ok = issue_s(0);
         for (int kt = 0; kt < n_kv && ok; ++kt) {
           const uint32_t it = n_tile + kt;
-          const int st = it & 1;
+          const int st = it % TA_KV_STAGES;
           if (kt + 1 < n_kv) ok = issue_s(kt + 1);      // overlaps the softmax of tile kt
           if (!ok) break;
           ok = mbar_wait(&bars[B_P_FULL], it & 1, p.status);
@@ -226,28 +240,36 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       }
     } else {
-      // ---------------- softmax and output: thread = query row
+      // ---------------- softmax and output: two threads per query row, one per half of the
+      // tile's 128 keys (and per half of the 64 output columns)
       const int q = warp & 3;                               // TMEM lane quarter of this warp
+      const int half = (warp - 2) >> 2;                     // 0: keys 0..63, 1: keys 64..127
       const int row = q * 32 + lane;
       const int pos_r = min(pos0 + row, pos_last);          // rows past nq: finite, never stored
       const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
       const float sl2 = p.scale * 1.4426950408889634f;
       float m = -INFINITY, l = 0.f, corr_pending = 1.f;
-      float o[TA_D];
+      long long t_mark = clock64();
+      auto lap = [&](int phase) {
+        if (p.timing != nullptr && threadIdx.x == 64) {
+          const long long now = clock64();
+          p.timing[(size_t)blockIdx.x * 8 + phase] += (unsigned long long)(now - t_mark);
+          t_mark = now;
+        }
+      };
+      constexpr int OC = TA_D / 2;                          // output columns of this thread
+      float o[OC];
 #pragma unroll
-      for (int d = 0; d < TA_D; ++d) o[d] = 0.f;
+      for (int d = 0; d < OC; ++d) o[d] = 0.f;
 
       auto accumulate_o = [&](uint32_t it) -> bool {
         if (!mbar_wait(&bars[B_O_FULL], it & 1, p.status)) return false;
         tc_fence_after();
+        uint32_t v[32];
+        tmem_ld32(lane_addr + O_COL + half * OC, v);
+        tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < TA_D; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(lane_addr + O_COL + c, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[c + j] = fmaf(o[c + j], corr_pending, __uint_as_float(v[j]));
-        }
+        for (int j = 0; j < OC; ++j) o[j] = fmaf(o[j], corr_pending, __uint_as_float(v[j]));
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[B_O_EMPTY]);
@@ -256,55 +278,90 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 
       for (int kt = 0; kt < n_kv && ok; ++kt) {
         const uint32_t it = n_tile + kt;
-        const int sb = it & 1, st = it & 1;
+        const int sb = it & 1, st = it % TA_KV_STAGES;
+        lap(5);
         ok = mbar_wait(&bars[B_S_FULL + sb], (it >> 1) & 1, p.status);
         if (!ok) break;
         tc_fence_after();
-        const int j0 = kt * TA_BKV;
-        const bool diagonal = j0 + TA_BKV - 1 > pos0;       // some row of the item needs the mask
-        // pass 1: the row's maximum (in raw score units; the scale is positive)
+        lap(0);
+        const int j0 = kt * TA_BKV + half * 64;             // first key of this thread's half
+        const bool diagonal = kt * TA_BKV + TA_BKV - 1 > pos0;   // some row needs the mask
+        const uint32_t s_addr = lane_addr + sb * S_COLS + half * 64;
+        // pass 1: the maximum over this half of the row (raw score units; the scale is positive);
+        // the second chunk's TMEM load is in flight while the first is reduced
+        uint32_t va[32], vb[32];
+        tmem_ld32(s_addr, va);
+        tmem_ld_wait();
+        tmem_ld32(s_addr + 32, vb);
         float mx = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < TA_BKV; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(lane_addr + sb * S_COLS + c, v);
+        if (diagonal) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j0 + j <= pos_r) mx = fmaxf(mx, __uint_as_float(va[j]));
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float s = __uint_as_float(v[j]);
-            if (!diagonal || j0 + c + j <= pos_r) mx = fmaxf(mx, s);
+          for (int j = 0; j < 32; ++j)
+            if (j0 + 32 + j <= pos_r) mx = fmaxf(mx, __uint_as_float(vb[j]));
+        } else {
+          float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            m0 = fmaxf(m0, __uint_as_float(va[j]));
+            m1 = fmaxf(m1, __uint_as_float(va[j + 1]));
+            m2 = fmaxf(m2, __uint_as_float(va[j + 2]));
+            m3 = fmaxf(m3, __uint_as_float(va[j + 3]));
           }
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            m0 = fmaxf(m0, __uint_as_float(vb[j]));
+            m1 = fmaxf(m1, __uint_as_float(vb[j + 1]));
+            m2 = fmaxf(m2, __uint_as_float(vb[j + 2]));
+            m3 = fmaxf(m3, __uint_as_float(vb[j + 3]));
+          }
+          mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
         }
+        // the other half's maximum, through shared memory (buffers alternate by tile parity)
+        s_max2[it & 1][half][row] = mx;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");   // the two warps of this quarter
+        mx = fmaxf(mx, s_max2[it & 1][half ^ 1][row]);
+        lap(1);
         const float m_new = fmaxf(m, mx * sl2);
         const float corr = (m_new == -INFINITY) ? 1.f : ex2_fast(m - m_new);
         const float base = (m_new == -INFINITY) ? 0.f : m_new;
-        // pass 2: exponentials, packed to bfloat16 (64 registers hold the row of P)
-        uint32_t pk[TA_BKV / 2];
+        // pass 2: exponentials of this half, packed to bfloat16 (32 registers)
+        uint32_t pk[32];
         float sum = 0.f;
 #pragma unroll
-        for (int c = 0; c < TA_BKV; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(lane_addr + sb * S_COLS + c, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            float e0 = ex2_fast(fmaf(__uint_as_float(v[j]), sl2, -base));
-            float e1 = ex2_fast(fmaf(__uint_as_float(v[j + 1]), sl2, -base));
-            if (diagonal) {
-              if (j0 + c + j > pos_r) e0 = 0.f;
-              if (j0 + c + j + 1 > pos_r) e1 = 0.f;
-            }
-            __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
-            pk[(c + j) >> 1] = *(uint32_t*)&b;
-            // the sum uses what the tensor core will see (rounded to bfloat16)
-            sum += __bfloat162float(b.x) + __bfloat162float(b.y);
+        for (int j = 0; j < 32; j += 2) {
+          float e0 = ex2_fast(fmaf(__uint_as_float(va[j]), sl2, -base));
+          float e1 = ex2_fast(fmaf(__uint_as_float(va[j + 1]), sl2, -base));
+          if (diagonal) {
+            if (j0 + j > pos_r) e0 = 0.f;
+            if (j0 + j + 1 > pos_r) e1 = 0.f;
           }
+          sum += e0 + e1;
+          __nv_bfloat162 bq = __floats2bfloat162_rn(e0, e1);
+          pk[j >> 1] = *(uint32_t*)&bq;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float e0 = ex2_fast(fmaf(__uint_as_float(vb[j]), sl2, -base));
+          float e1 = ex2_fast(fmaf(__uint_as_float(vb[j + 1]), sl2, -base));
+          if (diagonal) {
+            if (j0 + 32 + j > pos_r) e0 = 0.f;
+            if (j0 + 32 + j + 1 > pos_r) e1 = 0.f;
+          }
+          sum += e0 + e1;
+          __nv_bfloat162 bq = __floats2bfloat162_rn(e0, e1);
+          pk[16 + (j >> 1)] = *(uint32_t*)&bq;
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[B_S_EMPTY + sb]);   // S[sb] may be overwritten
-        l = l * corr + sum;
+        l = l * corr + sum;                                  // this half's share of the row sum
         m = m_new;
+        lap(2);
         // the previous tile's P V has finished (P is free) and its O_tile is ready
         if (it >= 1) {
           ok = mbar_wait(&bars[B_P_EMPTY], (it - 1) & 1, p.status);
@@ -315,34 +372,39 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
           }
         }
         corr_pending = corr;
-        // write this row of P: 16 chunks of 8 keys; chunk c of k-block kb at
-        //   kb * 16 KB + (row / 8) * 1 KB + (row % 8) * 128 B + ((c ^ (row % 8)) * 16 B)
-        uint8_t* prow = sP + (row >> 3) * 1024 + (row & 7) * 128;
+        lap(3);
+        // write this half-row of P: k-block `half`, 8 chunks of 8 keys; chunk c at
+        //   half * 16 KB + (row / 8) * 1 KB + (row % 8) * 128 B + ((c ^ (row % 8)) * 16 B)
+        uint8_t* prow = sP + half * 16384 + (row >> 3) * 1024 + (row & 7) * 128;
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
+        for (int c = 0; c < 8; ++c) {
           uint4 u = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-          *(uint4*)(prow + (c >> 3) * 16384 + (((c & 7) ^ (row & 7)) << 4)) = u;
+          *(uint4*)(prow + ((c ^ (row & 7)) << 4)) = u;
         }
-        // rows of V past the item's last position were not loaded: zero them (this thread's
-        // row index doubles as a key index of the tile)
-        if (j0 + row > pos_last) {
-          uint4* vrow = (uint4*)(sV + st * TA_KV_BYTES + row * 128);
+        // rows of V past the item's last position were not loaded: zero them (the row index
+        // doubles as a key index of the tile; each half clears half of the 128-byte row)
+        if (kt * TA_BKV + row > pos_last) {
+          uint4* vrow = (uint4*)(sV + st * TA_KV_BYTES + row * 128) + half * 4;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0, 0, 0, 0);
+          for (int c = 0; c < 4; ++c) vrow[c] = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[B_P_FULL]);
+        lap(4);
       }
       if (ok) ok = accumulate_o(n_tile + n_kv - 1);
-      // Q may be overwritten by the next item's load
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[B_Q_EMPTY]);
+      lap(6);
+      // the row sum is the two halves' shares together (the next write of s_l comes after
+      // at least one more barrier of these warps, so one barrier is enough)
+      s_l[half][row] = l;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
+      const float l_all = l + s_l[half ^ 1][row];
       if (ok && row < nq) {
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16* orow = p.out + ((size_t)(tok0 + row) * p.n_heads + h) * TA_D;
+        const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+        __nv_bfloat16* orow = p.out + ((size_t)(tok0 + row) * p.n_heads + h) * TA_D + half * OC;
 #pragma unroll
-        for (int c = 0; c < TA_D; c += 8) {
+        for (int c = 0; c < OC; c += 8) {
           __nv_bfloat162 a0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv);
           __nv_bfloat162 a1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
           __nv_bfloat162 a2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv);
@@ -412,7 +474,8 @@ HS_EXPORT int hs_attention_prefill_tc(void* out, const void* qkv, const void* po
                                       int page_size, int num_pages, int max_pages, int q_off,
                                       int qkv_stride, float scale, int* status, void* stream) {
   using namespace hs;
-  if (!out || !qkv || !pool || !table || !tile_info || !plan_head || !status || !work_counter)
+  (void)work_counter;      // items are assigned statically here; the argument is kept for symmetry
+  if (!out || !qkv || !pool || !table || !tile_info || !plan_head || !status)
     return HS_ERR_ARGUMENT;
   if (tile_cap <= 0) return HS_OK;
   if (head_dim != TA_D) return HS_ERR_UNSUPPORTED;
@@ -434,6 +497,7 @@ HS_EXPORT int hs_attention_prefill_tc(void* out, const void* qkv, const void* po
   p.num_pages = num_pages; p.max_pages = max_pages; p.q_off = q_off;
   p.ps_log2 = (page_size & (page_size - 1)) == 0 ? __builtin_ctz(page_size) : -1;
   p.scale = scale;
+  p.timing = hs_timing_buffer();
   static int sms = 0;
   if (sms == 0) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel,
@@ -442,8 +506,6 @@ HS_EXPORT int hs_attention_prefill_tc(void* out, const void* qkv, const void* po
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
   }
   cudaStream_t st = (cudaStream_t)stream;
-  cudaError_t e = cudaMemsetAsync(work_counter, 0, sizeof(int), st);
-  if (e != cudaSuccess) return (int)e;
   attention_prefill_tc_kernel<<<sms, TA_THREADS, TA_SMEM, st>>>(mq, mkv, p);
   HS_LAUNCH_CHECK();
   return HS_OK;
