@@ -198,9 +198,10 @@ def time_prefill(runner, torch, n_seqs, seq_len, vocab, seed, reps=5, warmup=3):
 
 
 def time_e2e(model_dir, torch, batch, prompt_len, steps, warmup, vocab, seed, num_blocks):
-    """The same decode steps through the public entry point: LLMEngine.step(), which takes
-    host token ids (packed into pinned memory and copied to the device each step) and
-    brings the sampled ids back to the host each step."""
+    """The same decode steps through the public entry point: LLMEngine.step(), which packs the
+    step's host-side inputs into pinned memory and copies them to the device, and brings
+    sampled ids back to the host, every call.  The engine pipelines: a call launches one step
+    and reads the tokens of the step before it, so K calls are K launches and K reads."""
     from hetero_serve_b200 import EngineConfig, LLMEngine, Request
     eng = LLMEngine(model_dir, EngineConfig(
         dtype="bfloat16", num_blocks=num_blocks, max_batch=batch, max_prefill_tokens=2048,
@@ -219,7 +220,7 @@ def time_e2e(model_dir, torch, batch, prompt_len, steps, warmup, vocab, seed, nu
         eng.step()
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
-    assert all(len(s.output_ids) == 1 + warmup + steps for s in seqs)
+    assert all(len(s.output_ids) + s.pending == 1 + warmup + steps for s in seqs)
     lay = eng.runner._layout(max(8, batch), batch, batch)
     h2d = lay.total * 4
     d2h = (batch + 1) * 4

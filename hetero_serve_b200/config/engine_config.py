@@ -38,6 +38,7 @@ class EngineConfig:
     policy: str = "prefill_first"     # "prefill_first" as the reference, or "mixed"
     prefix_cache: bool = True         # reuse pages of equal prompt prefixes
     cuda_graphs: bool = True          # replay captured steps for repeated shapes
+    pipeline: bool = True             # launch a step before the previous step's tokens are read
     seed: int = 0
     device: str = "cuda:0"
 

@@ -11,14 +11,17 @@ template <typename T>
 __global__ void embed_kernel(float* __restrict__ x, const int* __restrict__ ids,
                              const int* __restrict__ pos, const int* __restrict__ req,
                              const T* __restrict__ wte, const T* __restrict__ wpe, int width,
-                             int vocab, int n_pos, int* status) {
+                             int vocab, int n_pos, const int* __restrict__ feedback,
+                             int n_feedback, int* status) {
   pdl_trigger();
   const int t = blockIdx.x;
   float* row = x + (size_t)t * width;
   const int r = req[t];
-  const int id = ids[t];
+  int id = ids[t];
   const int p = pos[t];
   bool ok = r >= 0;
+  // id = -(s + 1): the token that the latest sampling step left in feedback[s]
+  if (ok && id < 0 && feedback != nullptr && -(id + 1) < n_feedback) id = feedback[-(id + 1)];
   if (ok && (id < 0 || id >= vocab)) {
     if (threadIdx.x == 0) atomicOr(status, HS_STATUS_BAD_TOKEN);
     ok = false;
@@ -148,20 +151,25 @@ layernorm_warp_kernel(TO* __restrict__ out, const float* __restrict__ x,
 
 }  // namespace hs
 
+// feedback (may be null): `n_feedback` token ids kept on the device; a negative id -(s + 1) in
+// `ids` stands for feedback[s], so that a step can start before the host has seen the token the
+// previous step sampled.
 HS_EXPORT int hs_embed(float* x, const int* ids, const int* pos, const int* req, const void* wte,
                        const void* wpe, int n_tokens, int width, int vocab, int n_pos,
-                       int table_dtype, int* status, void* stream) {
+                       int table_dtype, const int* feedback, int n_feedback, int* status,
+                       void* stream) {
   if (!x || !ids || !pos || !req || !wte || !status) return HS_ERR_ARGUMENT;
   if (n_tokens <= 0) return HS_OK;
   cudaStream_t st = (cudaStream_t)stream;
   int threads = width >= 1024 ? 256 : 128;
   if (table_dtype == HS_DT_F32)
     hs::embed_kernel<float><<<n_tokens, threads, 0, st>>>(
-        x, ids, pos, req, (const float*)wte, (const float*)wpe, width, vocab, n_pos, status);
+        x, ids, pos, req, (const float*)wte, (const float*)wpe, width, vocab, n_pos, feedback,
+        n_feedback, status);
   else if (table_dtype == HS_DT_BF16)
     hs::embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, st>>>(
         x, ids, pos, req, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, width, vocab,
-        n_pos, status);
+        n_pos, feedback, n_feedback, status);
   else
     return HS_ERR_UNSUPPORTED;
   HS_LAUNCH_CHECK();

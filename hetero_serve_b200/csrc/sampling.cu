@@ -162,13 +162,19 @@ __global__ void __launch_bounds__(SM_THREADS)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               const int* __restrict__ seed_lo, const int* __restrict__ seed_hi,
-              const int* __restrict__ position, int vocab) {
+              const int* __restrict__ position, int vocab, int* __restrict__ feedback,
+              const int* __restrict__ feedback_slot) {
   const int rowi = blockIdx.x;
   const float* row = logits + (size_t)rowi * vocab;
   const float temp = temperature[rowi];
   const ArgMax top = block_argmax(row, vocab);
+  // a row with a feedback slot also leaves its token there, for the next step's embedding
+  const int fb = (feedback != nullptr && feedback_slot != nullptr) ? feedback_slot[rowi] : -1;
   if (!(temp > 0.f)) {
-    if (threadIdx.x == 0) out[rowi] = top.i;
+    if (threadIdx.x == 0) {
+      out[rowi] = top.i;
+      if (fb >= 0) feedback[fb] = top.i;
+    }
     return;
   }
   const float mx = top.v / temp;
@@ -243,9 +249,13 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
     __syncthreads();
     atomicMax(&lastk, last_kept);
     __syncthreads();
-    if (threadIdx.x == 0) out[rowi] = lastk;
+    if (threadIdx.x == 0) {
+      out[rowi] = lastk;
+      if (fb >= 0) feedback[fb] = lastk;
+    }
   } else if (threadIdx.x == 0) {
     out[rowi] = found;
+    if (fb >= 0) feedback[fb] = found;
   }
 }
 
@@ -260,15 +270,17 @@ HS_EXPORT int hs_argmax(int* out, const float* logits, int rows, int vocab, void
   return HS_OK;
 }
 
+// feedback / feedback_slot (both may be null): row i also stores its token to
+// feedback[feedback_slot[i]] when that slot is not negative.
 HS_EXPORT int hs_sample(int* out, const float* logits, const float* temperature, const int* top_k,
                         const int* seed_lo, const int* seed_hi, const int* position, int rows,
-                        int vocab, void* stream) {
+                        int vocab, int* feedback, const int* feedback_slot, void* stream) {
   if (!out || !logits || !temperature || !top_k || !seed_lo || !seed_hi || !position)
     return HS_ERR_ARGUMENT;
   if (rows <= 0) return HS_OK;
   if (vocab <= 0) return HS_ERR_ARGUMENT;
   hs::sample_kernel<<<rows, hs::SM_THREADS, 0, (cudaStream_t)stream>>>(
-      out, logits, temperature, top_k, seed_lo, seed_hi, position, vocab);
+      out, logits, temperature, top_k, seed_lo, seed_hi, position, vocab, feedback, feedback_slot);
   HS_LAUNCH_CHECK();
   return HS_OK;
 }

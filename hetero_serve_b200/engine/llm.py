@@ -46,7 +46,8 @@ class LLMEngine:
         self.scheduler = Scheduler(
             self.runner.manager, self._run_step, max_batch=cfg.max_batch,
             max_prefill_tokens=cfg.max_prefill_tokens, max_ctx=max_ctx,
-            eos_token_id=spec.eos_token_id, policy=cfg.policy, vocab_size=spec.vocab_size)
+            eos_token_id=spec.eos_token_id, policy=cfg.policy, vocab_size=spec.vocab_size,
+            pipeline=cfg.pipeline)
         self._tmp = None
 
     # -- construction --------------------------------------------------------------
@@ -68,9 +69,13 @@ class LLMEngine:
         return eng
 
     # -- the loop -------------------------------------------------------------------
-    def _run_step(self, entries: list[StepEntry]) -> list[int]:
+    def _run_step(self, entries: list[StepEntry]):
+        """Launch a step with device sampling.  The copy of its tokens to the host is enqueued
+        behind it; the scheduler asks for them (``tokens_host``) when it needs them — with
+        ``pipeline``, after it has launched the following step."""
         res = self.runner.step(entries, sample=True)
-        return res.tokens_host()
+        res.start_fetch()
+        return res
 
     def submit_nowait(self, request: Request) -> SequenceState:
         return self.scheduler.add(request)
@@ -79,7 +84,8 @@ class LLMEngine:
         return self.scheduler.has_work()
 
     def step(self) -> list[RequestRecord]:
-        """One scheduler iteration; returns the records of requests that finished in it."""
+        """One scheduler iteration; returns the records of requests whose end became known in
+        it (with ``pipeline`` that is one call after the step that produced their last token)."""
         return [RequestRecord.of(s) for s in self.scheduler.step()]
 
     def run_until_done(self) -> list[RequestRecord]:

@@ -32,6 +32,18 @@ What happens when pages run out — decided here:
    (all but the last token, which decoding feeds).  Because the random draw of a token
    depends only on (seed, position), a preempted request continues exactly as it would
    have.
+
+Pipelining (``pipeline=True``).  ``step_fn`` may return, instead of a list of tokens, an object
+whose ``tokens_host()`` yields them later.  The scheduler then launches step i+1 BEFORE it reads
+step i's tokens: a request whose latest token is still on its way decodes with
+``FROM_DEVICE`` (the step reads the token from device memory), so the host's work and the
+transfer hide behind the device's.  What needs the token itself waits for it: a request that
+reaches ``max_new_tokens`` or the context limit with the token in flight sits the next step
+out (its end is known by counting); an end-of-sequence token is seen one step late, and the
+request's part in the step launched meanwhile is discarded (its pages were still its own when
+that step was launched, and whoever gets them next is ordered behind it on the stream);
+preemption first waits for the tokens in flight, since a preempted request is prefilled again
+over all of its tokens.
 """
 
 from __future__ import annotations
@@ -43,7 +55,7 @@ from dataclasses import dataclass, field
 from typing import Callable, Hashable, Sequence
 
 from ..cache import CacheManager, OutOfPages
-from .step import StepEntry
+from .step import FROM_DEVICE, StepEntry
 
 
 class SeqState:                     # heteroserve/worker/protocol.py:38-42
@@ -86,6 +98,7 @@ class SequenceState:
     prefill_tokens_computed: int = 0
     preemptions: int = 0
     finish_reason: str = ""
+    pending: int = 0                    # tokens sampled for it that the host has not read yet
     t_submit: float = 0.0
     t_admit: float = 0.0
     t_first_token: float = 0.0
@@ -130,14 +143,16 @@ class SchedulerStats:
 
 
 class Scheduler:
-    """Decides what each step runs.  ``step_fn(entries) -> list[int]`` runs a batch through
-    the step function with device sampling and returns one token per entry that wanted
-    one, in entry order; the scheduler owns everything around it."""
+    """Decides what each step runs.  ``step_fn(entries)`` runs a batch through the step
+    function with device sampling and returns one token per entry that wanted one, in entry
+    order — as a list, or as an object whose ``tokens_host()`` returns that list when asked
+    (see "Pipelining" above); the scheduler owns everything around it."""
 
-    def __init__(self, manager: CacheManager, step_fn: Callable[[list[StepEntry]], list[int]],
+    def __init__(self, manager: CacheManager, step_fn: Callable[[list[StepEntry]], object],
                  *, max_batch: int, max_prefill_tokens: int, max_ctx: int,
                  eos_token_id: int | None, policy: str = "prefill_first",
-                 vocab_size: int | None = None, clock: Callable[[], float] = time.perf_counter):
+                 vocab_size: int | None = None, clock: Callable[[], float] = time.perf_counter,
+                 pipeline: bool = False):
         if policy not in ("prefill_first", "mixed"):
             raise ValueError(f"unknown policy {policy!r}")
         self.manager = manager
@@ -153,6 +168,9 @@ class Scheduler:
         self.active: list[SequenceState] = []          # admitted, in admission order
         self.finished: list[SequenceState] = []
         self.stats = SchedulerStats()
+        self.pipeline = bool(pipeline)
+        self._inflight: tuple[list[Planned], object] | None = None   # launched, tokens unread
+        self._late_done: list[SequenceState] = []     # finished while a plan was being made
 
     # -- submission -----------------------------------------------------------
     def add(self, request: Request) -> SequenceState:
@@ -178,7 +196,7 @@ class Scheduler:
         return seq
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.active)
+        return bool(self.waiting or self.active or self._inflight is not None)
 
     # -- admission --------------------------------------------------------------
     def _admit(self) -> None:
@@ -246,12 +264,13 @@ class Scheduler:
         planned: list[Planned] = []
         running = [s for s in self.active if s.state == SeqState.RUNNING][: self.max_batch]
         for seq in running:
-            if seq.state != SeqState.RUNNING:       # preempted by an earlier iteration
-                continue
-            while True:
+            if seq.pending and self._ends_by_count(seq, seq.pending):
+                continue                            # its token in flight is its last
+            while seq.state == SeqState.RUNNING:    # else: preempted, or ended while we waited
                 try:
                     mgr.reserve(seq.req_id, seq.n_kv + 1)
-                    planned.append(Planned(seq, seq.n_kv, [seq.ctx[seq.n_kv]], True))
+                    tok = FROM_DEVICE if seq.pending else seq.ctx[seq.n_kv]
+                    planned.append(Planned(seq, seq.n_kv, [tok], True))
                     break
                 except OutOfPages:
                     victim = self._preempt_newest()
@@ -260,8 +279,17 @@ class Scheduler:
                     planned = [p for p in planned if p.seq is not victim]
         return planned
 
+    def _ends_by_count(self, seq: SequenceState, extra: int) -> bool:
+        """Would ``extra`` more tokens end the request whatever they are?"""
+        n = len(seq.output_ids) + extra
+        return (n >= seq.request.max_new_tokens
+                or len(seq.request.prompt_ids) + n >= self.max_ctx)
+
     def _preempt_newest(self) -> SequenceState | None:
         """Recompute-preemption of the newest running request (worker.py:738-757)."""
+        if self._inflight is not None:
+            # a preempted request is prefilled again over all its tokens: have them first
+            self._late_done.extend(self._resolve())
         running = [s for s in self.active if s.state == SeqState.RUNNING]
         if not running:
             return None
@@ -279,9 +307,17 @@ class Scheduler:
 
     # -- running a step -------------------------------------------------------------
     def step(self) -> list[SequenceState]:
-        """Plan and run one step; returns the requests that finished in it."""
+        """Plan and launch one step; returns the requests whose end became known in it.  With
+        ``pipeline`` the tokens of the step launched here are read in the NEXT call."""
         planned = self.plan()
+        done, self._late_done = self._late_done, []
+        # requests that ended while the plan waited for tokens in flight have left it
+        planned = [p for p in planned
+                   if p.seq.state in (SeqState.PREFILL, SeqState.RUNNING)]
         if not planned:
+            if self._inflight is not None:
+                done.extend(self._resolve())
+                return done
             if self.waiting and not self.active:
                 head = self.waiting[0]
                 if head.output_ids:
@@ -291,21 +327,18 @@ class Scheduler:
                     head.t_done = self.clock()
                     self.finished.append(head)
                     self.stats.finished += 1
-                    return [head]
+                    return done + [head]
                 raise RequestRefused(
                     f"request {head.req_id!r} cannot be admitted although nothing else is "
                     f"running: the pool is too small for it")
-            return []
+            return done
         entries = []
         for p in planned:
             r = p.seq.request
             entries.append(StepEntry(
                 p.seq.req_id, p.tokens, want=[len(p.tokens) - 1] if p.samples else (),
                 temperature=r.temperature, top_k=r.top_k, seed=r.seed))
-        tokens = self.step_fn(entries)
-        it = iter(tokens)
-        done: list[SequenceState] = []
-        now = self.clock()
+        result = self.step_fn(entries)
         n_dec = sum(1 for p in planned if len(p.tokens) == 1 and p.seq.state == SeqState.RUNNING)
         for p in planned:
             seq = p.seq
@@ -319,14 +352,7 @@ class Scheduler:
                     self.manager.publish(seq.req_id, seq.ctx[: seq.n_kv])
                     seq.state = SeqState.RUNNING
             if p.samples:
-                tok = int(next(it))
-                seq.output_ids.append(tok)
-                self.stats.tokens_generated += 1
-                if not seq.t_first_token:
-                    seq.t_first_token = now
-                if self._finished(seq, tok):
-                    self._finish(seq, now)
-                    done.append(seq)
+                seq.pending += 1
         self.stats.steps += 1
         if n_dec == len(planned):
             self.stats.decode_steps += 1
@@ -334,6 +360,39 @@ class Scheduler:
             self.stats.prefill_steps += 1
         else:
             self.stats.mixed_steps += 1
+        earlier, self._inflight = self._inflight, (planned, result)
+        if earlier is not None:
+            done.extend(self._read(earlier))
+        if not self.pipeline:
+            done.extend(self._resolve())
+        return done
+
+    def _resolve(self) -> list[SequenceState]:
+        """Read the tokens of the step in flight, if any."""
+        inflight, self._inflight = self._inflight, None
+        return self._read(inflight) if inflight is not None else []
+
+    def _read(self, inflight) -> list[SequenceState]:
+        planned, result = inflight
+        tokens = result.tokens_host() if hasattr(result, "tokens_host") else result
+        it = iter(tokens)
+        done: list[SequenceState] = []
+        now = self.clock()
+        for p in planned:
+            if not p.samples:
+                continue
+            tok = int(next(it))
+            seq = p.seq
+            if seq.state == SeqState.DONE:
+                continue            # ended (or aborted) while this step was in flight
+            seq.pending -= 1
+            seq.output_ids.append(tok)
+            self.stats.tokens_generated += 1
+            if not seq.t_first_token:
+                seq.t_first_token = now
+            if self._finished(seq, tok):
+                self._finish(seq, now)
+                done.append(seq)
         return done
 
     def _finished(self, seq: SequenceState, tok: int) -> bool:

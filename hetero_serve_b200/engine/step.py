@@ -39,6 +39,12 @@ class StepError(RuntimeError):
     pass
 
 
+# As the first token of an entry: "the token the device sampled for this request last", which
+# the step reads from device memory.  It lets a decode step be launched before the host has
+# read the previous step's tokens.
+FROM_DEVICE = -1
+
+
 @dataclass
 class StepEntry:
     """The next tokens of one request, and which of their logits are wanted."""
@@ -60,14 +66,27 @@ class StepResult:
     n_tokens: int = 0
     _with_status: torch.Tensor | None = None
     _runner: "Runner | None" = None
+    _host: torch.Tensor | None = None
+    _copied: "torch.cuda.Event | None" = None
+
+    def start_fetch(self) -> None:
+        """Enqueue the device-to-host copy of the sampled tokens (and the status word) behind
+        the step, without waiting for it.  Must be called before the next step is launched: the
+        device buffer is reused."""
+        if self._with_status is None or self._host is not None:
+            return
+        self._host, self._copied = self._runner._fetch(self._with_status)
 
     def tokens_host(self) -> list[int]:
         """The sampled tokens as Python ints: one device-to-host copy that also brings the
         kernels' status word, which is checked."""
         if self._with_status is None:
             return []
-        host = self._with_status.cpu().tolist()
+        self.start_fetch()
+        if self._copied is not None:
+            self._copied.synchronize()
         n = self.tokens.shape[0]
+        host = self._host.tolist()          # [bucketed rows..., status word]
         if host[-1]:
             self._runner.raise_status(host[-1])
         return host[:n]
@@ -105,6 +124,7 @@ class Layout:
         self.logit_rows = take(W)
         self.samp_temp, self.samp_topk = take(W), take(W)
         self.samp_seed_lo, self.samp_seed_hi, self.samp_pos = take(W), take(W), take(W)
+        self.samp_slot = take(W)
         self.tables = [take(R * mp) for mp in self.max_pages]
         self.plan = take(plan_ints)
         self.plan_ints = plan_ints
@@ -137,6 +157,8 @@ class StepContext:
         self.samp_seed_lo = meta[L.samp_seed_lo:L.samp_seed_lo + L.W]
         self.samp_seed_hi = meta[L.samp_seed_hi:L.samp_seed_hi + L.W]
         self.samp_pos = meta[L.samp_pos:L.samp_pos + L.W]
+        self.samp_slot = meta[L.samp_slot:L.samp_slot + L.W]
+        self.feedback = runner.feedback
         self.tables = [meta[o:o + L.R * mp].view(L.R, mp)
                        for o, mp in zip(L.tables, L.max_pages)]
         self.plan = None          # work lists for the specialised attention kernels, if any
@@ -219,6 +241,10 @@ class Runner:
         self.max_positions = model.spec.max_positions
         self.max_pages = [self.manager.pages_for(self.max_positions) for _ in model.cache_groups]
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # the token each request sampled last, by state slot: what FROM_DEVICE reads
+        self.feedback = torch.zeros(max(1, max_requests), dtype=torch.int32, device=self.device)
+        self._fetch_ring: list[torch.Tensor] = []
+        self._fetch_next = 0
         if hasattr(ops, "status"):
             ops.status = self.status       # kernels that take no status argument report here
         self.cuda = self.device.type == "cuda"
@@ -316,6 +342,7 @@ class Runner:
             hm[lay.samp_temp:lay.samp_temp + W] = 0
             hm[lay.samp_topk:lay.samp_topk + W] = 0
             hm[lay.samp_pos:lay.samp_pos + W] = 0
+            hm[lay.samp_slot:lay.samp_slot + W] = -1
         for gi, mp in enumerate(lay.max_pages):
             hm[lay.tables[gi]:lay.tables[gi] + R * mp] = -1
         hm[lay.req_len:lay.req_len + R] = 0
@@ -329,15 +356,19 @@ class Runner:
         for r, (e, start) in enumerate(zip(entries, starts)):
             n = len(e.tokens)
             toks = np.asarray(e.tokens, dtype=np.int64)
-            if toks.min() < 0 or toks.max() >= vocab:
+            slot = mgr.slot(e.req_id)
+            from_device = int(toks[0]) == FROM_DEVICE
+            known = toks[1:] if from_device else toks
+            if known.size and (known.min() < 0 or known.max() >= vocab):
                 raise StepError(f"request {e.req_id!r}: token id outside [0, {vocab})")
             hm[lay.tok_ids + t:lay.tok_ids + t + n] = toks
+            if from_device:
+                hm[lay.tok_ids + t] = -(slot + 1)
             hm[lay.tok_pos + t:lay.tok_pos + t + n] = np.arange(start, start + n)
             hm[lay.tok_req + t:lay.tok_req + t + n] = r
             hm[lay.req_start + r] = t
             hm[lay.req_len + r] = n
             hm[lay.req_ctx + r] = start + n
-            slot = mgr.slot(e.req_id)
             hm[lay.req_slot + r] = slot
             for gi, mp in enumerate(lay.max_pages):
                 tab = mgr.table(e.req_id, gi)
@@ -351,6 +382,8 @@ class Runner:
                 hm[lay.samp_seed_lo + w_i] = np.array(seed & 0xFFFFFFFF, dtype=np.uint32).view(np.int32)
                 hm[lay.samp_seed_hi + w_i] = np.array(seed >> 32, dtype=np.uint32).view(np.int32)
                 hm[lay.samp_pos + w_i] = start + w + 1     # position the new token will take
+                if w == n - 1:                             # the request's next token
+                    hm[lay.samp_slot + w_i] = slot
                 rows.append((e.req_id, w))
                 w_i += 1
             host_batch.append((e.req_id, slot, start, n))
@@ -385,8 +418,12 @@ class Runner:
                 from ..kernels.ops import AttentionPlan
                 ctx.plan = AttentionPlan(dev[lay.plan:lay.plan + lay.plan_ints], T, *plan_shape)
             if self.use_graphs and not self.model.state_shapes:
-                # run once eagerly (loads kernels, sizes buffers), then capture and replay
+                # run once eagerly (loads kernels, sizes buffers), then capture and replay.  The
+                # replay must see the same inputs as the eager run: all of them come from the
+                # metadata block except the tokens kept on the device, which sampling overwrites
+                kept = self.feedback.clone()
                 self._forward(ctx, sample)
+                self.feedback.copy_(kept)
                 torch.cuda.synchronize(self.device)
                 graph = torch.cuda.CUDAGraph()
                 # An object freed by the garbage collector in the middle of a capture (an
@@ -430,9 +467,29 @@ class Runner:
             W = ctx.n_logit_rows
             tokens = ctx.buffer("sampled", (W + 1,), torch.int32)
             self.ops.sample(tokens, logits, ctx.samp_temp, ctx.samp_topk, ctx.samp_seed_lo,
-                            ctx.samp_seed_hi, ctx.samp_pos)
+                            ctx.samp_seed_hi, ctx.samp_pos, feedback=self.feedback,
+                            feedback_slot=ctx.samp_slot)
             tokens[W:].copy_(self.status)
         return logits, tokens
+
+    def _fetch(self, dev: torch.Tensor):
+        """Start copying ``dev`` (int32) to pinned host memory behind the work enqueued so far;
+        returns (host tensor, event).  Four buffers rotate: a result is to be read before four
+        later ones have been fetched."""
+        n = dev.shape[0]
+        if not self.cuda:
+            return dev.clone(), None
+        if len(self._fetch_ring) < 4:
+            self._fetch_ring.append(torch.empty(1024, dtype=torch.int32).pin_memory())
+        i = self._fetch_next % 4
+        self._fetch_next += 1
+        if self._fetch_ring[i].shape[0] < n:
+            self._fetch_ring[i] = torch.empty(_bucket(n, 1024), dtype=torch.int32).pin_memory()
+        host = self._fetch_ring[i][:n]
+        host.copy_(dev, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return host, ev
 
     def check_status(self) -> None:
         """Read the status word the kernels OR their refusals into (synchronises)."""

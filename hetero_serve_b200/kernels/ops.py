@@ -115,7 +115,7 @@ def load_library():
 def _declare(lib) -> None:
     P, I, F = c_void_p, c_int, c_float
     sig = {
-        "hs_embed": [P, P, P, P, P, P, I, I, I, I, I, P, P],
+        "hs_embed": [P, P, P, P, P, P, I, I, I, I, I, P, I, P, P],
         "hs_layernorm": [P, P, P, P, P, I, I, F, I, P],
         "hs_linear_simt": [P, P, P, P, P, I, I, I, I, I, I, P],
         "hs_linear_tcgen05": [P, P, P, P, P, I, I, I, I, I, I, P, P, P, P],
@@ -129,7 +129,7 @@ def _declare(lib) -> None:
         "hs_attention_prefill": [P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P, P],
         "hs_attention_prefill_tc": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, P, P],
         "hs_argmax": [P, P, I, I, P],
-        "hs_sample": [P, P, P, P, P, P, P, I, I, P],
+        "hs_sample": [P, P, P, P, P, P, P, I, I, P, P, P],
     }
     for name, argtypes in sig.items():
         fn = getattr(lib, name)
@@ -200,8 +200,9 @@ class CudaOps:
         return torch.cuda.current_stream().cuda_stream
 
     # -- embedding and norm -------------------------------------------------
-    def embed(self, x, ids, pos, req, wte, wpe, status):
-        """x[t] = wte[ids[t]] (+ wpe[pos[t]]); rows with req[t] < 0 become zero."""
+    def embed(self, x, ids, pos, req, wte, wpe, status, feedback=None):
+        """x[t] = wte[ids[t]] (+ wpe[pos[t]]); rows with req[t] < 0 become zero.  With
+        ``feedback`` (int32 on the device) an id ``-(s + 1)`` stands for ``feedback[s]``."""
         _want(x, "x", torch.float32, 2)
         _want(wte, "wte", _FLOATS, 2)
         n, width = x.shape
@@ -217,9 +218,12 @@ class CudaOps:
             if wpe.shape[1] != width:
                 raise KernelError(f"wpe width {wpe.shape[1]} != x width {width}")
             n_pos = wpe.shape[0]
+        if feedback is not None:
+            _want(feedback, "feedback", torch.int32, 1)
         self.launches += 1
         _check(self.lib.hs_embed(_ptr(x), _ptr(ids), _ptr(pos), _ptr(req), _ptr(wte), _ptr(wpe),
-                                 n, width, wte.shape[0], n_pos, _DT[wte.dtype], _ptr(status),
+                                 n, width, wte.shape[0], n_pos, _DT[wte.dtype], _ptr(feedback),
+                                 0 if feedback is None else feedback.shape[0], _ptr(status),
                                  self._stream()), "embed")
 
     def layernorm(self, out, x, gamma, beta, eps, rows=None):
@@ -570,9 +574,12 @@ class CudaOps:
         self.launches += 1
         _check(self.lib.hs_argmax(_ptr(out), _ptr(logits), rows, vocab, self._stream()), "argmax")
 
-    def sample(self, out, logits, temperature, top_k, seed_lo, seed_hi, position):
+    def sample(self, out, logits, temperature, top_k, seed_lo, seed_hi, position,
+               feedback=None, feedback_slot=None):
         """Per row: argmax if temperature <= 0, else a draw from softmax(logits/temperature)
-        restricted to the top_k largest when 0 < top_k < vocab."""
+        restricted to the top_k largest when 0 < top_k < vocab.  With ``feedback`` and
+        ``feedback_slot`` row i also stores its token to ``feedback[feedback_slot[i]]`` (slots
+        below zero are skipped)."""
         _want(out, "out", torch.int32, 1)
         _want(logits, "logits", torch.float32, 2)
         rows, vocab = logits.shape
@@ -584,7 +591,14 @@ class CudaOps:
                 raise KernelError(f"sample: {nm} shorter than the rows")
         if out.shape[0] < rows or temperature.shape[0] < rows:
             raise KernelError("sample: out/temperature shorter than the rows")
+        if (feedback is None) != (feedback_slot is None):
+            raise KernelError("sample: feedback and feedback_slot come together")
+        if feedback is not None:
+            _want(feedback, "feedback", torch.int32, 1)
+            _want(feedback_slot, "feedback_slot", torch.int32, 1)
+            if feedback_slot.shape[0] < rows:
+                raise KernelError("sample: feedback_slot shorter than the rows")
         self.launches += 1
         _check(self.lib.hs_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(top_k),
                                   _ptr(seed_lo), _ptr(seed_hi), _ptr(position), rows, vocab,
-                                  self._stream()), "sample")
+                                  _ptr(feedback), _ptr(feedback_slot), self._stream()), "sample")

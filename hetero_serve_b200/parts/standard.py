@@ -56,7 +56,7 @@ class TokenEmbedding(Embedding):
 
     def forward(self, ctx, x, position):
         ctx.ops.embed(x, ctx.tok_ids, ctx.tok_pos, ctx.tok_req, self.table,
-                      position.embedding_table(), ctx.status)
+                      position.embedding_table(), ctx.status, feedback=ctx.feedback)
 
 
 class LayerNorm(Norm):

@@ -28,13 +28,16 @@ class PlainOps:
     def __init__(self, compute_dtype=torch.float64):
         self.cd = compute_dtype
 
-    def embed(self, x, ids, pos, req, wte, wpe, status):
+    def embed(self, x, ids, pos, req, wte, wpe, status, feedback=None):
         n = x.shape[0]
         for t in range(n):
             if int(req[t]) < 0:
                 x[t] = 0
                 continue
-            row = wte[int(ids[t])].to(self.cd)
+            tok = int(ids[t])
+            if tok < 0 and feedback is not None:
+                tok = int(feedback[-(tok + 1)])
+            row = wte[tok].to(self.cd)
             if wpe is not None:
                 row = row + wpe[int(pos[t])].to(self.cd)
             x[t] = row.to(x.dtype)
@@ -113,8 +116,11 @@ class PlainOps:
         rows = logits.shape[0]
         out[:rows] = torch.argmax(logits, dim=-1).to(torch.int32)
 
-    def sample(self, out, logits, temperature, top_k, seed_lo, seed_hi, position):
+    def sample(self, out, logits, temperature, top_k, seed_lo, seed_hi, position,
+               feedback=None, feedback_slot=None):
         for r in range(logits.shape[0]):
             seed = (int(seed_lo[r]) & 0xFFFFFFFF) | ((int(seed_hi[r]) & 0xFFFFFFFF) << 32)
             u = uniform_for(seed, int(position[r]))
             out[r] = sample_token(logits[r].cpu(), float(temperature[r]), int(top_k[r]), u)
+            if feedback is not None and int(feedback_slot[r]) >= 0:
+                feedback[int(feedback_slot[r])] = out[r]

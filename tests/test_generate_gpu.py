@@ -151,6 +151,42 @@ def test_eos_and_context_limit(lively):
     assert r.output_ids == plain_gpt2.greedy_generate(cfg, w, long, 50)[:len(r.output_ids)]
 
 
+@pytest.mark.parametrize("policy", ["prefill_first", "mixed"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_pipelined_steps_change_no_token(lively, dtype, policy):
+    """With ``pipeline`` a decode step is launched before the host has read the token the step
+    before it sampled (the step takes it from device memory).  Sampled and greedy requests, an
+    end-of-sequence token met on the way, few pages (preemption) and CUDA graphs: every token is
+    the one the engine gives when it reads each step's tokens before the next launch."""
+    d, cfg, w = lively["tiny_a"]
+    prompts = _prompts(cfg, (30, 28, 25, 7, 3), 21)
+    free = plain_gpt2.greedy_generate(cfg, w, prompts[0], 30)
+    k = next(i for i in range(5, 30) if free[i] not in free[:i])     # first met at place k
+    cfg2 = dict(cfg, eos_token_id=free[k])
+    import pathlib, shutil, tempfile
+    with tempfile.TemporaryDirectory() as t:
+        shutil.copy(d + "/model.safetensors", t)
+        pathlib.Path(t, "config.json").write_text(json.dumps(cfg2))
+        outs = {}
+        for pipeline in (False, True):
+            eng = LLMEngine(t, EngineConfig(dtype=dtype, num_blocks=10, max_batch=4,
+                                            max_prefill_tokens=32, prefix_cache=False,
+                                            policy=policy, pipeline=pipeline))
+            seqs = [eng.submit_nowait(Request(p, max_new_tokens=30, temperature=0.9 * (i % 2),
+                                              top_k=12 * (i % 2), seed=3 + i,
+                                              stop_at_eos=(i != 1)))
+                    for i, p in enumerate(prompts)]
+            recs = eng.run_until_done()
+            outs[pipeline] = [(s.output_ids, s.finish_reason) for s in seqs]
+            assert sum(r.preemptions for r in recs) >= 1
+            eng.runner.manager.check()
+            assert eng.runner.manager.free_slots() == eng.config.live_requests
+        assert outs[True] == outs[False]
+        if dtype == "float32":
+            assert outs[True][0] == (free[:k + 1], "eos")
+        assert any(r == "max_new_tokens" for _, r in outs[True])
+
+
 def test_command_line(lively):
     d, cfg, w = lively["tiny_a"]
     p = _prompts(cfg, (12,), 19)[0]

@@ -493,3 +493,45 @@ def test_sample_distribution(ops):
     freq = torch.bincount(out.long(), minlength=vocab).float() / n
     assert (freq - p).abs().max() < 0.03
     assert freq[p == 0].sum() == 0
+
+
+def test_tokens_kept_on_the_device_feed_the_next_embedding(ops, plain):
+    """Sampling leaves a row's token in ``feedback[slot]`` (slots below zero are skipped); the
+    embedding takes ``feedback[s]`` for an id ``-(s + 1)`` and checks it like any other id."""
+    torch.manual_seed(3)
+    V, E = 300, 48
+    lg = torch.randn(5, V, device=DEV)
+    temp = torch.tensor([0.0, 0.9, 0.0, 1.2, 0.0], device=DEV)
+    k = _i32([0, 0, 0, 7, 0])
+    z = torch.zeros(5, dtype=torch.int32, device=DEV)
+    pos = _i32([4, 9, 1, 30, 2])
+    slots = _i32([3, -1, 0, 6, -1])
+    fb = torch.full((8,), 77, dtype=torch.int32, device=DEV)
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops.sample(out, lg, temp, k, z + 11, z, pos, feedback=fb, feedback_slot=slots)
+    plain_out = torch.empty(5, dtype=torch.int32)
+    plain.sample(plain_out, lg.cpu(), temp.cpu(), k.cpu(), (z + 11).cpu(), z.cpu(), pos.cpu())
+    assert out.cpu().tolist() == plain_out.tolist()
+    want = [77] * 8
+    want[3], want[0], want[6] = int(out[0]), int(out[2]), int(out[3])
+    assert fb.cpu().tolist() == want
+    # the embedding of ids given directly and through the device copy agree bit for bit
+    wte = torch.randn(V, E, device=DEV)
+    wpe = torch.randn(40, E, device=DEV)
+    st = _status()
+    direct = torch.empty(4, E, device=DEV)
+    via = torch.empty(4, E, device=DEV)
+    p4, r4 = _i32([5, 10, 2, 31]), _i32([0, 1, 2, 3])
+    ops.embed(direct, _i32([want[3], 12, want[0], want[6]]), p4, r4, wte, wpe, st)
+    ops.embed(via, _i32([-(3 + 1), 12, -(0 + 1), -(6 + 1)]), p4, r4, wte, wpe, st, feedback=fb)
+    assert st.item() == 0 and torch.equal(direct, via)
+    # a slot outside the table, a negative id without a table, a kept token outside the vocabulary
+    ops.embed(via, _i32([-9, 1, 1, 1]), p4, r4, wte, wpe, st, feedback=fb)
+    assert st.item() == 1 and via[0].abs().max() == 0
+    st.zero_()
+    ops.embed(via, _i32([-1, 1, 1, 1]), p4, r4, wte, wpe, st)
+    assert st.item() == 1
+    st.zero_()
+    fb[2] = V
+    ops.embed(via, _i32([-3, 1, 1, 1]), p4, r4, wte, wpe, st, feedback=fb)
+    assert st.item() == 1 and via[0].abs().max() == 0

@@ -231,3 +231,143 @@ def test_abort_gives_everything_back():
     assert sch.abort(a.req_id) and sch.abort(b.req_id) and not sch.abort("nobody")
     mgr.check()
     assert not sch.has_work() and mgr.free_slots() == 8
+
+
+# ------------------------------------------------------------------ pipelined steps
+class LazyFakeStep(FakeStep):
+    """Like FakeStep, but the tokens come as an object that is read later, and an entry may
+    bring FROM_DEVICE: the fake keeps "device memory" of the last token per request."""
+
+    def __init__(self, manager):
+        super().__init__(manager)
+        self.device_last = {}
+        self.unread = 0           # results handed out whose tokens have not been asked for
+        self.max_unread = 0
+
+    def __call__(self, entries):
+        from hetero_serve_b200.engine.step import FROM_DEVICE
+        fed = []
+        for e in entries:
+            toks = list(e.tokens)
+            if toks[0] == FROM_DEVICE:
+                toks[0] = self.device_last[e.req_id]
+            assert all(0 <= t < VOCAB for t in toks)
+            fed.append(type(e)(e.req_id, toks, e.want, e.temperature, e.top_k, e.seed))
+        out = super().__call__(fed)
+        it = iter(out)
+        for e in entries:
+            for w in e.want:
+                tok = next(it)
+                if w == len(e.tokens) - 1:
+                    self.device_last[e.req_id] = tok
+        fake = self
+        fake.unread += 1
+        fake.max_unread = max(fake.max_unread, fake.unread)
+
+        class Later:
+            def tokens_host(self_inner):
+                fake.unread -= 1
+                return out
+        return Later()
+
+
+def make_pipelined(pipeline, **kw):
+    num_pages, page_size = kw.pop("num_pages", 64), kw.pop("page_size", 4)
+    mgr = CacheManager([GroupSpec()], num_pages, page_size, kw.pop("max_requests", 8),
+                       kw.pop("prefix_cache", True))
+    fake = LazyFakeStep(mgr)
+    sch = Scheduler(mgr, fake, max_batch=kw.pop("max_batch", 8),
+                    max_prefill_tokens=kw.pop("budget", 24), max_ctx=kw.pop("max_ctx", 200),
+                    eos_token_id=kw.pop("eos", None), policy=kw.pop("policy", "prefill_first"),
+                    vocab_size=VOCAB, pipeline=pipeline)
+    assert not kw
+    return sch, fake, mgr
+
+
+def test_pipelined_decoding_launches_before_it_reads():
+    sch, fake, mgr = make_pipelined(True)
+    seq = sch.add(Request(prompt(10), max_new_tokens=6))
+    run(sch, mgr)
+    assert seq.output_ids == expected_outputs(prompt(10), 6)
+    assert fake.max_unread == 2          # a step was launched while the previous one was unread
+    # the prompt, then five decode steps: the last token's end is known by counting, so no
+    # step is launched for it
+    assert [len(step) for step in fake.log] == [1] * 6
+    assert mgr.pages_free() == 64 and mgr.free_slots() == 8
+    sync, fake2, _ = make_pipelined(False)
+    sync.add(Request(prompt(10), max_new_tokens=6))
+    run(sync, _)
+    shape = lambda log: [[r[1:] for r in step] for step in log]
+    assert fake2.max_unread == 1 and shape(fake2.log) == shape(fake.log)
+
+
+def test_pipelined_sees_eos_one_step_late_and_discards_the_extra_step():
+    want = expected_outputs(prompt(9, base=5), 30)
+    eos = want[3]
+    assert eos not in want[:3]
+    sch, fake, mgr = make_pipelined(True, eos=eos)
+    seq = sch.add(Request(prompt(9, base=5), max_new_tokens=30))
+    other = sch.add(Request(prompt(7, base=2), max_new_tokens=12))
+    run(sch, mgr)
+    assert seq.output_ids == want[:4] and seq.finish_reason == "eos"
+    assert other.output_ids == expected_outputs(prompt(7, base=2), 12, eos=eos)
+    # one more step than it needed ran for the request that met eos
+    assert sum(1 for step in fake.log for r in step if r[0] == seq.req_id) == 1 + 4
+    assert mgr.pages_free() == 64 and mgr.free_slots() == 8
+
+
+@pytest.mark.parametrize("policy", ["prefill_first", "mixed"])
+@pytest.mark.parametrize("seed", range(6))
+def test_pipelined_and_plain_scheduling_give_the_same_tokens(policy, seed):
+    """Random workloads with too few pages (preemption), eos and the context limit: the
+    pipelined scheduler gives every request the tokens the plain one gives it."""
+    import random
+    rng = random.Random(seed)
+    reqs = []
+    for i in range(10):
+        n = rng.randint(1, 40)
+        reqs.append(dict(prompt_ids=[rng.randrange(VOCAB) for _ in range(n)],
+                         max_new_tokens=rng.randint(1, 30), seed=rng.randrange(100),
+                         stop_at_eos=rng.random() < 0.7))
+    outs = {}
+    for pipeline in (False, True):
+        sch, fake, mgr = make_pipelined(pipeline, num_pages=24, page_size=4, max_requests=4,
+                                        max_batch=4, budget=16, max_ctx=60, eos=11,
+                                        policy=policy)
+        seqs = []
+        pending = list(reqs)
+        steps = 0
+        while pending or sch.has_work():
+            # requests arrive while others run
+            for _ in range(rng.randint(0, 2) if pending else 0):
+                if pending:
+                    seqs.append(sch.add(Request(**pending.pop(0))))
+            if sch.has_work():
+                sch.step()
+                mgr.check()
+            steps += 1
+            assert steps < 5000
+        outs[pipeline] = [(s.output_ids, s.finish_reason) for s in seqs]
+        assert mgr.pages_free() == 24 and mgr.free_slots() == 4
+        for s, r in zip(seqs, reqs):
+            full = expected_outputs(r["prompt_ids"], r["max_new_tokens"], r["seed"],
+                                    eos=11 if r["stop_at_eos"] else None, max_ctx=60)
+            if s.finish_reason != "out_of_pages":
+                assert s.output_ids == full
+            else:
+                assert s.output_ids == full[:len(s.output_ids)]
+        assert sch.stats.preemptions > 0          # the pool is small on purpose
+
+
+def test_abort_while_a_token_is_in_flight():
+    sch, fake, mgr = make_pipelined(True)
+    a = sch.add(Request(prompt(6), max_new_tokens=20))
+    b = sch.add(Request(prompt(5, base=9), max_new_tokens=5))
+    for _ in range(4):
+        sch.step()
+    assert a.pending
+    assert sch.abort(a.req_id)
+    run(sch, mgr)
+    assert a.finish_reason == "aborted"
+    assert b.output_ids == expected_outputs(prompt(5, base=9), 5)
+    assert mgr.pages_free() == 64 and mgr.free_slots() == 8
