@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(TA_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                             const __grid_constant__ CUtensorMap map_kv,
                             const PrefillTcParams p) {
+  pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
@@ -114,6 +115,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();          // queries and this step's keys and values come from earlier kernels
 
   // running counts of completed phases, kept identically by every role
   uint32_t n_item = 0;        // items processed by this CTA
@@ -506,7 +508,9 @@ HS_EXPORT int hs_attention_prefill_tc(void* out, const void* qkv, const void* po
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
   }
   cudaStream_t st = (cudaStream_t)stream;
-  attention_prefill_tc_kernel<<<sms, TA_THREADS, TA_SMEM, st>>>(mq, mkv, p);
+  cudaError_t le = hs_launch(attention_prefill_tc_kernel, dim3(sms), dim3(TA_THREADS),
+                             (size_t)TA_SMEM, st, hs_pdl_enabled(), mq, mkv, p);
+  if (le != cudaSuccess) return (int)le;
   HS_LAUNCH_CHECK();
   return HS_OK;
 }

@@ -29,15 +29,18 @@ template <typename T>
 __global__ void kv_append_kernel(T* __restrict__ pool, const T* __restrict__ qkv,
                                  const int* __restrict__ table, const int* __restrict__ tok_pos,
                                  const int* __restrict__ tok_req, AttnGeom g, int* status) {
+  pdl_trigger();
   const int t = blockIdx.x;
   const int r = tok_req[t];
-  if (r < 0) return;
   const int p = tok_pos[t];
-  if (p < 0 || p / g.page_size >= g.max_pages) {
+  const bool pos_ok = r >= 0 && p >= 0 && p / g.page_size < g.max_pages;
+  const int page = pos_ok ? table[(size_t)r * g.max_pages + p / g.page_size] : -1;
+  pdl_wait();           // the rows of `qkv` are what the previous kernel wrote
+  if (r < 0) return;
+  if (!pos_ok) {
     if (threadIdx.x == 0) atomicOr(status, HS_STATUS_BAD_POSITION);
     return;
   }
-  const int page = table[(size_t)r * g.max_pages + p / g.page_size];
   if (page < 0 || page >= g.num_pages) {
     if (threadIdx.x == 0) atomicOr(status, HS_STATUS_BAD_PAGE);
     return;
@@ -176,14 +179,18 @@ HS_EXPORT int hs_kv_append(void* pool, const void* qkv, const int* table, const 
   if (n_tokens <= 0) return HS_OK;
   cudaStream_t st = (cudaStream_t)stream;
   int threads = n_kv_heads * head_dim >= 1024 ? 128 : 64;
+  cudaError_t le;
   if (dtype == HS_DT_F32)
-    hs::kv_append_kernel<float><<<n_tokens, threads, 0, st>>>(
-        (float*)pool, (const float*)qkv, table, tok_pos, tok_req, g, status);
+    le = hs_launch(hs::kv_append_kernel<float>, dim3(n_tokens), dim3(threads), 0, st,
+                   hs_pdl_enabled(), (float*)pool, (const float*)qkv, table, tok_pos, tok_req, g,
+                   status);
   else if (dtype == HS_DT_BF16)
-    hs::kv_append_kernel<__nv_bfloat16><<<n_tokens, threads, 0, st>>>(
-        (__nv_bfloat16*)pool, (const __nv_bfloat16*)qkv, table, tok_pos, tok_req, g, status);
+    le = hs_launch(hs::kv_append_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, st,
+                   hs_pdl_enabled(), (__nv_bfloat16*)pool, (const __nv_bfloat16*)qkv, table,
+                   tok_pos, tok_req, g, status);
   else
     return HS_ERR_UNSUPPORTED;
+  if (le != cudaSuccess) return (int)le;
   HS_LAUNCH_CHECK();
   return HS_OK;
 }

@@ -35,6 +35,7 @@
 #define HS_EXPORT extern "C" __attribute__((visibility("default")))
 
 unsigned long long* hs_timing_buffer();   // embed_norm.cu
+bool hs_pdl_enabled();                    // embed_norm.cu: programmatic dependent launch on?
 
 #define HS_LAUNCH_CHECK()                      \
   do {                                         \

@@ -57,6 +57,7 @@ __global__ void layernorm_kernel(TO* __restrict__ out, const float* __restrict__
   const int o = blockIdx.x;
   const int src = rows ? rows[o] : o;
   const float* xr = x + (size_t)src * width;
+  pdl_wait();
   float s = 0.f;
   for (int e = threadIdx.x; e < width; e += THREADS) {
     float v = xr[e];
@@ -112,6 +113,7 @@ layernorm_warp_kernel(TO* __restrict__ out, const float* __restrict__ x,
   const int src = rows ? rows[o] : o;
   const float4* xr = (const float4*)(x + (size_t)src * width);
   const int nf4 = width / 4;
+  pdl_wait();                      // x is what the previous kernel wrote
   float4 v[LN_F4];
 #pragma unroll
   for (int i = 0; i < LN_F4; ++i)
@@ -186,14 +188,18 @@ HS_EXPORT int hs_layernorm(void* out, const float* x, const float* gamma, const 
   if (width % 4 == 0 && width <= hs::LN_F4 * 128 && !((uintptr_t)x & 15) && !((uintptr_t)out & 15) &&
       !((uintptr_t)gamma & 15) && !((uintptr_t)beta & 15)) {
     const int grid = (n_rows + hs::LN_ROWS_PER_CTA - 1) / hs::LN_ROWS_PER_CTA;
+    cudaError_t le;
+    const bool pdl = hs_pdl_enabled();
     if (out_dtype == HS_DT_F32)
-      hs::layernorm_warp_kernel<float><<<grid, hs::LN_ROWS_PER_CTA * 32, 0, st0>>>(
-          (float*)out, x, gamma, beta, rows, n_rows, width, eps);
+      le = hs_launch(hs::layernorm_warp_kernel<float>, dim3(grid), dim3(hs::LN_ROWS_PER_CTA * 32),
+                     0, st0, pdl, (float*)out, x, gamma, beta, rows, n_rows, width, eps);
     else if (out_dtype == HS_DT_BF16)
-      hs::layernorm_warp_kernel<__nv_bfloat16><<<grid, hs::LN_ROWS_PER_CTA * 32, 0, st0>>>(
-          (__nv_bfloat16*)out, x, gamma, beta, rows, n_rows, width, eps);
+      le = hs_launch(hs::layernorm_warp_kernel<__nv_bfloat16>, dim3(grid),
+                     dim3(hs::LN_ROWS_PER_CTA * 32), 0, st0, pdl, (__nv_bfloat16*)out, x, gamma,
+                     beta, rows, n_rows, width, eps);
     else
       return HS_ERR_UNSUPPORTED;
+    if (le != cudaSuccess) return (int)le;
     HS_LAUNCH_CHECK();
     return HS_OK;
   }
@@ -205,12 +211,16 @@ HS_EXPORT int hs_layernorm(void* out, const float* x, const float* gamma, const 
     auto k = hs::layernorm_kernel<float, THREADS>;
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<n_rows, THREADS, smem, st>>>((float*)out, x, gamma, beta, rows, width, eps);
+    cudaError_t le = hs_launch(k, dim3(n_rows), dim3(THREADS), smem, st, hs_pdl_enabled(),
+                               (float*)out, x, gamma, beta, rows, width, eps);
+    if (le != cudaSuccess) return (int)le;
   } else if (out_dtype == HS_DT_BF16) {
     auto k = hs::layernorm_kernel<__nv_bfloat16, THREADS>;
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<n_rows, THREADS, smem, st>>>((__nv_bfloat16*)out, x, gamma, beta, rows, width, eps);
+    cudaError_t le = hs_launch(k, dim3(n_rows), dim3(THREADS), smem, st, hs_pdl_enabled(),
+                               (__nv_bfloat16*)out, x, gamma, beta, rows, width, eps);
+    if (le != cudaSuccess) return (int)le;
   } else {
     return HS_ERR_UNSUPPORTED;
   }
@@ -223,3 +233,12 @@ HS_EXPORT int hs_layernorm(void* out, const float* x, const float* gamma, const 
 static unsigned long long* g_timing_buffer = nullptr;
 HS_EXPORT void hs_set_timing_buffer(unsigned long long* buf) { g_timing_buffer = buf; }
 unsigned long long* hs_timing_buffer() { return g_timing_buffer; }
+
+// Programmatic dependent launch for the kernels that take no `pdl` argument of their own
+// (LayerNorm, the tcgen05 linear, the cache append, the prompt attention, sampling): each of
+// them waits (griddepcontrol.wait) before it first reads what an earlier kernel wrote, so with
+// the switch on they are launched with the programmatic-serialization attribute and their
+// prologue overlaps the tail of the kernel before them.  Off by default.
+static bool g_pdl = false;
+HS_EXPORT void hs_set_pdl(int on) { g_pdl = on != 0; }
+bool hs_pdl_enabled() { return g_pdl; }

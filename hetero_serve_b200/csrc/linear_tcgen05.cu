@@ -135,6 +135,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;
   constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;          // 64 .. 512, a power of two
 
+  pdl_trigger();       // the next kernel may set itself up while this one runs
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -154,6 +155,9 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above (barriers, tensor memory) touches nothing an earlier kernel writes; from
+  // here on activations, the residual stream and the split-k scratch are read.
+  pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -398,7 +402,9 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const TcParams& 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, TC_THREADS, smem, st>>>(ma, mw, p);
+  cudaError_t le = hs_launch(kern, dim3(grid), dim3(TC_THREADS), (size_t)smem, st,
+                             hs_pdl_enabled(), ma, mw, p);
+  if (le != cudaSuccess) return (int)le;
   HS_LAUNCH_CHECK();
   return HS_OK;
 }

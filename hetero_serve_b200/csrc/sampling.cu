@@ -167,6 +167,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
   const int rowi = blockIdx.x;
   const float* row = logits + (size_t)rowi * vocab;
   const float temp = temperature[rowi];
+  pdl_wait();                       // the logits are what the previous kernel wrote
   const ArgMax top = block_argmax(row, vocab);
   // a row with a feedback slot also leaves its token there, for the next step's embedding
   const int fb = (feedback != nullptr && feedback_slot != nullptr) ? feedback_slot[rowi] : -1;
@@ -279,8 +280,10 @@ HS_EXPORT int hs_sample(int* out, const float* logits, const float* temperature,
     return HS_ERR_ARGUMENT;
   if (rows <= 0) return HS_OK;
   if (vocab <= 0) return HS_ERR_ARGUMENT;
-  hs::sample_kernel<<<rows, hs::SM_THREADS, 0, (cudaStream_t)stream>>>(
-      out, logits, temperature, top_k, seed_lo, seed_hi, position, vocab, feedback, feedback_slot);
+  cudaError_t le = hs_launch(hs::sample_kernel, dim3(rows), dim3(hs::SM_THREADS), 0,
+                             (cudaStream_t)stream, hs_pdl_enabled(), out, logits, temperature,
+                             top_k, seed_lo, seed_hi, position, vocab, feedback, feedback_slot);
+  if (le != cudaSuccess) return (int)le;
   HS_LAUNCH_CHECK();
   return HS_OK;
 }

@@ -135,6 +135,8 @@ def _declare(lib) -> None:
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int
+    lib.hs_set_pdl.argtypes = [I]
+    lib.hs_set_pdl.restype = None
 
 
 def _ptr(t):
@@ -184,7 +186,7 @@ class CudaOps:
         self.sm_count = torch.cuda.get_device_properties(0).multi_processor_count
         self.fuse_norm = True      # LayerNorm fused into the few-row linear kernel
         self.fuse_append = True    # key/value append fused into the decode attention
-        self.pdl = True            # programmatic dependent launch of the decode kernels
+        self.pdl = True            # programmatic dependent launch (see the property below)
         self._skinny_need: dict = {}
         self._tc_need: dict = {}
         self._scratch: dict = {}
@@ -198,6 +200,20 @@ class CudaOps:
     @staticmethod
     def _stream():
         return torch.cuda.current_stream().cuda_stream
+
+    @property
+    def pdl(self) -> bool:
+        """Programmatic dependent launch: kernels are launched so that their set-up (and what
+        they fetch that no kernel of the step writes: weights, work lists) overlaps the end of
+        the kernel before them; each waits before it first reads an earlier kernel's output.
+        The few-row linear and the decode attention take it as an argument; the other kernels
+        read a switch in the library, which is process-wide (the last setter wins)."""
+        return self._pdl
+
+    @pdl.setter
+    def pdl(self, on: bool) -> None:
+        self._pdl = bool(on)
+        self.lib.hs_set_pdl(int(self._pdl))
 
     # -- embedding and norm -------------------------------------------------
     def embed(self, x, ids, pos, req, wte, wpe, status, feedback=None):
