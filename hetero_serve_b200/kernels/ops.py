@@ -118,8 +118,8 @@ def _declare(lib) -> None:
         "hs_embed": [P, P, P, P, P, P, I, I, I, I, I, P, I, P, P],
         "hs_layernorm": [P, P, P, P, P, I, I, F, I, P],
         "hs_linear_simt": [P, P, P, P, P, I, I, I, I, I, I, P],
-        "hs_linear_tcgen05": [P, P, P, P, P, I, I, I, I, I, I, P, P, P, P],
-        "hs_linear_tcgen05_scratch": [I, I, I, I, P, P],
+        "hs_linear_tcgen05": [P, P, P, P, P, I, I, I, I, I, I, I, P, P, P, P],
+        "hs_linear_tcgen05_scratch": [I, I, I, I, I, P, P],
         "hs_linear_skinny": [P, P, P, P, P, F, P, P, P, I, I, I, I, I, P, P, I, P],
         "hs_linear_skinny_scratch": [I, I, I, I, P, P],
         "hs_kv_append": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
@@ -192,6 +192,8 @@ class CudaOps:
         self._scratch: dict = {}
         self._retired: list = []
         self.tile_n = 0            # 0: chosen per shape; 64/128/256 force a tile width
+        self.cta_pairs = -1        # -1: pairs of CTAs (cta_group::2) when there are many rows;
+        #                            0: never; 1: always
         self.skinny_max_rows = 32  # up to this many rows the weight-streaming kernel is used
         # pipeline time-outs of the TMA/tcgen05 kernels are ORed into this word; the runner
         # replaces it with its own so that they surface with the step's results
@@ -297,11 +299,12 @@ class CudaOps:
             if self._skinny(out, a, None, w, bias, act, residual, M, N, K):
                 return
         if a.dtype == torch.bfloat16 and self.tensor_cores and K % 8 == 0:
-            key = (M, N, K, self.tile_n)
+            key = (M, N, K, self.tile_n, self.cta_pairs)
             need = self._tc_need.get(key)
             if need is None:
                 floats, counters = ctypes.c_longlong(0), ctypes.c_int(0)
-                rc = self.lib.hs_linear_tcgen05_scratch(M, N, K, self.tile_n, ctypes.byref(floats),
+                rc = self.lib.hs_linear_tcgen05_scratch(M, N, K, self.tile_n, self.cta_pairs,
+                                                        ctypes.byref(floats),
                                                         ctypes.byref(counters))
                 need = (floats.value, counters.value) if rc == 0 else (0, 0)
                 self._tc_need[key] = need
@@ -311,7 +314,8 @@ class CudaOps:
                 cnt = self._scratch_buffer("tc_counters", need[1], torch.int32)
             code = self.lib.hs_linear_tcgen05(
                 _ptr(out), _ptr(a), _ptr(w), _ptr(bias), _ptr(residual), M, N, K, act,
-                _DT[out.dtype], self.tile_n, _ptr(scratch), _ptr(cnt), _ptr(self.status),
+                _DT[out.dtype], self.tile_n, self.cta_pairs, _ptr(scratch), _ptr(cnt),
+                _ptr(self.status),
                 self._stream())
             if code != -1:
                 _check(code, f"linear_tcgen05(M={M},N={N},K={K})")
