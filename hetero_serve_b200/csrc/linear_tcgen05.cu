@@ -38,17 +38,20 @@ constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;          // 64 bf16 = 128 bytes = one swizzle row
 constexpr int TC_UMMA_K = 16;
 
+constexpr int TC_THREADS = 384;       // warp 0 TMA, warp 1 MMA, warps 4..11 epilogue
+constexpr int TC_EPI_WARPS = 8;
+constexpr int TC_PATCH_BYTES = 32 * 64;   // per epilogue warp: 32 rows x 64 bytes
+
 template <int BN, int STAGES>
 struct TcSmem {
   static constexpr int A_BYTES = TC_BM * TC_BK * 2;
   static constexpr int B_BYTES = BN * TC_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int PATCH_OFFSET = STAGES * STAGE_BYTES;          // epilogue staging
+  static constexpr int BIAS_OFFSET = PATCH_OFFSET + TC_EPI_WARPS * TC_PATCH_BYTES;
+  static constexpr int BAR_OFFSET = BIAS_OFFSET + 2 * 256 * 4;      // bias of two tiles
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024;  // + alignment slack
 };
-
-constexpr int TC_THREADS = 384;       // warp 0 TMA, warp 1 MMA, warps 4..11 epilogue
-constexpr int TC_EPI_WARPS = 8;
 
 struct TcParams {
   void* out;
@@ -154,10 +157,179 @@ __device__ __forceinline__ void finish_row32(const TcParams& p, const uint32_t (
   store_row32<TO>(out, off, f, nvalid, vec);
 }
 
+// Bias and activation of a full chunk of 32 columns, in registers.  `bias_s`: the chunk's 32
+// bias values in shared memory (staged by the epilogue warps before the accumulator is ready:
+// a global load here would cost an L2 round trip per chunk), or null.
+__device__ __forceinline__ void bias_act32(const TcParams& p, const uint32_t (&v)[32],
+                                           const float* bias_s, float (&f)[32]) {
+  if (bias_s != nullptr) {
+    const float4* b4 = (const float4*)bias_s;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 b = b4[j];
+      f[4 * j] = __uint_as_float(v[4 * j]) + b.x;
+      f[4 * j + 1] = __uint_as_float(v[4 * j + 1]) + b.y;
+      f[4 * j + 2] = __uint_as_float(v[4 * j + 2]) + b.z;
+      f[4 * j + 3] = __uint_as_float(v[4 * j + 3]) + b.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) + 0.f;
+  }
+  if (p.act != HS_ACT_NONE) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], p.act);
+  }
+}
+
+// Storing a full chunk (32 valid columns, N a multiple of 8) with coalesced global
+// accesses.  A lane owns one ROW of the accumulator, so storing its values directly makes every
+// warp instruction touch 32 different cache lines (the epilogue was bound by exactly that).
+// Instead the finished values go through a 32 x 64-byte patch of shared memory (pieces of 16
+// bytes, XOR-swizzled: no bank conflicts either way) and leave it with 4 lanes per row: a warp
+// instruction then covers 8 rows x 64 contiguous bytes.  The float32 residual is read with the
+// same coalesced pattern.  The arithmetic and its order are those of finish_row32.
+// The residual of a chunk in the layout the staged store uses: piece (h, i) is the float4 of row
+// 8 i + lane / 4 at columns 16 h + 4 (lane % 4) .. of the chunk.
+struct ResChunk {
+  float4 r[2][4];
+};
+__device__ __forceinline__ void load_residual_chunk(const TcParams& p, ResChunk& rc, int lane,
+                                                    int row0, int nbase) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = i * 8 + (lane >> 2);
+      const size_t off = (size_t)(row0 + r) * p.N + nbase + h * 16 + (lane & 3) * 4;
+      rc.r[h][i] = (row0 + r < p.M) ? *(const float4*)(p.residual + off)
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+}
+
+template <typename TO>
+__device__ __forceinline__ void store_chunk_staged(const TcParams& p, const float (&f)[32],
+                                                   const ResChunk* rc, uint8_t* patch, int lane,
+                                                   int row0, int nbase) {
+  constexpr int PER = 64 / (int)sizeof(TO);          // columns per 64-byte piece of a row
+  TO* out = (TO*)p.out;
+  const int sw_w = (lane >> 1) & 3;                   // swizzle of the row this lane writes
+#pragma unroll
+  for (int h = 0; h < 32 / PER; ++h) {
+#pragma unroll
+    for (int pc = 0; pc < 4; ++pc) {
+      uint4 u;
+      if constexpr (sizeof(TO) == 4) {
+        const int c = h * PER + pc * 4;
+        u.x = __float_as_uint(f[c]); u.y = __float_as_uint(f[c + 1]);
+        u.z = __float_as_uint(f[c + 2]); u.w = __float_as_uint(f[c + 3]);
+      } else {
+        const int c = h * PER + pc * 8;
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(f[c], f[c + 1]);
+        __nv_bfloat162 p1 = __floats2bfloat162_rn(f[c + 2], f[c + 3]);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(f[c + 4], f[c + 5]);
+        __nv_bfloat162 p3 = __floats2bfloat162_rn(f[c + 6], f[c + 7]);
+        u.x = *(uint32_t*)&p0; u.y = *(uint32_t*)&p1; u.z = *(uint32_t*)&p2; u.w = *(uint32_t*)&p3;
+      }
+      *(uint4*)(patch + lane * 64 + ((pc ^ sw_w) << 4)) = u;
+    }
+    __syncwarp();
+    const int pc = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = i * 8 + (lane >> 2);
+      const uint4 u = *(const uint4*)(patch + r * 64 + ((pc ^ ((r >> 1) & 3)) << 4));
+      if (row0 + r >= p.M) continue;
+      if constexpr (sizeof(TO) == 4) {
+        const size_t off = (size_t)(row0 + r) * p.N + nbase + h * PER + pc * 4;
+        float4 o = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z),
+                               __uint_as_float(u.w));
+        if (rc != nullptr) {
+          const float4 q = rc->r[h][i];
+          o.x += q.x; o.y += q.y; o.z += q.z; o.w += q.w;
+        }
+        *(float4*)((float*)out + off) = o;
+      } else {
+        const size_t off = (size_t)(row0 + r) * p.N + nbase + h * PER + pc * 8;
+        *(uint4*)((__nv_bfloat16*)out + off) = u;
+      }
+    }
+    __syncwarp();
+  }
+}
+
+// One epilogue warp's share of a tile: NCHUNK chunks of 32 columns from c_begin on, of the 32
+// rows it owns in tensor memory.  Before it waits for the accumulator it has the residual of
+// its first two chunks on the way (the main loop hides the loads); afterwards the tcgen05.ld of
+// the next chunk and the residual two chunks ahead are in flight while a chunk is finished and
+// stored.  `bias_s`: this tile's bias in shared memory (index = column inside the tile) or null.
+// Returns false if the wait ran out.
+template <typename TO, int NCHUNK, bool SPLIT>
+__device__ __forceinline__ bool epilogue_columns(const TcParams& p, uint64_t* acc_bar,
+                                                 uint32_t parity, uint32_t t_addr, int c_begin,
+                                                 int row0, int n0, int lane, uint8_t* patch,
+                                                 const float* bias_s, int split) {
+  const int row = row0 + lane;
+  const bool vec = (p.N % 8 == 0);
+  const bool staged_ok = !SPLIT && vec && !(sizeof(TO) == 2 && p.residual != nullptr);
+  const bool res_ahead = !SPLIT && sizeof(TO) == 4 && staged_ok && p.residual != nullptr;
+  auto full_chunk = [&](int c) { return n0 + c_begin + 32 * c + 32 <= p.N; };
+  ResChunk rc[2];
+  if constexpr (!SPLIT) if (res_ahead) {
+#pragma unroll
+    for (int c = 0; c < 2 && c < NCHUNK; ++c)
+      if (full_chunk(c)) load_residual_chunk(p, rc[c], lane, row0, n0 + c_begin + 32 * c);
+  }
+  const bool ok = mbar_wait(acc_bar, parity, p.status);
+  tc_fence_after();
+  if (!ok) return false;
+  uint32_t v[32];
+  tmem_ld32(t_addr + (uint32_t)c_begin, v);
+#pragma unroll
+  for (int c = 0; c < NCHUNK; ++c) {
+    const int c0 = c_begin + 32 * c;
+    tmem_ld_wait();
+    const int nbase = n0 + c0;
+    const int nvalid = min(32, p.N - nbase);
+    if (!SPLIT && staged_ok && nvalid == 32) {
+      float f[32];
+      bias_act32(p, v, bias_s ? bias_s + c0 : nullptr, f);
+      if (c + 1 < NCHUNK) tmem_ld32(t_addr + (uint32_t)(c0 + 32), v);
+      store_chunk_staged<TO>(p, f, res_ahead ? &rc[c & 1] : nullptr, patch, lane, row0, nbase);
+      if (res_ahead && c + 2 < NCHUNK && full_chunk(c + 2))
+        load_residual_chunk(p, rc[c & 1], lane, row0, nbase + 64);
+      continue;
+    }
+    if (row < p.M && nbase < p.N) {
+      if constexpr (SPLIT) {
+        // raw partial sums to scratch; the last split to arrive finishes the tile
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+        store_row32<float>(p.partial, ((size_t)split * p.M + row) * p.N + nbase, f, nvalid,
+                           p.N % 4 == 0);
+      } else {
+        finish_row32<TO>(p, v, row, nbase, nvalid, vec);
+      }
+    }
+    if (c + 1 < NCHUNK) tmem_ld32(t_addr + (uint32_t)(c0 + 32), v);
+  }
+  return true;
+}
+
+// The epilogue warps (256 threads) put the bias of the tile at columns n0 .. n0 + BN into
+// `dst` (zeros past N) and meet at their own barrier.
+template <int BN>
+__device__ __forceinline__ void stage_bias(const TcParams& p, float* dst, int n0) {
+  const int e = threadIdx.x - 4 * 32;
+  if (e < BN) dst[e] = (n0 + e < p.N) ? __ldg(p.bias + n0 + e) : 0.f;
+  epi_bar_sync();
+}
+
 // Persistent: each CTA takes work items (output tile x k split) blockIdx.x, + gridDim.x, ...
 // Tiles are numbered with n fastest, so CTAs running together share the rows of `a`.
 // Two accumulators in TMEM: the epilogue of one work item overlaps the MMAs of the next.
-template <int BN, int STAGES, typename TO>
+template <int BN, int STAGES, typename TO, bool SPLIT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                       const __grid_constant__ CUtensorMap map_w, const TcParams p) {
@@ -267,43 +439,29 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     const int q = warp & 3, half = (warp - 4) >> 2;
     constexpr int HALF_COLS = BN / 2;
     TO* out = (TO*)p.out;
-    const bool vec = (p.N % 8 == 0);
+    uint8_t* patch = smem + S::PATCH_OFFSET + (warp - 4) * TC_PATCH_BYTES;
     uint32_t wi = 0;
     for (int w = blockIdx.x; w < n_items; w += gridDim.x, ++wi) {
       const int tile = w / p.splits, split = w - tile * p.splits;
       const int m0 = (tile / p.tiles_n) * TC_BM, n0 = (tile % p.tiles_n) * BN;
       const uint32_t acc = wi & 1, acc_round = wi >> 1;
-      const bool ok = mbar_wait(&acc_full[acc], acc_round & 1, p.status);
-      tc_fence_after();
-      const int row = m0 + q * 32 + lane;
-      const uint32_t t_addr = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
-      if (ok) {
-#pragma unroll 1
-        for (int c0 = half * HALF_COLS; c0 < (half + 1) * HALF_COLS; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(t_addr + (uint32_t)c0, v);
-          tmem_ld_wait();
-          const int nbase = n0 + c0;
-          if (row >= p.M || nbase >= p.N) continue;
-          const int nvalid = min(32, p.N - nbase);
-          if (p.splits > 1) {
-            // raw partial sums to scratch; the last split to arrive finishes the tile below
-            float f[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-            store_row32<float>(p.partial, ((size_t)split * p.M + row) * p.N + nbase, f, nvalid,
-                               p.N % 4 == 0);
-            continue;
-          }
-          finish_row32<TO>(p, v, row, nbase, nvalid, vec);
-        }
+      // the tile's bias goes to shared memory while the MMAs still run (two buffers: a warp
+      // can be one tile ahead of the slowest at most, because of the barrier inside)
+      float* bias_s = nullptr;
+      if (!SPLIT && p.bias != nullptr) {
+        bias_s = (float*)(smem + S::BIAS_OFFSET) + (wi & 1) * 256;
+        stage_bias<BN>(p, bias_s, n0);
       }
+      const uint32_t t_addr = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
+      epilogue_columns<TO, HALF_COLS / 32, SPLIT>(p, &acc_full[acc], acc_round & 1, t_addr,
+                                                  half * HALF_COLS, m0 + q * 32, n0, lane, patch,
+                                                  bias_s, split);
       // the accumulator may be overwritten by the MMAs of the work item after next
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
 
-      if (p.splits > 1) {
+      if constexpr (SPLIT) {
         // ---- the last split of this tile to arrive adds the shares in split order
         __threadfence();
         epi_bar_sync();
@@ -382,7 +540,9 @@ struct PairSmem {
   static constexpr int A_BYTES = TC_BM * TC_BK * 2;
   static constexpr int B_BYTES = (BN / 2) * TC_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int PATCH_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int BIAS_OFFSET = PATCH_OFFSET + TC_EPI_WARPS * TC_PATCH_BYTES;
+  static constexpr int BAR_OFFSET = BIAS_OFFSET + 2 * 256 * 4;
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024;
 };
 
@@ -487,7 +647,7 @@ linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     // ---------------- epilogue: this CTA's 128 rows of the tile
     const int q = warp & 3, half = (warp - 4) >> 2;
     constexpr int HALF_COLS = BN / 2;
-    const bool vec = (p.N % 8 == 0);
+    uint8_t* patch = smem + S::PATCH_OFFSET + (warp - 4) * TC_PATCH_BYTES;
     const uint32_t acc_empty_leader0 = cluster_map(&acc_empty[0], 0);
     const uint32_t acc_empty_leader1 = cluster_map(&acc_empty[1], 0);
     uint32_t wi = 0;
@@ -495,21 +655,15 @@ linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       const int m0 = (w / p.tiles_n) * (2 * TC_BM) + (int)rank * TC_BM;
       const int n0 = (w % p.tiles_n) * BN;
       const uint32_t acc = wi & 1, acc_round = wi >> 1;
-      const bool ok = mbar_wait(&acc_full[acc], acc_round & 1, p.status);
-      tc_fence_after();
-      const int row = m0 + q * 32 + lane;
-      const uint32_t t_addr = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
-      if (ok) {
-#pragma unroll 1
-        for (int c0 = half * HALF_COLS; c0 < (half + 1) * HALF_COLS; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(t_addr + (uint32_t)c0, v);
-          tmem_ld_wait();
-          const int nbase = n0 + c0;
-          if (row >= p.M || nbase >= p.N) continue;
-          finish_row32<TO>(p, v, row, nbase, min(32, p.N - nbase), vec);
-        }
+      float* bias_s = nullptr;
+      if (p.bias != nullptr) {
+        bias_s = (float*)(smem + S::BIAS_OFFSET) + (wi & 1) * 256;
+        stage_bias<BN>(p, bias_s, n0);
       }
+      const uint32_t t_addr = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
+      epilogue_columns<TO, HALF_COLS / 32, false>(p, &acc_full[acc], acc_round & 1, t_addr,
+                                                  half * HALF_COLS, m0 + q * 32, n0, lane, patch,
+                                                  bias_s, 0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc ? acc_empty_leader1 : acc_empty_leader0);
@@ -561,10 +715,10 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
   return r == CUDA_SUCCESS ? HS_OK : HS_ERR_ARGUMENT;
 }
 
-template <int BN, int STAGES, typename TO>
+template <int BN, int STAGES, typename TO, bool SPLIT>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const TcParams& p, int grid,
                   cudaStream_t st) {
-  auto kern = linear_tcgen05_kernel<BN, STAGES, TO>;
+  auto kern = linear_tcgen05_kernel<BN, STAGES, TO, SPLIT>;
   constexpr int smem = TcSmem<BN, STAGES>::TOTAL;
   static bool configured = false;
   if (!configured) {
@@ -731,9 +885,12 @@ HS_EXPORT int hs_linear_tcgen05(void* out, const void* a, const void* w, const f
   p.kb_per_split = pl.kb_per_split;
   cudaStream_t st = (cudaStream_t)stream;
   using bf16 = __nv_bfloat16;
-#define HS_TC(BN, ST)                                                        \
-  (out_dtype == HS_DT_F32 ? launch<BN, ST, float>(ma, mw, p, pl.grid, st)    \
-                          : launch<BN, ST, bf16>(ma, mw, p, pl.grid, st))
+#define HS_TC(BN, ST)                                                                      \
+  (pl.splits > 1                                                                           \
+       ? (out_dtype == HS_DT_F32 ? launch<BN, ST, float, true>(ma, mw, p, pl.grid, st)     \
+                                 : launch<BN, ST, bf16, true>(ma, mw, p, pl.grid, st))     \
+       : (out_dtype == HS_DT_F32 ? launch<BN, ST, float, false>(ma, mw, p, pl.grid, st)    \
+                                 : launch<BN, ST, bf16, false>(ma, mw, p, pl.grid, st)))
   if (pl.pair) {
     if (pl.bn == 256)
       return out_dtype == HS_DT_F32 ? launch_pair<256, 6, float>(ma, mw, p, pl.grid, st)
