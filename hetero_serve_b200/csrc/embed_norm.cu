@@ -109,10 +109,18 @@ layernorm_warp_kernel(TO* __restrict__ out, const float* __restrict__ x,
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int o = blockIdx.x * LN_ROWS_PER_CTA + warp;
+  const int nf4 = width / 4;
+  // weight and bias of the norm do not change during a step: they are brought into shared
+  // memory before the dependency wait, off the critical path
+  extern __shared__ float4 s_gb[];                       // [nf4] weight, [nf4] bias
+  for (int i = threadIdx.x; i < nf4; i += blockDim.x) {
+    s_gb[i] = ((const float4*)gamma)[i];
+    s_gb[nf4 + i] = ((const float4*)beta)[i];
+  }
+  __syncthreads();
   if (o >= n_rows) return;
   const int src = rows ? rows[o] : o;
   const float4* xr = (const float4*)(x + (size_t)src * width);
-  const int nf4 = width / 4;
   pdl_wait();                      // x is what the previous kernel wrote
   float4 v[LN_F4];
 #pragma unroll
@@ -136,7 +144,7 @@ layernorm_warp_kernel(TO* __restrict__ out, const float* __restrict__ x,
   for (int i = 0; i < LN_F4; ++i) {
     const int e = (lane + 32 * i) * 4;
     if (lane + 32 * i < nf4) {
-      const float4 g = *(const float4*)(gamma + e), b = *(const float4*)(beta + e);
+      const float4 g = s_gb[lane + 32 * i], b = s_gb[nf4 + lane + 32 * i];
       const float y0 = (v[i].x - mu) * rstd * g.x + b.x, y1 = (v[i].y - mu) * rstd * g.y + b.y;
       const float y2 = (v[i].z - mu) * rstd * g.z + b.z, y3 = (v[i].w - mu) * rstd * g.w + b.w;
       if constexpr (sizeof(TO) == 4) {
@@ -192,11 +200,12 @@ HS_EXPORT int hs_layernorm(void* out, const float* x, const float* gamma, const 
     const bool pdl = hs_pdl_enabled();
     if (out_dtype == HS_DT_F32)
       le = hs_launch(hs::layernorm_warp_kernel<float>, dim3(grid), dim3(hs::LN_ROWS_PER_CTA * 32),
-                     0, st0, pdl, (float*)out, x, gamma, beta, rows, n_rows, width, eps);
+                     (size_t)width * 8, st0, pdl, (float*)out, x, gamma, beta, rows, n_rows, width,
+                     eps);
     else if (out_dtype == HS_DT_BF16)
       le = hs_launch(hs::layernorm_warp_kernel<__nv_bfloat16>, dim3(grid),
-                     dim3(hs::LN_ROWS_PER_CTA * 32), 0, st0, pdl, (__nv_bfloat16*)out, x, gamma,
-                     beta, rows, n_rows, width, eps);
+                     dim3(hs::LN_ROWS_PER_CTA * 32), (size_t)width * 8, st0, pdl,
+                     (__nv_bfloat16*)out, x, gamma, beta, rows, n_rows, width, eps);
     else
       return HS_ERR_UNSUPPORTED;
     if (le != cudaSuccess) return (int)le;

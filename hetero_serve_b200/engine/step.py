@@ -162,6 +162,7 @@ class StepContext:
         self.tables = [meta[o:o + L.R * mp].view(L.R, mp)
                        for o, mp in zip(L.tables, L.max_pages)]
         self.plan = None          # work lists for the specialised attention kernels, if any
+        self.position = None      # the model's position encoding (set by Model.forward)
         self.call_index: int | None = None
         # host-side view of the batch for parts written in plain PyTorch
         self.host: list[tuple[Hashable, int, int, int]] = []   # (req, slot, start, n)
@@ -417,7 +418,7 @@ class Runner:
             if plan_shape is not None:
                 from ..kernels.ops import AttentionPlan
                 ctx.plan = AttentionPlan(dev[lay.plan:lay.plan + lay.plan_ints], T, *plan_shape)
-            if self.use_graphs and not self.model.state_shapes:
+            if self.use_graphs and not self.model.state_shapes and self.model.capturable:
                 # run once eagerly (loads kernels, sizes buffers), then capture and replay.  The
                 # replay must see the same inputs as the eager run: all of them come from the
                 # metadata block except the tokens kept on the device, which sampling overwrites

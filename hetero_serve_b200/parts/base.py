@@ -55,6 +55,9 @@ class CacheRequest:
 
 class Part:
     kind: str = ""
+    # False for a part whose forward cannot be captured in a CUDA graph (its launches depend
+    # on values read back to the host); a model with such a part is run without graphs.
+    capturable: bool = True
 
     def tensor_requests(self) -> dict[str, TensorRequest]:
         return {}
@@ -109,6 +112,15 @@ class PositionEncoding(Part):
 
     def max_positions(self) -> int | None:
         return None
+
+    # A position encoding that acts on queries and keys instead of (or besides) the embedding
+    # sets ``acts_in_mixer`` and implements ``transform_qk``: an attention mixer calls it on its
+    # projected ``qkv`` rows ([tokens, q | k | v columns], in place) before keys are appended
+    # and scores are formed.  ``ctx.tok_pos`` holds the position of every row.
+    acts_in_mixer = False
+
+    def transform_qk(self, ctx, qkv, geometry) -> None:
+        raise NotImplementedError
 
 
 class Embedding(Part):

@@ -83,6 +83,7 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm)
         self.head = build_part("head", spec.head)
         self.schedule: tuple[LayerCall, ...] = spec.resolved_schedule()
+        self.capturable = all(part.capturable for part in self.parts())
         self._derive_cache()
         self.dtype = None
         self.device = None
@@ -170,6 +171,7 @@ class Model:
         spec = self.spec
         T = ctx.n_rows
         x = ctx.buffer("residual", (T, spec.width), torch.float32)
+        ctx.position = self.position          # mixers ask it whether it acts on queries and keys
         self.embedding.forward(ctx, x, self.position)
         for idx, call in enumerate(self.schedule):
             ctx.call_index = idx

@@ -149,6 +149,9 @@ class CausalAttention(Mixer):
         else:
             ctx.ops.linear(qkv, h, self.w_qkv, self.b_qkv)
         g = self.geometry(cache)
+        position = getattr(ctx, "position", None)
+        if position is not None and position.acts_in_mixer:
+            position.transform_qk(ctx, qkv, g)
         att = ctx.buffer("attn_out", (T, self.H * self.D), ctx.dtype)
         ctx.ops.attention_append(att, qkv, cache.pool, cache.table, ctx.tok_pos, ctx.tok_req, g,
                                  self.scale, ctx.status, ctx.plan, cache.writes)
