@@ -135,9 +135,13 @@ __device__ __forceinline__ void finish_row32(const TcParams& p, const uint32_t (
     for (int j = 0; j < 32; ++j)
       f[j] = __uint_as_float(v[j]) + ((p.bias && j < nvalid) ? p.bias[nbase + j] : 0.f);
   }
-  if (p.act != HS_ACT_NONE) {
+  // one branch per chunk, not per element (the compiler must not evaluate both forms)
+  if (p.act == HS_ACT_GELU_TANH) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], p.act);
+    for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], HS_ACT_GELU_TANH);
+  } else if (p.act == HS_ACT_GELU_ERF) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], HS_ACT_GELU_ERF);
   }
   const size_t off = (size_t)row * p.N + nbase;
   if (p.residual) {
@@ -176,9 +180,13 @@ __device__ __forceinline__ void bias_act32(const TcParams& p, const uint32_t (&v
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) + 0.f;
   }
-  if (p.act != HS_ACT_NONE) {
+  // one branch per chunk, not per element (the compiler must not evaluate both forms)
+  if (p.act == HS_ACT_GELU_TANH) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], p.act);
+    for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], HS_ACT_GELU_TANH);
+  } else if (p.act == HS_ACT_GELU_ERF) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], HS_ACT_GELU_ERF);
   }
 }
 
