@@ -308,18 +308,24 @@ __device__ __forceinline__ bool epilogue_columns(const TcParams& p, uint64_t* ac
         load_residual_chunk(p, rc[c & 1], lane, row0, nbase + 64);
       continue;
     }
-    if (row < p.M && nbase < p.N) {
-      if constexpr (SPLIT) {
-        // raw partial sums to scratch; the last split to arrive finishes the tile
-        float f[32];
+    if constexpr (SPLIT) {
+      // raw partial sums to this split's share of the scratch; the last split to arrive
+      // finishes the tile.  Whole chunks leave through the staging patch (coalesced).
+      float f[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+      for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+      if (c + 1 < NCHUNK) tmem_ld32(t_addr + (uint32_t)(c0 + 32), v);
+      if (vec && nvalid == 32) {
+        TcParams share = p;
+        share.out = p.partial + (size_t)split * p.M * p.N;
+        store_chunk_staged<float>(share, f, nullptr, patch, lane, row0, nbase);
+      } else if (row < p.M && nbase < p.N) {
         store_row32<float>(p.partial, ((size_t)split * p.M + row) * p.N + nbase, f, nvalid,
                            p.N % 4 == 0);
-      } else {
-        finish_row32<TO>(p, v, row, nbase, nvalid, vec);
       }
+      continue;
     }
+    if (row < p.M && nbase < p.N) finish_row32<TO>(p, v, row, nbase, nvalid, vec);
     if (c + 1 < NCHUNK) tmem_ld32(t_addr + (uint32_t)(c0 + 32), v);
   }
   return true;
@@ -483,7 +489,51 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           constexpr int PIECES = BN / 4;
           const int rows_here = min(TC_BM, p.M - m0);
           const bool vec4 = (p.N % 4 == 0);
-          for (int e = et; e < rows_here * PIECES; e += TC_EPI_WARPS * 32) {
+          const int n_pieces = rows_here * PIECES;
+          if (vec4 && p.splits <= 8) {
+            // every load of a piece (shares, bias, residual) is on its way before the first sum
+#pragma unroll 1
+            for (int e = et; e < n_pieces; e += TC_EPI_WARPS * 32) {
+              const int r = e / PIECES, n = n0 + (e % PIECES) * 4;
+              if (n >= p.N) continue;
+              const size_t off = (size_t)(m0 + r) * p.N + n;
+              float4 sh[8];
+#pragma unroll
+              for (int sp = 0; sp < 8; ++sp)
+                if (sp < p.splits)
+                  sh[sp] = __ldcg((const float4*)(p.partial + (size_t)sp * p.M * p.N + off));
+              float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), r4 = b4;
+              if (p.bias) b4 = __ldg((const float4*)(p.bias + n));
+              if (p.residual) r4 = *(const float4*)(p.residual + off);
+              float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+              for (int sp = 0; sp < 8; ++sp)
+                if (sp < p.splits) {
+                  a.x += sh[sp].x; a.y += sh[sp].y; a.z += sh[sp].z; a.w += sh[sp].w;
+                }
+              float x[4] = {a.x + b4.x, a.y + b4.y, a.z + b4.z, a.w + b4.w};
+              if (p.act == HS_ACT_GELU_TANH) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] = act_tc(x[j], HS_ACT_GELU_TANH);
+              } else if (p.act == HS_ACT_GELU_ERF) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] = act_tc(x[j], HS_ACT_GELU_ERF);
+              }
+              if (p.residual) {
+                x[0] += r4.x; x[1] += r4.y; x[2] += r4.z; x[3] += r4.w;
+              }
+              if constexpr (sizeof(TO) == 4) {
+                *(float4*)((float*)out + off) = make_float4(x[0], x[1], x[2], x[3]);
+              } else {
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(x[0], x[1]);
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(x[2], x[3]);
+                uint2 o;
+                o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1;
+                *(uint2*)((__nv_bfloat16*)out + off) = o;
+              }
+            }
+          } else
+          for (int e = et; e < n_pieces; e += TC_EPI_WARPS * 32) {
             const int r = e / PIECES, c = (e % PIECES) * 4;
             const int n = n0 + c;
             if (n >= p.N) continue;
