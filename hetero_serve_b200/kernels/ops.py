@@ -191,10 +191,12 @@ class CudaOps:
         self._tc_need: dict = {}
         self._scratch: dict = {}
         self._retired: list = []
+        self.decode_force = None   # (wide code, slices) of the decode attention, for tuning
         self.tile_n = 0            # 0: chosen per shape; 64/128/256 force a tile width
         self.cta_pairs = -1        # -1: pairs of CTAs (cta_group::2) when there are many rows;
         #                            0: never; 1: always
-        self.skinny_max_rows = 32  # up to this many rows the weight-streaming kernel is used
+        self.skinny_max_rows = 16  # up to this many rows the weight-streaming kernel is used
+        #                            (measured: from 17 rows on the tcgen05 kernel's split over k wins)
         # pipeline time-outs of the TMA/tcgen05 kernels are ORed into this word; the runner
         # replaces it with its own so that they surface with the step's results
         self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -490,6 +492,8 @@ class CudaOps:
     def decode_wide(self, decode_cap: int, n_heads: int) -> int:
         """Warps per CTA of the decode attention: 16 (code 2) while token x head count is below
         the SM count, 8 (code 1) up to twice that, else 4 (code 0)."""
+        if self.decode_force is not None:
+            return self.decode_force[0]
         pairs = decode_cap * n_heads
         return 2 if pairs <= self.sm_count else (1 if pairs <= 2 * self.sm_count else 0)
 
@@ -501,6 +505,8 @@ class CudaOps:
         small."""
         pairs = max(1, decode_cap * n_heads)
         wide = self.decode_wide(decode_cap, n_heads)
+        if self.decode_force is not None:
+            return self.decode_force[1]
         want = max(1, round(self.sm_count / pairs)) if wide == 2 else 1
         per_warp = 32 * 16 * (4, 8, 16)[wide]        # keys a CTA can cover: 32 pages per warp
         need = -(-max_context // per_warp)
