@@ -876,7 +876,9 @@ static bool plan_tc(int M, int N, int K, int tile_n, int pair, TcPlan& pl) {
         bn = cand;
       }
     }
-    if (mt == 1) bn = 64;     // few rows: narrow tiles (more CTAs stream the weights) and splits
+    // few rows: narrow tiles (more CTAs stream the weights) and splits; a very wide layer (the
+    // vocabulary) has tiles enough and reads the activations less often with 128 columns
+    if (mt == 1) bn = ((N + 63) / 64 >= 2 * sms) ? 128 : 64;
   }
   if (bn != 64 && bn != 128 && bn != 256) return false;
   pl.bn = bn;
