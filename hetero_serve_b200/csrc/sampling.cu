@@ -52,16 +52,18 @@ __device__ ArgMax block_argmax(const float* row, int vocab) {
   __shared__ ArgMax sh[SM_THREADS / 32];
   __shared__ ArgMax result;
   ArgMax best{-INFINITY, 0x7fffffff};
-  // eight loads in flight per thread; within a thread indices rise, so the first seen wins ties
-  for (int base = threadIdx.x; base < vocab; base += 8 * blockDim.x) {
-    float v[8];
+  // 32 loads in flight per thread (a row of 50k logits is two rounds for 1,024 threads); within
+  // a thread indices rise, so the first seen wins ties
+  constexpr int INFLIGHT = 32;
+  for (int base = threadIdx.x; base < vocab; base += INFLIGHT * blockDim.x) {
+    float v[INFLIGHT];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < INFLIGHT; ++j) {
       const int i = base + j * blockDim.x;
       v[j] = i < vocab ? row[i] : -INFINITY;
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < INFLIGHT; ++j) {
       const int i = base + j * blockDim.x;
       if (i < vocab && (v[j] > best.v || best.i == 0x7fffffff)) best = ArgMax{v[j], i};
     }
@@ -163,11 +165,13 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               const int* __restrict__ seed_lo, const int* __restrict__ seed_hi,
               const int* __restrict__ position, int vocab, int* __restrict__ feedback,
-              const int* __restrict__ feedback_slot) {
+              const int* __restrict__ feedback_slot, const int* __restrict__ status_word) {
   const int rowi = blockIdx.x;
   const float* row = logits + (size_t)rowi * vocab;
   const float temp = temperature[rowi];
   pdl_wait();                       // the logits are what the previous kernel wrote
+  // the engine's status word rides behind the tokens, so that one copy brings both to the host
+  if (status_word != nullptr && rowi == 0 && threadIdx.x == 0) out[gridDim.x] = *status_word;
   const ArgMax top = block_argmax(row, vocab);
   // a row with a feedback slot also leaves its token there, for the next step's embedding
   const int fb = (feedback != nullptr && feedback_slot != nullptr) ? feedback_slot[rowi] : -1;
@@ -272,17 +276,20 @@ HS_EXPORT int hs_argmax(int* out, const float* logits, int rows, int vocab, void
 }
 
 // feedback / feedback_slot (both may be null): row i also stores its token to
-// feedback[feedback_slot[i]] when that slot is not negative.
+// feedback[feedback_slot[i]] when that slot is not negative.  status_word (may be null): its
+// value is stored to out[rows].
 HS_EXPORT int hs_sample(int* out, const float* logits, const float* temperature, const int* top_k,
                         const int* seed_lo, const int* seed_hi, const int* position, int rows,
-                        int vocab, int* feedback, const int* feedback_slot, void* stream) {
+                        int vocab, int* feedback, const int* feedback_slot,
+                        const int* status_word, void* stream) {
   if (!out || !logits || !temperature || !top_k || !seed_lo || !seed_hi || !position)
     return HS_ERR_ARGUMENT;
   if (rows <= 0) return HS_OK;
   if (vocab <= 0) return HS_ERR_ARGUMENT;
   cudaError_t le = hs_launch(hs::sample_kernel, dim3(rows), dim3(hs::SM_THREADS), 0,
                              (cudaStream_t)stream, hs_pdl_enabled(), out, logits, temperature,
-                             top_k, seed_lo, seed_hi, position, vocab, feedback, feedback_slot);
+                             top_k, seed_lo, seed_hi, position, vocab, feedback, feedback_slot,
+                             status_word);
   if (le != cudaSuccess) return (int)le;
   HS_LAUNCH_CHECK();
   return HS_OK;

@@ -467,10 +467,14 @@ class Runner:
             # one extra element carries the status word, so that one copy brings both back
             W = ctx.n_logit_rows
             tokens = ctx.buffer("sampled", (W + 1,), torch.int32)
+            more = {}
+            if getattr(self.ops, "takes_status_word", False):
+                more["status_word"] = self.status          # stored to tokens[W] by the kernel
             self.ops.sample(tokens, logits, ctx.samp_temp, ctx.samp_topk, ctx.samp_seed_lo,
                             ctx.samp_seed_hi, ctx.samp_pos, feedback=self.feedback,
-                            feedback_slot=ctx.samp_slot)
-            tokens[W:].copy_(self.status)
+                            feedback_slot=ctx.samp_slot, **more)
+            if not more:
+                tokens[W:].copy_(self.status)
         return logits, tokens
 
     def _fetch(self, dev: torch.Tensor):

@@ -129,7 +129,7 @@ def _declare(lib) -> None:
         "hs_attention_prefill": [P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P, P],
         "hs_attention_prefill_tc": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, P, P],
         "hs_argmax": [P, P, I, I, P],
-        "hs_sample": [P, P, P, P, P, P, P, I, I, P, P, P],
+        "hs_sample": [P, P, P, P, P, P, P, I, I, P, P, P, P],
     }
     for name, argtypes in sig.items():
         fn = getattr(lib, name)
@@ -192,6 +192,7 @@ class CudaOps:
         self._scratch: dict = {}
         self._retired: list = []
         self.decode_force = None   # (wide code, slices) of the decode attention, for tuning
+        self.takes_status_word = True   # sample() can store the status word behind the tokens
         self.tile_n = 0            # 0: chosen per shape; 64/128/256 force a tile width
         self.cta_pairs = -1        # -1: pairs of CTAs (cta_group::2) when there are many rows;
         #                            0: never; 1: always
@@ -601,11 +602,12 @@ class CudaOps:
         _check(self.lib.hs_argmax(_ptr(out), _ptr(logits), rows, vocab, self._stream()), "argmax")
 
     def sample(self, out, logits, temperature, top_k, seed_lo, seed_hi, position,
-               feedback=None, feedback_slot=None):
+               feedback=None, feedback_slot=None, status_word=None):
         """Per row: argmax if temperature <= 0, else a draw from softmax(logits/temperature)
         restricted to the top_k largest when 0 < top_k < vocab.  With ``feedback`` and
         ``feedback_slot`` row i also stores its token to ``feedback[feedback_slot[i]]`` (slots
-        below zero are skipped)."""
+        below zero are skipped).  With ``status_word`` (one int32 on the device) its value is
+        stored to ``out[rows]``: the engine's status travels behind the tokens."""
         _want(out, "out", torch.int32, 1)
         _want(logits, "logits", torch.float32, 2)
         rows, vocab = logits.shape
@@ -624,7 +626,12 @@ class CudaOps:
             _want(feedback_slot, "feedback_slot", torch.int32, 1)
             if feedback_slot.shape[0] < rows:
                 raise KernelError("sample: feedback_slot shorter than the rows")
+        if status_word is not None:
+            _want(status_word, "status_word", torch.int32, 1)
+            if out.shape[0] < rows + 1:
+                raise KernelError("sample: out has no room for the status word")
         self.launches += 1
         _check(self.lib.hs_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(top_k),
                                   _ptr(seed_lo), _ptr(seed_hi), _ptr(position), rows, vocab,
-                                  _ptr(feedback), _ptr(feedback_slot), self._stream()), "sample")
+                                  _ptr(feedback), _ptr(feedback_slot), _ptr(status_word),
+                                  self._stream()), "sample")
