@@ -102,3 +102,31 @@ def test_sampling_through_the_step_matches_the_plain_sampler(tiny_models):
     u = plain_gpt2.uniform_for(77, 12)
     assert got[0] == plain_gpt2.sample_token(tiny.logits(toks)[11], 0.8, 40, u)
     assert got[1] == int(torch.argmax(tiny.logits(toks[:5])[4]))
+
+
+def test_a_token_can_be_taken_from_the_device_copy(tiny_models):
+    """FROM_DEVICE as the first token of an entry stands for the token the latest sampling step
+    left on the device for that request: two requests decode three steps each without the host
+    feeding their tokens back, and get the logits of a replay that knows the tokens."""
+    from hetero_serve_b200.engine.step import FROM_DEVICE
+    tiny = tiny_models["tiny_b"]
+    rn = _runner(tiny, pages=12)
+    a, b = tiny.tokens(9, 4), tiny.tokens(20, 5)
+    first = rn.step([StepEntry("a", a, want=[8]), StepEntry("b", b, want=[19], temperature=0.7,
+                                                           seed=3)], sample=True)
+    ctx = {"a": list(a) + [first.tokens_host()[0]], "b": list(b) + [first.tokens_host()[1]]}
+    for _ in range(3):
+        res = rn.step([StepEntry("b", [FROM_DEVICE], want=[0], temperature=0.7, seed=3),
+                       StepEntry("a", [FROM_DEVICE], want=[0])], sample=True)
+        lg = res.logits.double().clone()
+        tb, ta = res.tokens_host()
+        assert (lg[0] - tiny.logits(ctx["b"])[-1]).abs().max() < TOL
+        assert (lg[1] - tiny.logits(ctx["a"])[-1]).abs().max() < TOL
+        ctx["a"].append(ta)
+        ctx["b"].append(tb)
+    # known tokens may follow the device token in the same entry; a device token elsewhere is refused
+    res = rn.step([StepEntry("a", [FROM_DEVICE, 7, 9], want=[2])])
+    assert (res.logits[0].double() - tiny.logits(ctx["a"] + [7, 9])[-1]).abs().max() < TOL
+    with pytest.raises(StepError, match="token id"):
+        rn.step([StepEntry("b", [3, FROM_DEVICE])])
+    rn.manager.check()
