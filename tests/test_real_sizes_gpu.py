@@ -1,5 +1,5 @@
-"""The engine at the real widths of GPT-2 medium, large and XL (a few layers of each, random
-weights): widths 1024 / 1280 / 1600, 16 / 20 / 25 heads of 64, inner 4x, the real vocabulary
+"""The engine at the real widths of GPT-2 small, medium, large and XL (a few layers of each,
+random weights): widths 768 / 1024 / 1280 / 1600, 12 / 16 / 20 / 25 heads of 64, inner 4x, the real vocabulary
 of 50,257 (odd, no power of two).  In 32-bit and in bfloat16, whole prompts against decoding
 and portions, compared with the plain implementation on the last positions."""
 
@@ -16,6 +16,7 @@ from hetero_serve_b200.weights import read_safetensors, write_model_dir
 pytestmark = pytest.mark.gpu
 
 SIZES = {
+    "small": dict(n_layer=2, n_embd=768, n_head=12),
     "medium": dict(n_layer=3, n_embd=1024, n_head=16),
     "large": dict(n_layer=2, n_embd=1280, n_head=20),
     "xl": dict(n_layer=2, n_embd=1600, n_head=25),
