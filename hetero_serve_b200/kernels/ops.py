@@ -126,6 +126,8 @@ def _declare(lib) -> None:
         "hs_attention_simt": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
         "hs_attention_decode_append": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I,
                                        F, I, I, I, I, P, P, P, P, P],
+        "hs_attention_decode_mma": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, I, I,
+                                    P, P, P, P, P],
         "hs_attention_prefill": [P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P, P],
         "hs_attention_prefill_tc": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, P, P],
         "hs_argmax": [P, P, I, I, P],
@@ -192,6 +194,8 @@ class CudaOps:
         self._scratch: dict = {}
         self._retired: list = []
         self.decode_force = None   # (wide code, slices) of the decode attention, for tuning
+        self.decode_mma = True     # batches beyond one (token, head) per SM: tensor-core decode
+        #                            attention ("always": whatever the batch, for tests)
         self.takes_status_word = True   # sample() can store the status word behind the tokens
         self.tile_n = 0            # 0: chosen per shape; 64/128/256 force a tile width
         self.cta_pairs = -1        # -1: pairs of CTAs (cta_group::2) when there are many rows;
@@ -555,7 +559,13 @@ class CudaOps:
         st = self._stream()
         if plan.decode_cap:
             max_ctx = g.max_pages * g.page_size
-            splits = self.decode_splits(plan.decode_cap, g.n_heads, max_ctx)
+            group = g.n_heads // g.n_kv_heads
+            use_mma = (self.decode_mma and self.decode_force is None
+                       and (plan.decode_cap * g.n_heads > self.sm_count
+                            or self.decode_mma == "always")
+                       and g.head_dim in (32, 64, 128) and group <= 16)
+            splits = (max(1, -(-max_ctx // 2048)) if use_mma
+                      else self.decode_splits(plan.decode_cap, g.n_heads, max_ctx))
             acc = ml = cnt = None
             if splits > 1:
                 rows = plan.decode_cap * g.n_heads * splits
@@ -564,14 +574,22 @@ class CudaOps:
                 cnt = self._scratch_buffer("decode_counters", plan.decode_cap * g.n_heads,
                                            torch.int32)
             self.launches += 1
-            _check(self.lib.hs_attention_decode_append(
-                _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req),
-                _ptr(dec_info), _ptr(head), plan.decode_cap, g.n_heads, g.n_kv_heads, g.head_dim,
-                g.page_size, g.num_pages, g.max_pages, g.q_off, g.k_off, g.v_off, g.qkv_stride,
-                g.window, scale, splits, int(bool(fuse)),
-                int(self.decode_wide(plan.decode_cap, g.n_heads)), int(self.pdl), _ptr(acc),
-                _ptr(ml), _ptr(cnt),
-                _ptr(status), st), f"attention_decode(head_dim={g.head_dim})")
+            if use_mma:
+                _check(self.lib.hs_attention_decode_mma(
+                    _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(dec_info), _ptr(head),
+                    plan.decode_cap, g.n_heads, g.n_kv_heads, g.head_dim, g.page_size,
+                    g.num_pages, g.max_pages, g.q_off, g.k_off, g.v_off, g.qkv_stride, scale,
+                    splits, int(bool(fuse)), int(self.pdl), _ptr(acc), _ptr(ml), _ptr(cnt),
+                    _ptr(status), st), f"attention_decode_mma(head_dim={g.head_dim})")
+            else:
+                _check(self.lib.hs_attention_decode_append(
+                    _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req),
+                    _ptr(dec_info), _ptr(head), plan.decode_cap, g.n_heads, g.n_kv_heads,
+                    g.head_dim, g.page_size, g.num_pages, g.max_pages, g.q_off, g.k_off, g.v_off,
+                    g.qkv_stride, g.window, scale, splits, int(bool(fuse)),
+                    int(self.decode_wide(plan.decode_cap, g.n_heads)), int(self.pdl), _ptr(acc),
+                    _ptr(ml), _ptr(cnt),
+                    _ptr(status), st), f"attention_decode(head_dim={g.head_dim})")
         if plan.tile_cap:
             self.launches += 1
             counter = self._scratch_buffer("prefill_counter", 1, torch.int32)

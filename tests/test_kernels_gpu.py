@@ -282,6 +282,19 @@ def _host_batch(lens, new):
     return [(f"r{r}", r, n - k, k) for r, (n, k) in enumerate(zip(lens, new))]
 
 
+@pytest.fixture
+def decode_kernel(request, ops):
+    """Which kernel serves single-query tokens: chosen by batch size, always the tensor-core
+    one (head sizes 32/64/128), or never."""
+    was = ops.decode_mma
+    ops.decode_mma = {"auto": True, "tensor_cores": "always", "cuda_cores": False}[request.param]
+    yield request.param
+    ops.decode_mma = was
+
+
+DECODE_KERNELS = ["auto", "tensor_cores", "cuda_cores"]
+
+
 FAST_CASES = [
     # H, HK, D, PS, lens, new     (bfloat16, no window: the specialised kernels)
     (4, 4, 16, 16, [5, 17, 33, 200], [5, 17, 33, 200]),          # prompts: tensor-core tiles
@@ -294,9 +307,10 @@ FAST_CASES = [
 ]
 
 
+@pytest.mark.parametrize("decode_kernel", DECODE_KERNELS, indirect=True)
 @pytest.mark.parametrize("case", FAST_CASES,
                          ids=[f"H{c[0]}k{c[1]}D{c[2]}P{c[3]}n{len(c[4])}" for c in FAST_CASES])
-def test_specialised_attention_kernels(ops, plain, case):
+def test_specialised_attention_kernels(ops, plain, case, decode_kernel):
     H, HK, D, PS, lens, new = case
     geom, qkv, pool, table, tok_pos, tok_req = _attention_case(H, HK, D, PS, lens, new, 0,
                                                                torch.bfloat16, seed=H * D)
@@ -332,11 +346,15 @@ DECODE_ONLY = [
     (4, 2, 32, 16, [300]),                                         # few pairs: several slices
     (8, 8, 128, 32, [90] * 40),                                    # many pairs: narrow CTAs
     (2, 1, 16, 16, [33, 2]),
+    (6, 2, 64, 16, [1, 2, 31, 32, 33, 64, 65, 500, 1000, 96, 97]),  # grouped heads, chunk edges
+    (3, 3, 32, 48, [200, 49, 48, 47, 700]),                        # pages of 48, head size 32
+    (20, 20, 64, 16, [600] * 16),                                  # 320 pairs: chosen by size
 ]
 
 
+@pytest.mark.parametrize("decode_kernel", DECODE_KERNELS, indirect=True)
 @pytest.mark.parametrize("case", DECODE_ONLY, ids=[f"H{c[0]}D{c[2]}n{len(c[4])}" for c in DECODE_ONLY])
-def test_decode_attention_with_the_append_fused_in(ops, plain, case):
+def test_decode_attention_with_the_append_fused_in(ops, plain, case, decode_kernel):
     H, HK, D, PS, lens = case
     new = [1] * len(lens)
     geom, qkv, pool, table, tok_pos, tok_req = _attention_case(H, HK, D, PS, lens, new, 0,
