@@ -56,11 +56,12 @@ class LLMEngine:
         return cls(model_dir, **kw)
 
     @classmethod
-    def random(cls, config: str | dict, seed: int = 0, *, store_dtype: str | None = None,
+    def random(cls, model: str | dict, seed: int = 0, *, store_dtype: str | None = None,
                **kw) -> "LLMEngine":
         """Random-weights mode: write a model folder for a preset name or a config.json
-        dictionary and a seed into a temporary folder, then load it like any other."""
-        raw = preset(config) if isinstance(config, str) else dict(config)
+        dictionary (``model``) and a seed into a temporary folder, then load it like any other;
+        ``config=EngineConfig(...)`` or single engine options go through as for the constructor."""
+        raw = preset(model) if isinstance(model, str) else dict(model)
         tmp = tempfile.TemporaryDirectory(prefix="hetero_serve_b200-")
         dtype = kw.get("dtype", (kw.get("config") or EngineConfig()).dtype)
         write_model_dir(tmp.name, raw, seed, store_dtype or ("bfloat16" if str(dtype).startswith("b") else "float32"))

@@ -199,3 +199,19 @@ def test_command_line(lively):
     lines = [json.loads(l) for l in res.stdout.strip().splitlines()]
     assert lines[0]["output_ids"] == plain_gpt2.greedy_generate(cfg, w, p, 6)
     assert lines[-1]["n_requests"] == 1
+
+
+def test_command_line_and_demo_with_random_weights():
+    """`--model NAME` builds seeded random weights for a named configuration (no folder given)."""
+    res = subprocess.run(
+        [sys.executable, "-m", "hetero_serve_b200", "--model", "tiny-b", "--dtype", "bfloat16",
+         "--num-blocks", "16", "--max-new-tokens", "5", "--no-eos-stop", "--json",
+         "--random-prompts", "3:9", "--temperature", "0.7", "--top-k", "20"],
+        capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [json.loads(l) for l in res.stdout.strip().splitlines()]
+    assert [len(l["output_ids"]) for l in lines[:3]] == [5, 5, 5]
+    assert lines[-1]["n_requests"] == 3
+    demo = subprocess.run([sys.executable, "run_demo.py", "--model", "tiny"],
+                          capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert demo.returncode == 0, demo.stderr[-2000:]
