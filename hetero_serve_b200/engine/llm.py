@@ -14,12 +14,9 @@ continuous-batching loop for callers that feed requests while others run.
 from __future__ import annotations
 
 import tempfile
-import time
 from dataclasses import replace
 from pathlib import Path
 from typing import Sequence
-
-import torch
 
 from ..config import EngineConfig, preset
 from ..weights import write_model_dir

@@ -22,14 +22,13 @@ word, or nothing at all when the caller only wants device logits.  With
 from __future__ import annotations
 
 import gc
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Hashable, Sequence
 
 import numpy as np
 import torch
 
 from ..cache import CacheManager, CacheStorage, GroupSpec
-from ..kernels.ops import KernelError
 
 STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a position outside the table",
                4: "a page number outside the pool", 8: "a kernel pipeline timed out"}

@@ -23,7 +23,7 @@ part and build a model around it without touching this package.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Mapping
+from typing import Callable, Mapping
 
 import torch
 

@@ -7,7 +7,6 @@ kernel interface of the step context; none refers to a model.
 
 from __future__ import annotations
 
-from typing import Mapping
 
 import torch
 
