@@ -1,15 +1,15 @@
 // Paged attention for single-query tokens on the tensor cores (mma.sync), bfloat16: the decode
-// kernel for batches large enough that bandwidth, not latency, decides.
+// kernel for head sizes 32, 64 and 128 at every batch size.
 //
 // Same work as attention_decode.cu (the successor of the reference's split-K decode kernels,
 // heteroserve/model/paged_attn_v3.py:75-232), arranged for streaming:
 //   * one CTA serves one (token, key/value head, slice): the G = n_heads / n_kv_heads query
 //     heads that share those keys are the rows of one 16-row MMA tile (GPT-2 has G = 1; the
 //     other rows are zero), so grouped heads read their keys once;
-//   * each of the 4 warps takes every 4th chunk of 32 keys and owns a ring of chunk buffers in
-//     shared memory, filled by cp.async 16 bytes at a time through the block table (a chunk is
-//     two 16-position blocks, each inside one page) and never touched by another warp: no
-//     block-wide barrier in the loop, two or three chunks in flight per warp;
+//   * each of the NW (4 or 8) warps takes every NW-th chunk of 32 keys and owns a ring of chunk
+//     buffers in shared memory, filled by cp.async 16 bytes at a time through the block table
+//     (a chunk is two 16-position blocks, each inside one page) and never touched by another
+//     warp: no block-wide barrier in the loop, one to three chunks in flight per warp;
 //   * S = Q K^T and O += P V are mma.sync m16n8k16 (bf16 in, float32 accumulate) on fragments
 //     fetched with ldmatrix from XOR-swizzled tiles; scores are multiplied by the scale after
 //     the dot product (heteroserve/model/torch_engine.py:135); running maximum, sum and O are
@@ -26,7 +26,7 @@
 
 namespace hs {
 
-constexpr int DM_WARPS = 4;
+constexpr int DM_WARPS = 4;             // fewest warps per CTA (the launcher picks 4 or 8)
 constexpr int DM_CHUNK = 32;            // keys per chunk
 
 struct DecodeMmaParams {
@@ -91,19 +91,19 @@ __device__ __forceinline__ uint32_t dm_pack(float lo, float hi) {
   return *(uint32_t*)&v;
 }
 
-template <int D, int STAGES_>
+template <int D, int STAGES_, int NW_ = DM_WARPS>
 struct DmShape {
   static constexpr int CPR = D / 8;
   static constexpr int STAGES = STAGES_;
   static constexpr int CHUNK_PIECES = DM_CHUNK * CPR;            // uint4 per chunk of keys
   static constexpr int WARP_PIECES = STAGES * 2 * CHUNK_PIECES;  // keys and values
-  static constexpr size_t SMEM = (size_t)DM_WARPS * WARP_PIECES * 16;
+  static constexpr size_t SMEM = (size_t)NW_ * WARP_PIECES * 16;
 };
 
-template <int D, int STAGES_>
-__global__ void __launch_bounds__(DM_WARPS * 32)
+template <int D, int STAGES_, int NW>
+__global__ void __launch_bounds__(NW * 32)
 attention_decode_mma_kernel(const DecodeMmaParams p) {
-  using SH = DmShape<D, STAGES_>;
+  using SH = DmShape<D, STAGES_, NW>;
   constexpr int CPR = SH::CPR, STAGES = SH::STAGES;
   constexpr int KSTEPS = D / 16;       // k-steps of Q K^T
   constexpr int DT = D / 8;            // 8-wide tiles of the output
@@ -138,14 +138,14 @@ attention_decode_mma_kernel(const DecodeMmaParams p) {
   const int* trow = p.table + (size_t)r * p.max_pages;
   const __nv_bfloat16* own_row = p.qkv + (size_t)tok * p.qkv_stride;
 
-  // This warp's chunks are warp, warp + 4, ...; lane i keeps the page of the warp's i-th
+  // This warp's chunks are warp, warp + NW, ...; lane i keeps the page of the warp's i-th
   // 16-position block (two a chunk), so that no copy waits for a table lookup.
-  const int my_chunks = n_chunks > warp ? (n_chunks - warp + DM_WARPS - 1) / DM_WARPS : 0;
+  const int my_chunks = n_chunks > warp ? (n_chunks - warp + NW - 1) / NW : 0;
   int my_page = -1;
   {
     const int ci = lane >> 1, b = lane & 1;
     if (ci < my_chunks) {
-      const int j0 = k_begin + (warp + ci * DM_WARPS) * DM_CHUNK + b * 16;
+      const int j0 = k_begin + (warp + ci * NW) * DM_CHUNK + b * 16;
       if (j0 < k_end) {
         my_page = trow[j0 / PS];
         if (my_page < 0 || my_page >= p.num_pages) {
@@ -169,7 +169,7 @@ attention_decode_mma_kernel(const DecodeMmaParams p) {
   auto load_chunk = [&](int ci) {             // ci: index among this warp's chunks
     uint4* dK = ring + (size_t)(ci % STAGES) * 2 * SH::CHUNK_PIECES;
     uint4* dV = dK + SH::CHUNK_PIECES;
-    const int c0 = k_begin + (warp + ci * DM_WARPS) * DM_CHUNK;      // first key of the chunk
+    const int c0 = k_begin + (warp + ci * NW) * DM_CHUNK;      // first key of the chunk
     const int page_a = __shfl_sync(0xffffffffu, my_page, (2 * ci) & 31);
     const int page_b = __shfl_sync(0xffffffffu, my_page, (2 * ci + 1) & 31);
     // the two 16-position blocks of the chunk: where they start inside their pages
@@ -202,7 +202,7 @@ attention_decode_mma_kernel(const DecodeMmaParams p) {
   // it is this warp's) takes a row from the projection's output, so it comes after the wait.
   // Without fusion the previous kernel may be the one that appends this step's keys (up to
   // four positions of a request): nothing is requested before the wait.
-  const int own_ci = (own_chunk >= 0 && own_chunk % DM_WARPS == warp) ? own_chunk / DM_WARPS : -1;
+  const int own_ci = (own_chunk >= 0 && own_chunk % NW == warp) ? own_chunk / NW : -1;
   const int first_fill = min(STAGES, my_chunks);                  // chunks of the first ring fill
   int n_pre = first_fill;
   if (!p.fuse_append) n_pre = 0;
@@ -263,7 +263,7 @@ attention_decode_mma_kernel(const DecodeMmaParams p) {
     __syncwarp();
     const uint4* tK = ring + (size_t)(ci % STAGES) * 2 * SH::CHUNK_PIECES;
     const uint4* tV = tK + SH::CHUNK_PIECES;
-    const int c0 = k_begin + (warp + ci * DM_WARPS) * DM_CHUNK;
+    const int c0 = k_begin + (warp + ci * NW) * DM_CHUNK;
     float s[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
@@ -346,9 +346,9 @@ attention_decode_mma_kernel(const DecodeMmaParams p) {
 
   // ---- merge the warps' partial results through the ring memory (all copies have landed)
   __syncthreads();
-  float* s_m = (float*)dm_smem;                       // [DM_WARPS][16]
-  float* s_l = s_m + DM_WARPS * 16;                   // [DM_WARPS][16]
-  float* s_o = s_l + DM_WARPS * 16;                   // [DM_WARPS][16][D]
+  float* s_m = (float*)dm_smem;                       // [NW][16]
+  float* s_l = s_m + NW * 16;                   // [NW][16]
+  float* s_o = s_l + NW * 16;                   // [NW][16][D]
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
@@ -371,10 +371,10 @@ attention_decode_mma_kernel(const DecodeMmaParams p) {
     const int row = e / D, d = e - row * D;
     float cm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < DM_WARPS; ++w) cm = fmaxf(cm, s_m[w * 16 + row]);
+    for (int w = 0; w < NW; ++w) cm = fmaxf(cm, s_m[w * 16 + row]);
     float cl = 0.f, a = 0.f;
 #pragma unroll
-    for (int w = 0; w < DM_WARPS; ++w) {
+    for (int w = 0; w < NW; ++w) {
       const float mw = s_m[w * 16 + row];
       const float ws = (mw == -INFINITY) ? 0.f : dm_ex2(mw - cm);
       cl += s_l[w * 16 + row] * ws;
@@ -425,17 +425,17 @@ attention_decode_mma_kernel(const DecodeMmaParams p) {
     p.counters[slot * p.n_heads + hk * G + threadIdx.x] = 0;        // ready for the next launch
 }
 
-template <int D, int STAGES_>
+template <int D, int STAGES_, int NW = DM_WARPS>
 static cudaError_t dm_launch(const DecodeMmaParams& p, dim3 grid, cudaStream_t st, bool pdl) {
-  auto kern = attention_decode_mma_kernel<D, STAGES_>;
+  auto kern = attention_decode_mma_kernel<D, STAGES_, NW>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)DmShape<D, STAGES_>::SMEM);
+                                         (int)DmShape<D, STAGES_, NW>::SMEM);
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  return hs_launch(kern, grid, dim3(DM_WARPS * 32), DmShape<D, STAGES_>::SMEM, st, pdl, p);
+  return hs_launch(kern, grid, dim3(NW * 32), DmShape<D, STAGES_, NW>::SMEM, st, pdl, p);
 }
 
 }  // namespace hs
@@ -482,20 +482,30 @@ HS_EXPORT int hs_attention_decode_mma(void* out, const void* qkv, void* pool, co
   dim3 grid(token_cap, n_kv_heads, splits);
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t le;
-  // Three chunks in flight per warp while at most two CTAs per SM are wanted; beyond that two,
-  // so that a third CTA fits an SM and the fixed parts of a CTA overlap more of the streaming
-  // (measured at batch 48 and 64).  Head size 128: two (its chunks are twice as large).
+  // Shape by the number of CTAs against the SMs (measured with 16 heads of 64 at contexts of
+  // 200 and 760): up to one CTA per SM, 8 warps with two chunks in flight each (128 KB); up to
+  // two per SM, 8 warps with one chunk each (64 KB, so that two or three CTAs share an SM);
+  // beyond that 4 warps with two chunks, and a third CTA per SM covers the fixed parts of the
+  // others.  Head size 128 has chunks twice as large: one stage where 64 has two.
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
-  const bool deep = (long long)token_cap * n_kv_heads * splits <= 2LL * sms;
+  const long long ctas = (long long)token_cap * n_kv_heads * splits;
+  const int load = ctas <= sms ? 0 : (ctas <= 2LL * sms ? 1 : 2);
+  const bool dep = pdl != 0;
   switch (head_dim) {
     case 32:
-      le = deep ? dm_launch<32, 3>(p, grid, st, pdl != 0) : dm_launch<32, 2>(p, grid, st, pdl != 0);
+      le = load == 0   ? dm_launch<32, 3, 8>(p, grid, st, dep)
+           : load == 1 ? dm_launch<32, 2, 8>(p, grid, st, dep)
+                       : dm_launch<32, 2, 4>(p, grid, st, dep);
       break;
     case 64:
-      le = deep ? dm_launch<64, 3>(p, grid, st, pdl != 0) : dm_launch<64, 2>(p, grid, st, pdl != 0);
+      le = load == 0   ? dm_launch<64, 2, 8>(p, grid, st, dep)
+           : load == 1 ? dm_launch<64, 1, 8>(p, grid, st, dep)
+                       : dm_launch<64, 2, 4>(p, grid, st, dep);
       break;
-    case 128: le = dm_launch<128, 2>(p, grid, st, pdl != 0); break;
+    case 128:
+      le = load == 0 ? dm_launch<128, 1, 8>(p, grid, st, dep) : dm_launch<128, 2, 4>(p, grid, st, dep);
+      break;
     default: return HS_ERR_UNSUPPORTED;
   }
   if (le != cudaSuccess) return (int)le;

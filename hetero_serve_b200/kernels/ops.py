@@ -194,8 +194,8 @@ class CudaOps:
         self._scratch: dict = {}
         self._retired: list = []
         self.decode_force = None   # (wide code, slices) of the decode attention, for tuning
-        self.decode_mma = True     # batches beyond one (token, head) per SM: tensor-core decode
-        #                            attention ("always": whatever the batch, for tests)
+        self.decode_mma = True     # tensor-core decode attention where the shape allows it
+        #                            (head size 32/64/128, at most 16 query heads per kv head)
         self.takes_status_word = True   # sample() can store the status word behind the tokens
         self.tile_n = 0            # 0: chosen per shape; 64/128/256 force a tile width
         self.cta_pairs = -1        # -1: pairs of CTAs (cta_group::2) when there are many rows;
@@ -561,8 +561,6 @@ class CudaOps:
             max_ctx = g.max_pages * g.page_size
             group = g.n_heads // g.n_kv_heads
             use_mma = (self.decode_mma and self.decode_force is None
-                       and (plan.decode_cap * g.n_heads > self.sm_count
-                            or self.decode_mma == "always")
                        and g.head_dim in (32, 64, 128) and group <= 16)
             splits = (max(1, -(-max_ctx // 2048)) if use_mma
                       else self.decode_splits(plan.decode_cap, g.n_heads, max_ctx))

@@ -284,15 +284,15 @@ def _host_batch(lens, new):
 
 @pytest.fixture
 def decode_kernel(request, ops):
-    """Which kernel serves single-query tokens: chosen by batch size, always the tensor-core
-    one (head sizes 32/64/128), or never."""
+    """Which kernel serves single-query tokens: the tensor-core one where the shape allows it
+    (head sizes 32/64/128), or the CUDA-core one everywhere."""
     was = ops.decode_mma
-    ops.decode_mma = {"auto": True, "tensor_cores": "always", "cuda_cores": False}[request.param]
+    ops.decode_mma = {"tensor_cores": True, "cuda_cores": False}[request.param]
     yield request.param
     ops.decode_mma = was
 
 
-DECODE_KERNELS = ["auto", "tensor_cores", "cuda_cores"]
+DECODE_KERNELS = ["tensor_cores", "cuda_cores"]
 
 
 FAST_CASES = [
@@ -348,7 +348,10 @@ DECODE_ONLY = [
     (2, 1, 16, 16, [33, 2]),
     (6, 2, 64, 16, [1, 2, 31, 32, 33, 64, 65, 500, 1000, 96, 97]),  # grouped heads, chunk edges
     (3, 3, 32, 48, [200, 49, 48, 47, 700]),                        # pages of 48, head size 32
-    (20, 20, 64, 16, [600] * 16),                                  # 320 pairs: chosen by size
+    (20, 20, 64, 16, [600] * 16),                                  # 320 pairs: narrow CTAs
+    (16, 16, 64, 16, [300, 31, 97] * 4),                           # 192 pairs: between the two
+    (8, 8, 32, 16, [150, 33] * 12),                                # the same for head size 32
+    (8, 8, 32, 16, [70] * 40),
 ]
 
 
