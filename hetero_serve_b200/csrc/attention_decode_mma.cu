@@ -425,17 +425,37 @@ attention_decode_mma_kernel(const DecodeMmaParams p) {
     p.counters[slot * p.n_heads + hk * G + threadIdx.x] = 0;        // ready for the next launch
 }
 
+template <int D, int STAGES_, int NW>
+static cudaError_t dm_configure() {
+  static cudaError_t state = cudaErrorUnknown;
+  if (state != cudaSuccess)
+    state = cudaFuncSetAttribute(attention_decode_mma_kernel<D, STAGES_, NW>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)DmShape<D, STAGES_, NW>::SMEM);
+  return state;
+}
+
+// CTAs of this shape that share an SM (0: could not be asked)
+template <int D, int STAGES_, int NW>
+static int dm_occupancy() {
+  static int occ = -1;
+  if (occ < 0) {
+    int n = 0;
+    if (dm_configure<D, STAGES_, NW>() != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+            &n, attention_decode_mma_kernel<D, STAGES_, NW>, NW * 32,
+            DmShape<D, STAGES_, NW>::SMEM) != cudaSuccess)
+      return 0;
+    occ = n;
+  }
+  return occ;
+}
+
 template <int D, int STAGES_, int NW = DM_WARPS>
 static cudaError_t dm_launch(const DecodeMmaParams& p, dim3 grid, cudaStream_t st, bool pdl) {
-  auto kern = attention_decode_mma_kernel<D, STAGES_, NW>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)DmShape<D, STAGES_, NW>::SMEM);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
-  return hs_launch(kern, grid, dim3(NW * 32), DmShape<D, STAGES_, NW>::SMEM, st, pdl, p);
+  if (cudaError_t e = dm_configure<D, STAGES_, NW>()) return e;
+  return hs_launch(attention_decode_mma_kernel<D, STAGES_, NW>, grid, dim3(NW * 32),
+                   DmShape<D, STAGES_, NW>::SMEM, st, pdl, p);
 }
 
 }  // namespace hs
@@ -486,7 +506,8 @@ HS_EXPORT int hs_attention_decode_mma(void* out, const void* qkv, void* pool, co
   // 200 and 760): up to one CTA per SM, 8 warps with two chunks in flight each (128 KB); up to
   // two per SM, 8 warps with one chunk each (64 KB, so that two or three CTAs share an SM);
   // beyond that 4 warps with two chunks, and a third CTA per SM covers the fixed parts of the
-  // others.  Head size 128 has chunks twice as large: one stage where 64 has two.
+  // others.  Head size 128 has chunks twice as large: one chunk in flight per warp (with 32 heads
+  // over 8 key/value heads at batch 64: 49 us against 74 with two).
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
   const long long ctas = (long long)token_cap * n_kv_heads * splits;
@@ -499,12 +520,21 @@ HS_EXPORT int hs_attention_decode_mma(void* out, const void* qkv, void* pool, co
                        : dm_launch<32, 2, 4>(p, grid, st, dep);
       break;
     case 64:
-      le = load == 0   ? dm_launch<64, 2, 8>(p, grid, st, dep)
-           : load == 1 ? dm_launch<64, 1, 8>(p, grid, st, dep)
-                       : dm_launch<64, 2, 4>(p, grid, st, dep);
+      if (load == 2) {
+        // One chunk in flight per warp lets a fourth CTA share an SM: taken when that leaves
+        // fewer empty places in the last round of CTAs (1,024 CTAs: 2 rounds of 592 places
+        // instead of 3 of 444; 768 CTAs: 2 of 444 instead of 2 of 592).
+        const long long two = (long long)dm_occupancy<64, 2, 4>() * sms;
+        const long long one = (long long)dm_occupancy<64, 1, 4>() * sms;
+        if (two <= 0 || one <= 0) return HS_ERR_UNSUPPORTED;
+        const bool shallow = (ctas + one - 1) / one * one < (ctas + two - 1) / two * two;
+        le = shallow ? dm_launch<64, 1, 4>(p, grid, st, dep) : dm_launch<64, 2, 4>(p, grid, st, dep);
+        break;
+      }
+      le = load == 0 ? dm_launch<64, 2, 8>(p, grid, st, dep) : dm_launch<64, 1, 8>(p, grid, st, dep);
       break;
     case 128:
-      le = load == 0 ? dm_launch<128, 1, 8>(p, grid, st, dep) : dm_launch<128, 2, 4>(p, grid, st, dep);
+      le = load == 0 ? dm_launch<128, 1, 8>(p, grid, st, dep) : dm_launch<128, 1, 4>(p, grid, st, dep);
       break;
     default: return HS_ERR_UNSUPPORTED;
   }

@@ -352,6 +352,7 @@ DECODE_ONLY = [
     (16, 16, 64, 16, [300, 31, 97] * 4),                           # 192 pairs: between the two
     (8, 8, 32, 16, [150, 33] * 12),                                # the same for head size 32
     (8, 8, 32, 16, [70] * 40),
+    (16, 16, 64, 16, [90, 17, 160, 33] * 8),                       # 512 pairs: four CTAs an SM
 ]
 
 
