@@ -29,6 +29,7 @@ import numpy as np
 import torch
 
 from ..cache import CacheManager, CacheStorage, GroupSpec
+from ..kernels.ops import size_class
 
 STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a position outside the table",
                4: "a page number outside the pool", 8: "a kernel pipeline timed out"}
@@ -324,8 +325,8 @@ class Runner:
             mgr.reserve(e.req_id, start + len(e.tokens))      # OutOfPages: nothing ran
 
         if self.use_graphs:
-            T, R = _bucket(n_tok, 8), _bucket(len(entries), 1)
-            W = _bucket(n_want, 1) if n_want else 0
+            T, R = max(8, size_class(n_tok)), size_class(len(entries))
+            W = size_class(n_want) if n_want else 0
         else:
             T, R, W = n_tok, len(entries), n_want
         lay = self._layout(T, R, W)
@@ -427,9 +428,9 @@ class Runner:
                 torch.cuda.synchronize(self.device)
                 graph = torch.cuda.CUDAGraph()
                 # An object freed by the garbage collector in the middle of a capture (an
-                # older runner's graphs, say) would invalidate it: collect first, then hold
-                # the collector off until the capture has ended.
-                gc.collect()
+                # older runner's graphs, say) would invalidate it: hold the collector off
+                # until the capture has ended.  (No collection beforehand: it takes 25-35 ms,
+                # four times the rest of a capture.)
                 gc_was_on = gc.isenabled()
                 gc.disable()
                 before = getattr(self.ops, "launches", 0)

@@ -82,6 +82,16 @@ def _pow2(n: int) -> int:
     return b
 
 
+def size_class(n: int) -> int:
+    """The size a count is rounded up to where shapes must repeat (captured graphs): powers of
+    two up to 8, then four classes per doubling (10, 12, 14, 16, 20, 24, 28, 32, 40, 48, ...),
+    so that padding stays below a quarter of the work."""
+    if n <= 8:
+        return _pow2(n)
+    step = _pow2(n) // 8
+    return -(-n // step) * step
+
+
 def plan_tile_slots(n_rows: int) -> int:
     """Tile entries a plan holds: every tile a batch of n_rows tokens can have, rounded up to
     a power of two (grids are sized in powers of two when steps are captured)."""
@@ -472,7 +482,8 @@ class CudaOps:
         view[0], view[1], view[2], view[3] = n_dec, n_tiles, max_ctx, 0
         single = single and n_dec > 0
         if bucketed:
-            return (_pow2(n_dec) if n_dec else 0, _pow2(n_tiles) if n_tiles else 0, single)
+            return (size_class(n_dec) if n_dec else 0, size_class(n_tiles) if n_tiles else 0,
+                    single)
         return n_dec, n_tiles, single
 
     def make_plan(self, host_batch, n_rows: int, page_size: int) -> AttentionPlan:
