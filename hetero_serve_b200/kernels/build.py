@@ -126,13 +126,15 @@ def build(force: bool = False, verbose: bool = True) -> Path:
             o.unlink()
         except OSError:
             pass
-    # older libraries of other source versions are of no use to anyone
-    for old in bdir.glob(f"{LIB_STEM}-*.so"):
-        if old != lib:
-            try:
-                old.unlink()
-            except OSError:
-                pass
+    # older libraries of other source versions are of no use to anyone, nor are the objects an
+    # interrupted build left behind (an hour old: no build still running wrote them)
+    stale = [old for old in bdir.glob(f"{LIB_STEM}-*.so") if old != lib]
+    stale += [o for o in bdir.glob("*.o") if time.time() - o.stat().st_mtime > 3600]
+    for old in stale:
+        try:
+            old.unlink()
+        except OSError:
+            pass
     if verbose:
         _say(f"built {lib.name} in {time.time() - t0:.0f}s")
     return lib
