@@ -361,7 +361,8 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (p.K + TC_BK - 1) / TC_BK;
   const int n_items = p.tiles_m * p.tiles_n * p.splits;
-  constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;
+  // columns from one accumulator to the other: a power of two (192-wide tiles sit 256 apart)
+  constexpr uint32_t ACC_COLS = BN < 32 ? 32 : (BN == 192 ? 256 : BN);
   constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;          // 64 .. 512, a power of two
 
   pdl_trigger();       // the next kernel may set itself up while this one runs
@@ -867,7 +868,7 @@ static bool plan_tc(int M, int N, int K, int tile_n, int pair, TcPlan& pl) {
     // A tile's time grows with the bytes it loads per k-block (128 + width rows) plus a fixed
     // part; pick the width for which rounds over the SMs x that is smallest.
     long best = -1;
-    for (int cand : {256, 128, 64}) {
+    for (int cand : {256, 192, 128, 64}) {
       if (cand > 64 && cand / 2 >= N) continue;
       const long tiles = (long)mt * ((N + cand - 1) / cand);
       const long cost = ((tiles + sms - 1) / sms) * (cand + 128 + 64);
@@ -880,7 +881,7 @@ static bool plan_tc(int M, int N, int K, int tile_n, int pair, TcPlan& pl) {
     // vocabulary) has tiles enough and reads the activations less often with 128 columns
     if (mt == 1) bn = ((N + 63) / 64 >= 2 * sms) ? 128 : 64;
   }
-  if (bn != 64 && bn != 128 && bn != 256) return false;
+  if (bn != 64 && bn != 128 && bn != 192 && bn != 256) return false;
   pl.bn = bn;
   pl.tiles_m = mt;
   pl.tiles_n = (N + bn - 1) / bn;
@@ -960,6 +961,7 @@ HS_EXPORT int hs_linear_tcgen05(void* out, const void* a, const void* w, const f
   }
   switch (pl.bn) {
     case 256: return HS_TC(256, 4);
+    case 192: return HS_TC(192, 5);
     case 128: return HS_TC(128, 6);
     default: return HS_TC(64, 8);
   }

@@ -207,7 +207,7 @@ class CudaOps:
         self.decode_mma = True     # tensor-core decode attention where the shape allows it
         #                            (head size 32/64/128, at most 16 query heads per kv head)
         self.takes_status_word = True   # sample() can store the status word behind the tokens
-        self.tile_n = 0            # 0: chosen per shape; 64/128/256 force a tile width
+        self.tile_n = 0            # 0: chosen per shape; 64/128/192/256 force a tile width
         self.cta_pairs = -1        # -1: pairs of CTAs (cta_group::2) when there are many rows;
         #                            0: never; 1: always
         self.skinny_max_rows = 16  # up to this many rows the weight-streaming kernel is used
