@@ -11,9 +11,14 @@
 // A work item is up to 128 consecutive queries of one request x one head.  CTAs are persistent;
 // the host lists the items with the most keys first and CTA b walks b, 2G-1-b, 2G+b, ... (a snake
 // over the sorted list, G CTAs), so every role knows its sequence and runs ahead on its own.
-//   warp 0      TMA producer: the Q tile [128 x 64] once per item; per 128-key tile, one
-//               [16 x 64] box of K and of V per 16-position block, found through the block table
-//               (a page holds whole blocks), into a four-stage ring;
+//   warp 0      TMA producer, all 32 lanes: the Q tile [128 x 64] once per item (two buffers, so
+//               the next item's queries are fetched while this item's MMAs still run); per
+//               128-key tile, one [16 x 64] box of K and of V per 16-position block, found
+//               through the block table (a page holds whole blocks), into a four-stage ring:
+//               lanes 0..7 look the eight blocks up and copy the keys, lanes 8..15 the values,
+//               lane 0 waits for the ring slot and announces the bytes (with one lane doing
+//               all of it the producer barely kept ahead: the softmax threads waited 30 % of
+//               their time for S, now 18 %);
 //   warp 1      one thread issues  S[b] = Q K^T  (M=128, N=128, 4 k-steps) into one of two TMEM
 //               buffers, and  O_tile = P V  (M=128, N=64, 8 k-steps, V as the N-contiguous
 //               operand) once the softmax warps have written P;
@@ -41,7 +46,7 @@ constexpr int TA_KV_BYTES = TA_BKV * TA_D * 2;           // 16 KB per K or V til
 constexpr int TA_P_BYTES = TA_BQ * TA_BKV * 2;           // 32 KB: two 64-key k-blocks
 // padded beyond half of an SM's shared memory: two of these CTAs must never share an SM, since
 // each allocates all 512 TMEM columns
-constexpr int TA_SMEM = TA_Q_BYTES + 2 * TA_KV_STAGES * TA_KV_BYTES + TA_P_BYTES + 256 + 1024 + 4096;
+constexpr int TA_SMEM = 2 * TA_Q_BYTES + 2 * TA_KV_STAGES * TA_KV_BYTES + TA_P_BYTES + 256 + 1024 + 4096;
 
 struct PrefillTcParams {
   __nv_bfloat16* out;
@@ -52,14 +57,16 @@ struct PrefillTcParams {
   int* work_counter;
   int n_heads, n_kv_heads, page_size, num_pages, max_pages, q_off, ps_log2;
   float scale;
-  unsigned long long* timing;   // null, or 8 x uint64 per CTA: cycles per softmax phase
+  unsigned long long* timing;   // null, or 8 x uint64 per CTA: cycles per softmax phase (0 wait
+                                // for S, 1 maximum, 2 exponentials, 3 wait for P V and add O,
+                                // 4 write P, 5 loop, 6 last O, 7 wait for an item's first S)
 };
 
 // barriers, in this order in shared memory
-enum { B_Q_FULL = 0, B_KV_FULL = 1, B_KV_EMPTY = 1 + TA_KV_STAGES, B_S_FULL = 1 + 2 * TA_KV_STAGES,
+enum { B_Q_FULL = 0, B_KV_FULL = 2, B_KV_EMPTY = 2 + TA_KV_STAGES, B_S_FULL = 2 + 2 * TA_KV_STAGES,
        B_S_EMPTY = B_S_FULL + 2, B_P_FULL = B_S_EMPTY + 2, B_P_EMPTY = B_P_FULL + 1,
        B_O_FULL = B_P_EMPTY + 1, B_O_EMPTY = B_O_FULL + 1, B_Q_EMPTY = B_O_EMPTY + 1,
-       B_COUNT = B_Q_EMPTY + 1 };
+       B_COUNT = B_Q_EMPTY + 2 };
 
 __device__ __forceinline__ float ex2_fast(float x) {
   float y;
@@ -74,8 +81,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem;
-  uint8_t* sK = sQ + TA_Q_BYTES;                          // [stages][128 keys][128 B]
+  uint8_t* sQ = smem;                                     // [2 items][128 queries][128 B]
+  uint8_t* sK = sQ + 2 * TA_Q_BYTES;                      // [stages][128 keys][128 B]
   uint8_t* sV = sK + TA_KV_STAGES * TA_KV_BYTES;
   uint8_t* sP = sV + TA_KV_STAGES * TA_KV_BYTES;          // [2 k-blocks][128 rows][128 B]
   uint64_t* bars = (uint64_t*)(sP + TA_P_BYTES);
@@ -91,8 +98,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   constexpr uint32_t TMEM_COLS = 512;
 
   if (threadIdx.x == 0) {
-    mbar_init(&bars[B_Q_FULL], 1);
-    mbar_init(&bars[B_Q_EMPTY], 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[B_Q_FULL + i], 1);
+      mbar_init(&bars[B_Q_EMPTY + i], 1);
+    }
     for (int i = 0; i < TA_KV_STAGES; ++i) {
       mbar_init(&bars[B_KV_FULL + i], 1);
       mbar_init(&bars[B_KV_EMPTY + i], 1);
@@ -144,60 +153,62 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int* trow = p.table + (size_t)r * p.max_pages;
 
     if (warp == 0) {
+      // ---------------- TMA producer: the whole warp.  Lane 0 waits and announces the bytes;
+      // lanes 0..7 look up the pages of the tile's eight 16-position blocks and copy their keys,
+      // lanes 8..15 the values, so that a tile costs one table round trip and one issue slot
+      // per lane.  Q has two buffers: the next item's queries never wait for this item's MMAs.
+      const int qb = n_item & 1;
       if (lane == 0) {
-        // ---------------- TMA producer
-        if (n_item > 0) ok = mbar_wait(&bars[B_Q_EMPTY], (n_item - 1) & 1, p.status);
+        if (n_item >= 2)
+          ok = mbar_wait(&bars[B_Q_EMPTY + qb], ((n_item >> 1) - 1) & 1, p.status);
         if (ok) {
-          mbar_expect_tx(&bars[B_Q_FULL], TA_Q_BYTES);
-          tma_load_2d(sQ, &map_q, &bars[B_Q_FULL], p.q_off + h * TA_D, tok0);
+          mbar_expect_tx(&bars[B_Q_FULL + qb], TA_Q_BYTES);
+          tma_load_2d(sQ + qb * TA_Q_BYTES, &map_q, &bars[B_Q_FULL + qb], p.q_off + h * TA_D,
+                      tok0);
         }
-        for (int kt = 0; kt < n_kv && ok; ++kt) {
-          const uint32_t it = n_tile + kt;
-          const int st = it % TA_KV_STAGES;
+      }
+      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+      const int v_rows = p.n_kv_heads * PS;                // from a page's keys to its values
+      for (int kt = 0; kt < n_kv && ok; ++kt) {
+        const uint32_t it = n_tile + kt;
+        const int st = it % TA_KV_STAGES;
+        // blocks of 16 positions up to the item's last one; the lookup needs only the table,
+        // so it comes before the wait for the ring slot
+        const int first = kt * TA_BKV;
+        const int n_blocks = min(TA_BKV / 16, (pos_last - first) / 16 + 1);
+        const int b = lane & 7;
+        int src_row = -1;          // row of the block's first position in the [rows, 64] view
+        if (lane < 16 && b < n_blocks) {
+          const int j = first + b * 16;
+          const int pg = p.ps_log2 >= 0 ? (j >> p.ps_log2) : (j / PS);
+          const int page = trow[pg];
+          if (page < 0 || page >= p.num_pages) {
+            if (lane < 8) atomicOr(p.status, HS_STATUS_BAD_PAGE);
+          } else {
+            src_row = ((page * 2) * p.n_kv_heads + hk) * PS + (j - pg * PS) +
+                      (lane >= 8 ? v_rows : 0);
+          }
+        }
+        const unsigned good = __ballot_sync(0xffffffffu, src_row >= 0) & 0xffu;   // key blocks
+        if (lane == 0) {
           if (it >= TA_KV_STAGES)
             ok = mbar_wait(&bars[B_KV_EMPTY + st], ((it / TA_KV_STAGES) - 1) & 1, p.status);
-          if (!ok) break;
-          // blocks of 16 positions up to the item's last one
-          const int first = kt * TA_BKV;
-          const int n_blocks = min(TA_BKV / 16, (pos_last - first) / 16 + 1);
-          int pages[TA_BKV / 16];
-          int good = 0;
-#pragma unroll
-          for (int b = 0; b < TA_BKV / 16; ++b) {
-            pages[b] = -1;
-            if (b < n_blocks) {
-              const int j = first + b * 16;
-              const int pg = p.ps_log2 >= 0 ? (j >> p.ps_log2) : (j / PS);
-              const int page = trow[pg];
-              if (page < 0 || page >= p.num_pages) {
-                atomicOr(p.status, HS_STATUS_BAD_PAGE);
-              } else {
-                // row of the block's first position in the [rows, 64] view of the pool
-                pages[b] = ((page * 2) * p.n_kv_heads + hk) * PS + (j - pg * PS);
-                ++good;
-              }
-            }
-          }
-          mbar_expect_tx(&bars[B_KV_FULL + st], good * 2 * 16 * TA_D * 2);
-          const int v_rows = p.n_kv_heads * PS;            // from a page's keys to its values
-#pragma unroll
-          for (int b = 0; b < TA_BKV / 16; ++b) {
-            if (pages[b] >= 0) {
-              tma_load_2d(sK + st * TA_KV_BYTES + b * 2048, &map_kv, &bars[B_KV_FULL + st], 0,
-                          pages[b]);
-              tma_load_2d(sV + st * TA_KV_BYTES + b * 2048, &map_kv, &bars[B_KV_FULL + st], 0,
-                          pages[b] + v_rows);
-            }
-          }
+          if (ok) mbar_expect_tx(&bars[B_KV_FULL + st], __popc(good) * 2 * 16 * TA_D * 2);
         }
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok) break;
+        if (src_row >= 0)
+          tma_load_2d((lane >= 8 ? sV : sK) + st * TA_KV_BYTES + b * 2048, &map_kv,
+                      &bars[B_KV_FULL + st], 0, src_row);
       }
     } else if (warp == 1) {
       if (lane == 0) {
         // ---------------- MMA issuer
         constexpr uint32_t idesc_s = make_idesc(TA_BQ, TA_BKV, false);
         constexpr uint32_t idesc_o = make_idesc(TA_BQ, TA_D, true);
-        const uint32_t q_addr = smem_u32(sQ);
-        ok = mbar_wait(&bars[B_Q_FULL], n_item & 1, p.status);
+        const int qb = n_item & 1;
+        const uint32_t q_addr = smem_u32(sQ + qb * TA_Q_BYTES);
+        ok = mbar_wait(&bars[B_Q_FULL + qb], (n_item >> 1) & 1, p.status);
         auto issue_s = [&](int kt) -> bool {
           const uint32_t it = n_tile + kt;
           const int st = it % TA_KV_STAGES, sb = it & 1;
@@ -213,7 +224,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                       idesc_s, k > 0 ? 1u : 0u);
           umma_commit(&bars[B_S_FULL + sb]);
           // the item's last S: once it has completed, Q may be replaced by the next item's
-          if (kt == n_kv - 1) umma_commit(&bars[B_Q_EMPTY]);
+          if (kt == n_kv - 1) umma_commit(&bars[B_Q_EMPTY + qb]);
           return true;
         };
         if (ok) ok = issue_s(0);
@@ -285,7 +296,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         ok = mbar_wait(&bars[B_S_FULL + sb], (it >> 1) & 1, p.status);
         if (!ok) break;
         tc_fence_after();
-        lap(0);
+        lap(kt == 0 ? 7 : 0);
         const int j0 = kt * TA_BKV + half * 64;             // first key of this thread's half
         const bool diagonal = kt * TA_BKV + TA_BKV - 1 > pos0;   // some row needs the mask
         const uint32_t s_addr = lane_addr + sb * S_COLS + half * 64;
