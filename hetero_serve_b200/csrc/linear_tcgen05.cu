@@ -385,8 +385,23 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // Everything above (barriers, tensor memory) touches nothing an earlier kernel writes; from
-  // here on activations, the residual stream and the split-k scratch are read.
+  // Everything above (barriers, tensor memory) touches nothing an earlier kernel writes, and
+  // neither do the weights: the weight tiles of the first work item's first stages are
+  // requested here, before the dependency wait, so that their way from DRAM overlaps the
+  // kernel before; the activations of those stages follow after the wait.  From there on
+  // activations, the residual stream and the split-k scratch are read.
+  int pre = 0;                                  // stages whose weight tile is already requested
+  if (threadIdx.x == 0 && (int)blockIdx.x < n_items) {
+    const int tile = blockIdx.x / p.splits, split = blockIdx.x - tile * p.splits;
+    const int n0 = (tile % p.tiles_n) * BN;
+    const int kb0 = split * p.kb_per_split;
+    pre = min(STAGES, min(kb0 + p.kb_per_split, num_kb) - kb0);
+    for (int i = 0; i < pre; ++i) {
+      mbar_expect_tx(&full_bar[i], S::STAGE_BYTES);
+      tma_load_2d(smem + i * S::STAGE_BYTES + S::A_BYTES, &map_w, &full_bar[i],
+                  (kb0 + i) * TC_BK, n0);
+    }
+  }
   pdl_wait();
 
   if (warp == 0) {
@@ -406,9 +421,11 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           if (!ok) break;
           uint8_t* a_dst = smem + s * S::STAGE_BYTES;
           uint8_t* b_dst = a_dst + S::A_BYTES;
-          mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+          if ((int)it >= pre) {
+            mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+            tma_load_2d(b_dst, &map_w, &full_bar[s], kb * TC_BK, n0);
+          }
           tma_load_2d(a_dst, &map_a, &full_bar[s], kb * TC_BK, m0);
-          tma_load_2d(b_dst, &map_w, &full_bar[s], kb * TC_BK, n0);
         }
       }
     }
