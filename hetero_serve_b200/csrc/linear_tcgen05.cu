@@ -757,6 +757,227 @@ linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 }
 
 // ---------------------------------------------------------------- host side
+// ---------------------------------------------------------------------------------------------
+// Few rows, deep layer: the k splits of a tile as a thread-block cluster.
+//
+// One row tile (M <= 128), tiles of 64 columns, 2..8 splits over k.  The CTAs of a cluster are
+// the splits of one tile: each runs its k range into tensor memory as above, then the partial
+// tiles are exchanged through distributed shared memory instead of scratch in global memory:
+// the tile's rows are dealt to the CTAs of the cluster, every CTA sends each row of its partial
+// to the row's owner (st.shared::cluster), one hardware cluster barrier follows, and each owner
+// adds the shares of its rows in split order and applies bias, activation and residual.  No
+// counters, no fences, and the last step is spread over all CTAs of the cluster (with scratch
+// and a counter the last CTA to arrive swept the whole tile alone: 3.5 us of a 9.4 us launch
+// at 64 x 3072 x 1024).
+constexpr int CL_BN = 64, CL_STAGES = 6, CL_MAX_SPLITS = 8;
+
+struct ClSmem {
+  static constexpr int A_BYTES = TC_BM * TC_BK * 2;
+  static constexpr int B_BYTES = CL_BN * TC_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int RED_OFFSET = CL_STAGES * STAGE_BYTES;
+  // [splits][rows per owner][64] floats; splits * rows per owner < 128 + splits
+  static constexpr int RED_BYTES = (TC_BM + CL_MAX_SPLITS) * CL_BN * 4;
+  static constexpr int BAR_OFFSET = RED_OFFSET + RED_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + (2 * CL_STAGES + 1) * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ void st_cluster_f4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
+                                              uint32_t d) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b),
+               "r"(c), "r"(d)
+               : "memory");
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+linear_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_a,
+                              const __grid_constant__ CUtensorMap map_w, const TcParams p) {
+  using S = ClSmem;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  float* red = (float*)(smem + S::RED_OFFSET);
+  uint64_t* full_bar = (uint64_t*)(smem + S::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + CL_STAGES;
+  uint64_t* acc_full = empty_bar + CL_STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int splits = p.splits;                       // = the cluster's size
+  const int rank = (int)cluster_ctarank();           // = this CTA's split
+  const int tile = blockIdx.x / splits;
+  const int m0 = (tile / p.tiles_n) * TC_BM, n0 = (tile % p.tiles_n) * CL_BN;
+  const int num_kb = (p.K + TC_BK - 1) / TC_BK;
+  const int kb0 = rank * p.kb_per_split;
+  const int kb1 = min(kb0 + p.kb_per_split, num_kb);
+  constexpr uint32_t TMEM_COLS = CL_BN;
+
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < CL_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // the weights do not change during a step: the first stages' weight tiles are requested
+  // before the dependency wait
+  int pre = 0;
+  if (threadIdx.x == 0) {
+    pre = min(CL_STAGES, kb1 - kb0);
+    for (int i = 0; i < pre; ++i) {
+      mbar_expect_tx(&full_bar[i], S::STAGE_BYTES);
+      tma_load_2d(smem + i * S::STAGE_BYTES + S::A_BYTES, &map_w, &full_bar[i],
+                  (kb0 + i) * TC_BK, n0);
+    }
+  }
+  // every CTA of the cluster has started: its shared memory may be written by the others
+  __syncwarp();
+  cluster_sync();
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer
+      bool ok = true;
+      for (int kb = kb0, it = 0; kb < kb1 && ok; ++kb, ++it) {
+        const int s = it % CL_STAGES;
+        const int round = it / CL_STAGES;
+        if (round > 0) ok = mbar_wait(&empty_bar[s], (round - 1) & 1, p.status);
+        if (!ok) break;
+        uint8_t* a_dst = smem + s * S::STAGE_BYTES;
+        if (it >= pre) {
+          mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+          tma_load_2d(a_dst + S::A_BYTES, &map_w, &full_bar[s], kb * TC_BK, n0);
+        }
+        tma_load_2d(a_dst, &map_a, &full_bar[s], kb * TC_BK, m0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer
+      constexpr uint32_t idesc = make_idesc(TC_BM, CL_BN);
+      bool ok = true;
+      for (int kb = kb0, it = 0; kb < kb1 && ok; ++kb, ++it) {
+        const int s = it % CL_STAGES;
+        ok = mbar_wait(&full_bar[s], (it / CL_STAGES) & 1, p.status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
+        const uint64_t adesc = make_smem_desc(a_addr);
+        const uint64_t bdesc = make_smem_desc(a_addr + S::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < TC_BK / TC_UMMA_K; ++k)
+          umma_bf16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
+                    (kb > kb0 || k > 0) ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(acc_full);            // the partial tile is complete (or the pipeline gave up)
+    }
+  }
+
+  // rows of the tile that exist, dealt to the CTAs of the cluster in blocks of `rpo`
+  const int rows_here = min(TC_BM, p.M - m0);
+  const int rpo = (rows_here + splits - 1) / splits;
+  const int et = threadIdx.x - 4 * 32;                   // 0..255 among the epilogue threads
+  if (warp >= 4) {
+    // ---------------- send: warp (w % 4) owns TMEM lanes 32*(w%4) .. +31 = rows of the tile,
+    // the two groups of four warps take the two halves of the 64 columns
+    const int q = warp & 3, half = (warp - 4) >> 2;
+    const int row = q * 32 + lane;
+    if (mbar_wait(acc_full, 0, p.status)) {
+      tc_fence_after();
+      uint32_t v[32];
+      tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + half * 32, v);
+      tmem_ld_wait();
+      if (row < rows_here) {
+        const int owner = row / rpo, lr = row - owner * rpo;
+        const uint32_t dst =
+            cluster_map(red + ((size_t)(rank * rpo + lr) * CL_BN + half * 32), (uint32_t)owner);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          st_cluster_f4(dst + 16 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      }
+    }
+    tc_fence_before();
+  }
+  // all shares have arrived everywhere (every thread of every CTA comes here, also after a
+  // time-out, whose status bit tells the host that the result is not to be used)
+  __syncwarp();
+  cluster_sync();
+
+  if (warp >= 4) {
+    // ---------------- this CTA's rows: shares added in split order, then the epilogue
+    const int my_first = rank * rpo;
+    const int my_rows = max(0, min(rpo, rows_here - my_first));
+    TO* out = (TO*)p.out;
+    const bool vec4 = (p.N % 4 == 0);
+    constexpr int PIECES = CL_BN / 4;
+    for (int e = et; e < my_rows * PIECES; e += TC_EPI_WARPS * 32) {
+      const int lr = e / PIECES, c = (e % PIECES) * 4;
+      const int n = n0 + c;
+      if (n >= p.N) continue;
+      const size_t off = (size_t)(m0 + my_first + lr) * p.N + n;
+      float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), r4 = b4;
+      if (vec4) {
+        if (p.bias) b4 = __ldg((const float4*)(p.bias + n));
+        if (p.residual) r4 = *(const float4*)(p.residual + off);
+      } else {
+        float* bb = (float*)&b4;
+        float* rr = (float*)&r4;
+        for (int j = 0; j < 4; ++j)
+          if (n + j < p.N) {
+            if (p.bias) bb[j] = p.bias[n + j];
+            if (p.residual) rr[j] = p.residual[off + j];
+          }
+      }
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int sp = 0; sp < splits; ++sp) {
+        const float4 sh = *(const float4*)(red + ((size_t)(sp * rpo + lr) * CL_BN + c));
+        a.x += sh.x; a.y += sh.y; a.z += sh.z; a.w += sh.w;
+      }
+      float x[4] = {a.x + b4.x, a.y + b4.y, a.z + b4.z, a.w + b4.w};
+      if (p.act == HS_ACT_GELU_TANH) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[j] = act_tc(x[j], HS_ACT_GELU_TANH);
+      } else if (p.act == HS_ACT_GELU_ERF) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[j] = act_tc(x[j], HS_ACT_GELU_ERF);
+      }
+      x[0] += r4.x; x[1] += r4.y; x[2] += r4.z; x[3] += r4.w;
+      if (vec4) {
+        if constexpr (sizeof(TO) == 4) {
+          *(float4*)((float*)out + off) = make_float4(x[0], x[1], x[2], x[3]);
+        } else {
+          __nv_bfloat162 p0 = __floats2bfloat162_rn(x[0], x[1]);
+          __nv_bfloat162 p1 = __floats2bfloat162_rn(x[2], x[3]);
+          uint2 o;
+          o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1;
+          *(uint2*)((__nv_bfloat16*)out + off) = o;
+        }
+      } else {
+        for (int j = 0; j < 4; ++j)
+          if (n + j < p.N) out[off + j] = from_f<TO>(x[j]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -840,10 +1061,74 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const TcPar
   return HS_OK;
 }
 
+template <typename TO>
+static int launch_cluster(const CUtensorMap& ma, const CUtensorMap& mw, const TcParams& p,
+                          int tiles, cudaStream_t st) {
+  auto kern = linear_tcgen05_cluster_kernel<TO>;
+  constexpr int smem = ClSmem::TOTAL;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles * p.splits);
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = p.splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = hs_pdl_enabled() ? 2 : 1;
+  cudaError_t le = cudaLaunchKernelEx(&cfg, kern, ma, mw, p);
+  if (le != cudaSuccess) return (int)le;
+  HS_LAUNCH_CHECK();
+  return HS_OK;
+}
+
 struct TcPlan {
   int bn, splits, kb_per_split, tiles_m, tiles_n, grid;
   bool pair;
+  bool cluster;      // the splits of a tile exchange their shares inside a cluster: no scratch
 };
+
+static bool g_split_clusters = true;
+
+
+// How many clusters of `size` CTAs of the cluster kernel the device holds at once (asked once
+// per size; 0: the question could not be asked).
+static int cluster_capacity(int size) {
+  static int cached[CL_MAX_SPLITS + 1] = {0};
+  static bool asked[CL_MAX_SPLITS + 1] = {false};
+  if (size < 1 || size > CL_MAX_SPLITS) return 0;
+  if (asked[size]) return cached[size];
+  asked[size] = true;
+  auto kern = linear_tcgen05_cluster_kernel<float>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ClSmem::TOTAL) !=
+      cudaSuccess)
+    return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(size * 64);
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = ClSmem::TOTAL;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = size;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) n = 0;
+  cached[size] = n;
+  return n;
+}
 
 // pair: -1 = decide here, 0 = single CTAs, 1 = pairs of CTAs (256-row tiles)
 static bool plan_tc(int M, int N, int K, int tile_n, int pair, TcPlan& pl) {
@@ -853,6 +1138,7 @@ static bool plan_tc(int M, int N, int K, int tile_n, int pair, TcPlan& pl) {
   const int num_kb = (K + TC_BK - 1) / TC_BK;
   // measured on B200: pairs gain 5-9 % from 4,096 rows on (4096^3, 8192^3) and nothing at 2,048
   pl.pair = pair == 1 || (pair < 0 && M >= 4096);
+  pl.cluster = false;
   if (pl.pair) {
     // 256 x BN tiles over sms / 2 pairs; a CTA loads 128 + BN/2 rows per k-block
     const int pairs = sms / 2 > 0 ? sms / 2 : 1;
@@ -911,9 +1197,25 @@ static bool plan_tc(int M, int N, int K, int tile_n, int pair, TcPlan& pl) {
     if (splits > num_kb / 2) splits = num_kb / 2;
     if (splits < 1) splits = 1;
     if (splits > 16) splits = 16;
+    // One row tile of 64-column tiles: the splits form a cluster, as many as the device holds
+    // at once for all tiles.  A cluster that has to wait for the next round costs more than
+    // its splits save: of this kernel 74 clusters of two fit, 45 of three, 33 of four, 22 of
+    // six, 15 of eight, so 48 tiles take two splits and 16 tiles six.  Measured in a decode
+    // step of GPT-2 medium at batch 32: 1.23 ms, against 1.53 ms with the shares going through
+    // scratch memory (3, 8, 2 and 8 splits).
+    if (g_split_clusters && mt == 1 && bn == CL_BN) {
+      int pick = 0;
+      for (int cand = 2; cand <= splits && cand <= CL_MAX_SPLITS; ++cand)
+        if (cluster_capacity(cand) >= tiles) pick = cand;
+      if (pick) {
+        pl.cluster = true;
+        splits = pick;
+      }
+    }
   }
   pl.kb_per_split = (num_kb + splits - 1) / splits;
   pl.splits = (num_kb + pl.kb_per_split - 1) / pl.kb_per_split;
+  if (pl.splits < 2) pl.cluster = false;
   const int items = tiles * pl.splits;
   pl.grid = items < sms ? items : sms;
   return true;
@@ -928,10 +1230,16 @@ HS_EXPORT int hs_linear_tcgen05_scratch(int M, int N, int K, int tile_n, int pai
   hs::TcPlan pl;
   if (M <= 0 || N <= 0 || K <= 0 || !hs::plan_tc(M, N, K, tile_n, pair, pl))
     return HS_ERR_UNSUPPORTED;
-  *floats = pl.splits > 1 ? (long long)pl.splits * M * N : 0;
-  *counters = pl.splits > 1 ? pl.tiles_m * pl.tiles_n : 0;
+  const bool scratch = pl.splits > 1 && !pl.cluster;
+  *floats = scratch ? (long long)pl.splits * M * N : 0;
+  *counters = scratch ? pl.tiles_m * pl.tiles_n : 0;
   return HS_OK;
 }
+
+// Few rows split over k: the splits of a tile as a thread-block cluster that exchanges the
+// shares through distributed shared memory (on, the default), or through scratch memory and a
+// counter.  Scratch sizes depend on it: ask hs_linear_tcgen05_scratch again after a change.
+HS_EXPORT void hs_set_split_clusters(int on) { hs::g_split_clusters = on != 0; }
 
 // Returns HS_ERR_UNSUPPORTED for shapes the TMA path cannot take (K not a multiple of 8:
 // row strides must be multiples of 16 bytes; pointers not 16-byte aligned); the caller falls
@@ -952,7 +1260,7 @@ HS_EXPORT int hs_linear_tcgen05(void* out, const void* a, const void* w, const f
   if (out_dtype != HS_DT_F32 && out_dtype != HS_DT_BF16) return HS_ERR_UNSUPPORTED;
   TcPlan pl;
   if (!plan_tc(M, N, K, tile_n, pair, pl)) return HS_ERR_UNSUPPORTED;
-  if (pl.splits > 1 && (!scratch || !counters)) return HS_ERR_ARGUMENT;
+  if (pl.splits > 1 && !pl.cluster && (!scratch || !counters)) return HS_ERR_ARGUMENT;
   CUtensorMap ma, mw;
   if (int e = make_map(&ma, a, M, K, TC_BM)) return e;
   if (int e = make_map(&mw, w, N, K, pl.pair ? pl.bn / 2 : pl.bn)) return e;
@@ -969,6 +1277,10 @@ HS_EXPORT int hs_linear_tcgen05(void* out, const void* a, const void* w, const f
                                  : launch<BN, ST, bf16, true>(ma, mw, p, pl.grid, st))     \
        : (out_dtype == HS_DT_F32 ? launch<BN, ST, float, false>(ma, mw, p, pl.grid, st)    \
                                  : launch<BN, ST, bf16, false>(ma, mw, p, pl.grid, st)))
+  if (pl.cluster)
+    return out_dtype == HS_DT_F32
+               ? launch_cluster<float>(ma, mw, p, pl.tiles_m * pl.tiles_n, st)
+               : launch_cluster<bf16>(ma, mw, p, pl.tiles_m * pl.tiles_n, st);
   if (pl.pair) {
     if (pl.bn == 256)
       return out_dtype == HS_DT_F32 ? launch_pair<256, 6, float>(ma, mw, p, pl.grid, st)

@@ -149,6 +149,8 @@ def _declare(lib) -> None:
         fn.restype = c_int
     lib.hs_set_pdl.argtypes = [I]
     lib.hs_set_pdl.restype = None
+    lib.hs_set_split_clusters.argtypes = [I]
+    lib.hs_set_split_clusters.restype = None
 
 
 def _ptr(t):
@@ -210,6 +212,8 @@ class CudaOps:
         self.tile_n = 0            # 0: chosen per shape; 64/128/192/256 force a tile width
         self.cta_pairs = -1        # -1: pairs of CTAs (cta_group::2) when there are many rows;
         #                            0: never; 1: always
+        self.split_clusters = True  # few rows split over k: the splits of a tile exchange their
+        #                            shares inside a thread-block cluster (False: through scratch)
         self.skinny_max_rows = 16  # up to this many rows the weight-streaming kernel is used
         #                            (measured: from 17 rows on the tcgen05 kernel's split over k wins)
         # pipeline time-outs of the TMA/tcgen05 kernels are ORed into this word; the runner
@@ -316,7 +320,10 @@ class CudaOps:
             if self._skinny(out, a, None, w, bias, act, residual, M, N, K):
                 return
         if a.dtype == torch.bfloat16 and self.tensor_cores and K % 8 == 0:
-            key = (M, N, K, self.tile_n, self.cta_pairs)
+            if CudaOps._lib_split_clusters != bool(self.split_clusters):   # a switch of the library
+                CudaOps._lib_split_clusters = bool(self.split_clusters)
+                self.lib.hs_set_split_clusters(int(CudaOps._lib_split_clusters))
+            key = (M, N, K, self.tile_n, self.cta_pairs, bool(self.split_clusters))
             need = self._tc_need.get(key)
             if need is None:
                 floats, counters = ctypes.c_longlong(0), ctypes.c_int(0)
@@ -529,6 +536,7 @@ class CudaOps:
         return max(1, need, min(want, max(1, max_context // 64), 32))
 
     FAST_HEAD_DIMS = (16, 32, 64, 128)
+    _lib_split_clusters = True     # what the library's switch was last set to
 
     def _fast_ok(self, qkv, g, plan, n, scale=1.0) -> bool:
         return (plan is not None and self.fast_attention and qkv.dtype == torch.bfloat16

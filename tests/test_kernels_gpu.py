@@ -120,15 +120,17 @@ TC_SHAPES = [(1, 1000, 96), (5, 50257, 64), (16, 192, 320), (17, 1024, 1024), (4
 
 
 @pytest.mark.parametrize("M,N,K", TC_SHAPES + [(256, 128, 64), (700, 1000, 1000), (1024, 3072, 1024)])
-@pytest.mark.parametrize("path", ["few_rows", "tcgen05", "tiles_of_192", "cta_pairs"])
+@pytest.mark.parametrize("path", ["few_rows", "tcgen05", "splits_through_scratch", "tiles_of_192",
+                                  "cta_pairs"])
 def test_bfloat16_linear_kernels_each_on_its_own(ops, plain, M, N, K, path):
     """The weight-streaming kernel (up to 64 rows, k a multiple of 32), the tcgen05 kernel
-    (any rows; few rows take its split over k; once more with its 192-column tiles, which
+    (any rows; few rows take its split over k, whose shares travel inside a thread-block
+    cluster or, once more, through scratch memory; once more with its 192-column tiles, which
     the shapes here would not choose) and its variant on pairs of CTAs (cta_group::2, 256-row
     tiles) forced one at a time, all epilogues."""
     if path == "few_rows" and (M > 64 or K % 32):
         pytest.skip("the few-row kernel takes up to 64 rows and k in multiples of 32")
-    if path in ("few_rows", "tcgen05") and M > 300:
+    if path in ("few_rows", "tcgen05", "splits_through_scratch") and M > 300:
         pytest.skip("the larger shapes are there for the pairs and the 192-column tiles")
     if path == "tiles_of_192" and K % 8:
         pytest.skip("TMA needs rows of a multiple of 16 bytes")
@@ -138,10 +140,11 @@ def test_bfloat16_linear_kernels_each_on_its_own(ops, plain, M, N, K, path):
     a = torch.randn(M, K, device=DEV).bfloat16()
     w = (torch.randn(N, K, device=DEV) / K ** 0.5).bfloat16()
     bias = torch.randn(N, device=DEV)
-    saved = ops.skinny_max_rows, ops.cta_pairs, ops.tile_n
+    saved = ops.skinny_max_rows, ops.cta_pairs, ops.tile_n, ops.split_clusters
     ops.skinny_max_rows = 64 if path == "few_rows" else 0
     ops.cta_pairs = 1 if path == "cta_pairs" else 0
     ops.tile_n = 192 if path == "tiles_of_192" else 0
+    ops.split_clusters = path != "splits_through_scratch"
     try:
         for act, out_dtype, with_res in (("none", torch.bfloat16, False), ("gelu_tanh", torch.bfloat16, False),
                                          ("gelu_erf", torch.bfloat16, False), ("none", torch.float32, False),
@@ -165,7 +168,7 @@ def test_bfloat16_linear_kernels_each_on_its_own(ops, plain, M, N, K, path):
                 assert torch.equal(out, out2)
         assert ops.status.item() == 0
     finally:
-        ops.skinny_max_rows, ops.cta_pairs, ops.tile_n = saved
+        ops.skinny_max_rows, ops.cta_pairs, ops.tile_n, ops.split_clusters = saved
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 192, 64), (8, 3072, 1024), (16, 4096, 1024), (5, 288, 96),
