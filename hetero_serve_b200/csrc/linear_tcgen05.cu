@@ -760,7 +760,7 @@ linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 // ---------------------------------------------------------------------------------------------
 // Few rows, deep layer: the k splits of a tile as a thread-block cluster.
 //
-// One row tile (M <= 128), tiles of 64 columns, 2..8 splits over k.  The CTAs of a cluster are
+// Tiles of 64 columns (few rows), 2..8 splits over k.  The CTAs of a cluster are
 // the splits of one tile: each runs its k range into tensor memory as above, then the partial
 // tiles are exchanged through distributed shared memory instead of scratch in global memory:
 // the tile's rows are dealt to the CTAs of the cluster, every CTA sends each row of its partial
@@ -1197,13 +1197,13 @@ static bool plan_tc(int M, int N, int K, int tile_n, int pair, TcPlan& pl) {
     if (splits > num_kb / 2) splits = num_kb / 2;
     if (splits < 1) splits = 1;
     if (splits > 16) splits = 16;
-    // One row tile of 64-column tiles: the splits form a cluster, as many as the device holds
-    // at once for all tiles.  A cluster that has to wait for the next round costs more than
+    // 64-column tiles split over k: the splits of a tile form a cluster, as many as the device
+    // holds at once for all tiles.  A cluster that has to wait for the next round costs more than
     // its splits save: of this kernel 74 clusters of two fit, 45 of three, 33 of four, 22 of
     // six, 15 of eight, so 48 tiles take two splits and 16 tiles six.  Measured in a decode
     // step of GPT-2 medium at batch 32: 1.23 ms, against 1.53 ms with the shares going through
     // scratch memory (3, 8, 2 and 8 splits).
-    if (g_split_clusters && mt == 1 && bn == CL_BN) {
+    if (g_split_clusters && bn == CL_BN) {
       int pick = 0;
       for (int cand = 2; cand <= splits && cand <= CL_MAX_SPLITS; ++cand)
         if (cluster_capacity(cand) >= tiles) pick = cand;
