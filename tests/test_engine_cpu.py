@@ -130,3 +130,23 @@ def test_a_token_can_be_taken_from_the_device_copy(tiny_models):
     with pytest.raises(StepError, match="token id"):
         rn.step([StepEntry("b", [3, FROM_DEVICE])])
     rn.manager.check()
+
+
+def test_size_classes_bound_the_padding():
+    """Counts are rounded up to size classes where shapes must repeat: never below the count,
+    monotone, powers of two up to 8, then four classes per doubling (padding under a quarter)."""
+    from hetero_serve_b200.kernels.ops import size_class
+    assert [size_class(n) for n in (1, 2, 3, 5, 8)] == [1, 2, 4, 8, 8]
+    assert [size_class(n) for n in (9, 16, 17, 33, 48, 49, 64, 65, 2048, 2049)] == \
+        [10, 16, 20, 40, 48, 56, 64, 80, 2048, 2560]
+    last = 0
+    classes = set()
+    for n in range(1, 5000):
+        c = size_class(n)
+        assert c >= n and c >= last
+        assert c == size_class(c)                  # a class is its own class
+        if n > 8:
+            assert (c - n) / n < 0.25
+        last = c
+        classes.add(c)
+    assert len(classes) <= 4 + 4 * 10              # 8 .. 8192: ten doublings
