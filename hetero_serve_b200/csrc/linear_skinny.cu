@@ -386,6 +386,18 @@ static bool plan_skinny(int M, int N, int K, bool with_norm, SkinnyPlan& pl) {
     pl.smem = smem_for(K, stride);
     return true;
   }
+  // 9-16 rows with the LayerNorm fused in, more feature blocks than SMs: 16 warps per CTA and
+  // two feature groups, so that a warp normalises one row instead of two and one round of CTAs
+  // covers the layer (a decode step at batch 16: 0.92 ms against 0.97).
+  if (pl.mt == 2 && with_norm && pl.ng == 1 && K <= SK_LN_ROW_F4 * 128 && pl.blocks > sms) {
+    pl.ng = 2;
+    pl.blocks = (N + 31) / 32;
+    pl.nw = 16;
+    pl.ksplit = 1;
+    pl.kper = K;
+    pl.smem = smem_for(K, pl.stride);
+    return true;
+  }
   // otherwise: k per CTA at most what fits ~96 KB of shared memory, at least 1024 (four blocks
   // a warp), and few enough splits that about two CTAs per SM are in flight
   const size_t budget = 96 * 1024;
