@@ -30,7 +30,7 @@ import hashlib
 import struct
 from collections import OrderedDict
 from dataclasses import dataclass, field
-from typing import Hashable, Iterable, Sequence
+from typing import Callable, Hashable, Iterable, Sequence
 
 
 class OutOfPages(RuntimeError):
@@ -220,6 +220,10 @@ class CacheManager:
         self._requests: dict[Hashable, _Request] = {}
         self.hit_tokens = 0
         self.miss_tokens = 0
+        # called with the state slot of every request that is opened, whoever opens it (the
+        # step function, the scheduler): the owner of the state tensors clears the slot here,
+        # so that a request never starts on what the slot's previous owner left
+        self.on_open: Callable[[int], None] | None = None
 
     # -- queries ------------------------------------------------------------
     def __contains__(self, req_id) -> bool:
@@ -281,6 +285,8 @@ class CacheManager:
             self.hit_tokens += req.cached_tokens
             self.miss_tokens += len(token_ids) - req.cached_tokens
         self._requests[req_id] = req
+        if self.on_open is not None:
+            self.on_open(req.slot)
         return Opened(req.slot, req.cached_tokens)
 
     def pages_needed(self, req_id, new_len: int) -> list[int]:
@@ -304,6 +310,22 @@ class CacheManager:
         for gi, (n, pool) in enumerate(zip(need, self.pools)):
             if n:
                 req.tables[gi].extend(pool.take(n))
+
+    def table_lengths(self, req_id) -> list[int]:
+        return [len(t) for t in self._get(req_id).tables]
+
+    def unreserve(self, req_id, lengths: Sequence[int]) -> None:
+        """Give back the pages reserved beyond ``lengths`` (what :meth:`table_lengths` said
+        before the reservation): undoes a :meth:`reserve` whose step did not run."""
+        req = self._get(req_id)
+        for gi, (n, pool) in enumerate(zip(lengths, self.pools)):
+            if self.pages_for(req.length) > n:
+                raise CacheError("unreserve below the resident positions")
+            table = req.tables[gi]
+            while len(table) > n:
+                page = table.pop()
+                if page >= 0:
+                    pool.drop(page)
 
     def commit(self, req_id, new_len: int) -> None:
         """Positions < new_len are now resident.  Pages of a windowed group that no later

@@ -509,7 +509,7 @@ HS_EXPORT int hs_attention_decode_mma(void* out, const void* qkv, void* pool, co
   // others.  Head size 128 has chunks twice as large: one chunk in flight per warp (with 32 heads
   // over 8 key/value heads at batch 64: 49 us against 74 with two).
   int sms = 148;
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+  sms = hs_sm_count();
   const long long ctas = (long long)token_cap * n_kv_heads * splits;
   const int load = ctas <= sms ? 0 : (ctas <= 2LL * sms ? 1 : 2);
   const bool dep = pdl != 0;

@@ -314,7 +314,7 @@ static int launch_prefill(const PrefillParams& p, cudaStream_t st) {
     cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, AP_WARPS * 32,
                                                                   smem);
     if (e != cudaSuccess) return (int)e;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    sms = hs_sm_count();
     if (per_sm < 1) per_sm = 1;
     if (per_sm > 2) per_sm = 2;
     ctas = per_sm * sms;

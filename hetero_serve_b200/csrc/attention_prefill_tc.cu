@@ -511,13 +511,17 @@ HS_EXPORT int hs_attention_prefill_tc(void* out, const void* qkv, const void* po
   p.ps_log2 = (page_size & (page_size - 1)) == 0 ? __builtin_ctz(page_size) : -1;
   p.scale = scale;
   p.timing = hs_timing_buffer();
-  static int sms = 0;
-  if (sms == 0) {
+  static bool ready[64] = {};            // per device: the shared-memory attribute is set
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return HS_ERR_UNSUPPORTED;
+  if (!ready[dev]) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, TA_SMEM);
     if (e != cudaSuccess) return (int)e;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    ready[dev] = true;
   }
+  const int sms = hs_sm_count();
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t le = hs_launch(attention_prefill_tc_kernel, dim3(sms), dim3(TA_THREADS),
                              (size_t)TA_SMEM, st, hs_pdl_enabled(), mq, mkv, p);

@@ -37,6 +37,15 @@
 unsigned long long* hs_timing_buffer();   // embed_norm.cu
 bool hs_pdl_enabled();                    // embed_norm.cu: programmatic dependent launch on?
 
+// SM count of the device that is current when an entry point is called (the device of the
+// stream the caller passes; the engine makes its own device current around every step).
+static inline int hs_sm_count() {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess)
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms;
+}
+
 #define HS_LAUNCH_CHECK()                      \
   do {                                         \
     cudaError_t e__ = cudaGetLastError();      \

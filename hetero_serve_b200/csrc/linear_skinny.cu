@@ -361,7 +361,7 @@ static bool plan_skinny(int M, int N, int K, bool with_norm, SkinnyPlan& pl) {
   pl.mt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
   pl.mp = pl.mt * 8;
   int sms = 148;
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+  sms = hs_sm_count();
   // more features per CTA (the activations are staged less often) while the grid still fills
   // the GPU twice
   pl.ng = 1;

@@ -1133,7 +1133,7 @@ static int cluster_capacity(int size) {
 // pair: -1 = decide here, 0 = single CTAs, 1 = pairs of CTAs (256-row tiles)
 static bool plan_tc(int M, int N, int K, int tile_n, int pair, TcPlan& pl) {
   int sms = 148;
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+  sms = hs_sm_count();
   const int mt = (M + TC_BM - 1) / TC_BM;
   const int num_kb = (K + TC_BK - 1) / TC_BK;
   // measured on B200: pairs gain 5-9 % from 4,096 rows on (4096^3, 8192^3) and nothing at 2,048

@@ -28,7 +28,7 @@ from typing import Hashable, Sequence
 import numpy as np
 import torch
 
-from ..cache import CacheManager, CacheStorage, GroupSpec
+from ..cache import CacheManager, CacheStorage, GroupSpec, OutOfPages
 from ..kernels.ops import size_class
 
 STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a position outside the table",
@@ -225,19 +225,20 @@ class Runner:
     def __init__(self, model, *, num_pages: int, page_size: int, max_requests: int,
                  dtype: torch.dtype, device, ops=None, prefix_cache: bool = False,
                  cuda_graphs: bool = False):
+        self.device = torch.device(device)
         if ops is None:
             from ..kernels.ops import CudaOps
-            ops = CudaOps()
+            ops = CudaOps(self.device)
         self.ops = ops
         self.model = model
         self.dtype = dtype
-        self.device = torch.device(device)
         if model.dtype != dtype:
             raise StepError("the model was bound with another dtype than the runner's")
         self.manager = CacheManager(
             [GroupSpec(window=g.window) for g in model.cache_groups], num_pages, page_size,
             max_requests, prefix_cache=prefix_cache, has_state=bool(model.state_shapes))
         self.storage = CacheStorage(model, self.manager, dtype, self.device)
+        self.manager.on_open = self._clear_slot
         self.workspace = Workspace(self.device)
         self.max_positions = model.spec.max_positions
         self.max_pages = [self.manager.pages_for(self.max_positions) for _ in model.cache_groups]
@@ -262,10 +263,14 @@ class Runner:
     def open(self, req_id, token_ids=None):
         """Start a request (state slot; prefix pages if ``token_ids`` is given and prefix
         reuse is on).  Returns how many leading tokens are already cached."""
-        opened = self.manager.open(req_id, token_ids)
+        return self.manager.open(req_id, token_ids).cached_tokens
+
+    def _clear_slot(self, slot: int) -> None:
+        """Every request starts on zeroed state, whoever opened it (this runner, the scheduler
+        at admission or after a preemption): the manager calls this for each slot it hands
+        out."""
         for st in self.storage.states.values():
-            st[opened.slot].zero_()
-        return opened.cached_tokens
+            st[slot].zero_()
 
     def close(self, req_id) -> None:
         self.manager.close(req_id)
@@ -301,16 +306,18 @@ class Runner:
         seen = set()
         starts = []
         n_tok = n_want = 0
+        vocab = self.model.spec.vocab_size
         for e in entries:
             if e.req_id in seen:
                 raise StepError(f"request {e.req_id!r} appears twice in one step")
             seen.add(e.req_id)
-            if e.req_id not in mgr:
-                self.open(e.req_id)
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"request {e.req_id!r} brings no tokens")
-            start = mgr.length(e.req_id)
+            known = e.tokens[1:] if e.tokens[0] == FROM_DEVICE else e.tokens
+            if len(known) and not (0 <= min(known) and max(known) < vocab):
+                raise StepError(f"request {e.req_id!r}: token id outside [0, {vocab})")
+            start = mgr.length(e.req_id) if e.req_id in mgr else 0
             if start + n > self.max_positions:
                 raise StepError(f"request {e.req_id!r}: {start + n} positions exceed the "
                                 f"model's {self.max_positions}")
@@ -321,8 +328,25 @@ class Runner:
             starts.append(start)
             n_tok += n
             n_want += len(e.want)
-        for e, start in zip(entries, starts):
-            mgr.reserve(e.req_id, start + len(e.tokens))      # OutOfPages: nothing ran
+        # Nothing above changed anything.  Requests the cache does not know are opened here and
+        # pages are reserved entry by entry; if one cannot be had, what this step took so far
+        # is given back, so that a refused step leaves the cache as it found it.
+        taken: list[tuple[Hashable, list[int] | None]] = []     # (request, table lengths | opened)
+        try:
+            for e, start in zip(entries, starts):
+                if e.req_id not in mgr:
+                    self.open(e.req_id)
+                    taken.append((e.req_id, None))
+                else:
+                    taken.append((e.req_id, mgr.table_lengths(e.req_id)))
+                mgr.reserve(e.req_id, start + len(e.tokens))
+        except OutOfPages:
+            for req_id, lengths in taken:
+                if lengths is None:
+                    mgr.close(req_id)
+                else:
+                    mgr.unreserve(req_id, lengths)
+            raise
 
         if self.use_graphs:
             T, R = max(8, size_class(n_tok)), size_class(len(entries))
@@ -334,7 +358,6 @@ class Runner:
         if self._copy_done is not None:
             self._copy_done.synchronize()     # the previous step's upload has left the buffer
         hm = host.numpy()
-        vocab = self.model.spec.vocab_size
         hm[lay.tok_req:lay.tok_req + T] = -1
         hm[lay.tok_ids:lay.tok_ids + T] = 0
         hm[lay.tok_pos:lay.tok_pos + T] = 0
@@ -359,9 +382,6 @@ class Runner:
             toks = np.asarray(e.tokens, dtype=np.int64)
             slot = mgr.slot(e.req_id)
             from_device = int(toks[0]) == FROM_DEVICE
-            known = toks[1:] if from_device else toks
-            if known.size and (known.min() < 0 or known.max() >= vocab):
-                raise StepError(f"request {e.req_id!r}: token id outside [0, {vocab})")
             hm[lay.tok_ids + t:lay.tok_ids + t + n] = toks
             if from_device:
                 hm[lay.tok_ids + t] = -(slot + 1)

@@ -189,15 +189,23 @@ class CudaOps:
 
     name = "cuda"
 
-    def __init__(self):
+    def __init__(self, device=None):
         if not torch.cuda.is_available():
             raise KernelError("hetero_serve_b200 needs a CUDA device: its kernels have no CPU path")
+        dev = torch.device("cuda" if device is None else device)
+        if dev.type != "cuda":
+            raise KernelError(f"hetero_serve_b200 needs a CUDA device, got {dev}")
+        if dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        # One object drives one device.  Its kernels are launched on that device's current
+        # stream, so the device must be current while they are (the runner sees to it).
+        self.device = dev
         self.lib = load_library()
         self.launches = 0          # kernels launched through this object (graph captures count once)
         self.tensor_cores = True   # bfloat16 linears on tcgen05 (False: CUDA cores, for tests)
         self.fast_attention = True  # bfloat16 attention on the split-context / tensor-core kernels
         self.tc_attention = True    # head size 64: prompt portions on the tcgen05 attention kernel
-        self.sm_count = torch.cuda.get_device_properties(0).multi_processor_count
+        self.sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
         self.fuse_norm = True      # LayerNorm fused into the few-row linear kernel
         self.fuse_append = True    # key/value append fused into the decode attention
         self.pdl = True            # programmatic dependent launch (see the property below)
@@ -218,11 +226,10 @@ class CudaOps:
         #                            (measured: from 17 rows on the tcgen05 kernel's split over k wins)
         # pipeline time-outs of the TMA/tcgen05 kernels are ORed into this word; the runner
         # replaces it with its own so that they surface with the step's results
-        self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
 
-    @staticmethod
-    def _stream():
-        return torch.cuda.current_stream().cuda_stream
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
 
     @property
     def pdl(self) -> bool:
@@ -500,7 +507,7 @@ class CudaOps:
         view = np.zeros(self.attention_plan_ints(n_rows, len(host_batch)), dtype=np.int32)
         dec, tiles, single = self.plan_attention(view, host_batch, n_rows, len(host_batch),
                                                  page_size, False)
-        return AttentionPlan(torch.from_numpy(view).to("cuda"), n_rows, dec, tiles, single)
+        return AttentionPlan(torch.from_numpy(view).to(self.device), n_rows, dec, tiles, single)
 
     def _scratch_buffer(self, name, numel, dtype):
         key = (name, dtype)
@@ -508,7 +515,7 @@ class CudaOps:
         if buf is None or buf.numel() < numel:
             if buf is not None:
                 self._retired.append(buf)       # captured graphs may still point into it
-            buf = torch.zeros(max(numel, 1), dtype=dtype, device="cuda")
+            buf = torch.zeros(max(numel, 1), dtype=dtype, device=self.device)
             self._scratch[key] = buf
         return buf
 

@@ -158,10 +158,11 @@ def prepare_weights(tensors, dtype=torch.float64, round_to=None):
     return out
 
 
-def forward(config, weights, token_ids, dtype=torch.float64, start_pos=0):
+def forward(config, weights, token_ids, dtype=torch.float64, start_pos=0, rows=None):
     """Logits [T, vocab] of one whole sequence (positions start_pos..start_pos+T-1,
-    nothing cached).  Pre-LayerNorm blocks on a residual stream, in the reference's
-    order (heteroserve/model/numpy_engine.py:120-150):
+    nothing cached); with ``rows`` only the logits of these places, [len(rows), vocab]
+    (the head is the costly part of a long sequence).  Pre-LayerNorm blocks on a residual
+    stream, in the reference's order (heteroserve/model/numpy_engine.py:120-150):
         x = wte[ids] + wpe[pos]
         x = x + attn(ln_1(x));  x = x + mlp(ln_2(x))    for each layer
         logits = ln_f(x) @ wte^T
@@ -185,6 +186,8 @@ def forward(config, weights, token_ids, dtype=torch.float64, start_pos=0):
         x = x + attention_block(h, w, p, n_head, scale)
         h = layer_norm(x, w[p + "ln_2.weight"], w[p + "ln_2.bias"], eps)
         x = x + mlp_block(h, w, p, act)
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long)]
     return lm_logits(x, w, eps)
 
 

@@ -150,3 +150,24 @@ def test_size_classes_bound_the_padding():
         last = c
         classes.add(c)
     assert len(classes) <= 4 + 4 * 10              # 8 .. 8192: ten doublings
+
+
+def test_a_refused_step_leaves_the_cache_as_it_found_it(tiny_models):
+    """Pages run out at the THIRD entry of a step: what the first two took is given back, the
+    request the step opened on its own is closed again, and the step can be run in two."""
+    tiny = tiny_models["tiny_a"]
+    rn = _runner(tiny, pages=5)
+    a = tiny.tokens(40, 1)
+    rn.step([StepEntry("a", a[:20])])                         # a holds 2 pages
+    free, live = rn.manager.pages_free(), set(rn.manager.live())
+    with pytest.raises(OutOfPages):
+        rn.step([StepEntry("a", a[20:40]), StepEntry("b", [1] * 30), StepEntry("c", [2] * 20)])
+    assert rn.manager.pages_free() == free and set(rn.manager.live()) == live
+    assert rn.manager.length("a") == 20 and rn.manager.table_lengths("a") == [2]
+    rn.manager.check()
+    with pytest.raises(StepError, match="token id"):          # refused before anything is taken
+        rn.step([StepEntry("a", a[20:40]), StepEntry("d", [1, 999])])
+    assert rn.manager.pages_free() == free and "d" not in rn.manager
+    res = rn.step([StepEntry("a", a[20:40], want=[19])])
+    assert (res.logits[0].double() - tiny.logits(a)[39]).abs().max() < TOL
+    rn.manager.check()

@@ -5,8 +5,9 @@ they run (a loop with memory fixed at start-up, a process whose GPU memory is pr
 another allocator): it is the split-context decode attention with its scratch memory in a
 static device array instead of buffers the caller allocates.  This test calls the symbol
 with ``ctypes`` exactly as such a host would — raw pointers, no wrapper of the package — and
-checks its output against the existing entry point's (scratch allocated by PyTorch), twice
-in a row, since the second call finds the array as the first one left it.
+checks its output against the existing entry point's (scratch allocated by PyTorch) and
+against the plain implementation in float64, twice in a row, since the second call finds the
+array as the first one left it.
 
 It is collected last (the file name sorts after every other test file), so a run that stops
 at the first failure has already run everything else.
@@ -69,9 +70,17 @@ def test_no_alloc_entry_point_matches_the_allocating_one_twice_in_a_row():
     plan = ops.make_plan(host_batch, R, geom.page_size)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     scale = 0.125
-    # the existing entry point: scratch allocated by PyTorch
+    # the existing entry point: the same kernel (hs_attention_decode_append) with its scratch
+    # allocated by PyTorch; decode_mma off, or the wrapper would pick the tensor-core kernel
+    ops.decode_mma = False
     want = torch.empty(R, geom.n_heads * geom.head_dim, device=DEV, dtype=torch.bfloat16)
     ops.attention(want, qkv, pool, table, tok_pos, tok_req, geom, scale, status, plan)
+    # and the plain implementation in float64, so that a fault both entry points share shows
+    import plain_ops
+    plain = torch.empty(R, geom.n_heads * geom.head_dim, dtype=torch.float64)
+    plain_ops.PlainOps().attention(plain, qkv.cpu(), pool.cpu(), table.cpu(), tok_pos.cpu(),
+                                   tok_req.cpu(), geom, scale, None)
+    assert (want.double().cpu() - plain).abs().max() < 2e-2
     splits = ops.decode_splits(plan.decode_cap, geom.n_heads, geom.max_pages * geom.page_size)
     assert splits > 1                                    # the scratch memory really is used
     lib.hs_attention_decode_noalloc_capacity.restype = ctypes.c_longlong
@@ -89,6 +98,7 @@ def test_no_alloc_entry_point_matches_the_allocating_one_twice_in_a_row():
         assert torch.isfinite(got).all()
         # the tolerance the attention tests use for bfloat16 outputs
         assert (got.float() - want.float()).abs().max() < 2e-2, call
+        assert (got.double().cpu() - plain).abs().max() < 2e-2, call
     assert torch.cuda.mem_get_info()[0] == free_before   # nothing was allocated on the device
 
 
