@@ -7,9 +7,9 @@ a continuous-batching scheduler, device-side sampling, and hand-written CUDA ker
 """
 
 from . import architectures  # noqa: F401
-from .config import EngineConfig, GPT2Config, preset
+from .config import EngineConfig, preset
 from .engine import LLMEngine, Request, RequestRecord, Runner, StepEntry
 
 __version__ = "0.1.0"
-__all__ = ["EngineConfig", "GPT2Config", "LLMEngine", "Request", "RequestRecord", "Runner",
+__all__ = ["EngineConfig", "LLMEngine", "Request", "RequestRecord", "Runner",
            "StepEntry", "preset"]

@@ -18,14 +18,14 @@ import json
 import sys
 import time
 
-from .config import PRESETS, EngineConfig
+from .config import EngineConfig, preset_names
 from .engine import LLMEngine, Request
 
 
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="hetero_serve_b200", description=__doc__.split("\n\n")[0])
     ap.add_argument("--model", default="gpt2",
-                    help=f"named configuration for random weights: {', '.join(sorted(PRESETS))}")
+                    help=f"named configuration for random weights: {', '.join(preset_names())}")
     ap.add_argument("--weights", default="",
                     help="model folder (config.json + model.safetensors); overrides --model")
     ap.add_argument("--device", default="cuda:0")

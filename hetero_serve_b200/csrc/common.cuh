@@ -90,15 +90,20 @@ __device__ __forceinline__ float apply_act(float u, int act) {
   return u;
 }
 
-// Optional phase timing for tuning: when a buffer has been set with hs_set_timing_buffer, thread
-// 0 of every CTA of the instrumented kernels stores the global nanosecond timer at a few
-// marks: buffer[(cta * 8) + mark].  Null (the default) costs one predictable branch.
+// Phase timing for tuning builds only: compiled in with -DHS_PHASE_MARKS (the build script adds
+// it when HETERO_SERVE_PHASE_MARKS=1 is set).  Then, once a buffer has been set with
+// hs_set_timing_buffer, thread 0 of every CTA of the instrumented kernels stores the global
+// nanosecond timer at a few marks: buffer[(cta * 8) + mark].  The product build has none of it.
 __device__ __forceinline__ void mark_time(unsigned long long* buf, int cta, int mark) {
+#ifdef HS_PHASE_MARKS
   if (buf != nullptr && threadIdx.x == 0) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     buf[(size_t)cta * 8 + mark] = t;
   }
+#else
+  (void)buf; (void)cta; (void)mark;
+#endif
 }
 
 // Programmatic dependent launch: a kernel launched with the programmatic-serialization
@@ -106,6 +111,12 @@ __device__ __forceinline__ void mark_time(unsigned long long* buf, int cta, int 
 // the predecessor has completed and its writes are visible (a no-op for a normal launch);
 // `pdl_trigger` lets the successor start.  What a kernel does before `pdl_wait` must not read
 // anything an earlier kernel of the step writes (weights, block tables and work lists are safe).
+// The decode attention kernels also fetch cache pages of EARLIER positions before the wait.
+// Those were written by a kernel of an earlier step, and that is safe only because steps are
+// separated on the stream by an operation that is not a kernel (the upload of the step's
+// metadata): a programmatic launch overlaps its predecessor kernel, never a copy.  A caller
+// that chains steps without such an operation between them must launch these kernels without
+// the attribute (`pdl` = 0).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

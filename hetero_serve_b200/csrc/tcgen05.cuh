@@ -25,9 +25,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait.  Returns false (and records it) when the limit is hit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status,
+                                          uint32_t limit = HS_SPIN_LIMIT) {
   const uint32_t addr = smem_u32(bar);
-  for (uint32_t spin = 0; spin < HS_SPIN_LIMIT; ++spin) {
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     uint32_t done;
     asm volatile(
         "{\n"

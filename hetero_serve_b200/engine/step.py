@@ -226,6 +226,8 @@ class Runner:
                  dtype: torch.dtype, device, ops=None, prefix_cache: bool = False,
                  cuda_graphs: bool = False):
         self.device = torch.device(device)
+        if self.device.type == "cuda" and self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
         if ops is None:
             from ..kernels.ops import CudaOps
             ops = CudaOps(self.device)
@@ -299,8 +301,16 @@ class Runner:
 
     def step(self, entries: Sequence[StepEntry], sample: bool = False,
              check_status: bool = True) -> StepResult:
+        """Run one batch.  The kernels are launched on the current stream of the runner's own
+        device, which is made current for the duration if another one is."""
         if not entries:
             return StepResult(None, None, [], 0)
+        if self.cuda and torch.cuda.current_device() != self.device.index:
+            with torch.cuda.device(self.device):
+                return self._step(entries, sample, check_status)
+        return self._step(entries, sample, check_status)
+
+    def _step(self, entries, sample, check_status) -> StepResult:
         mgr = self.manager
         # ---- host side: validate, reserve pages, lay the batch out ----------------
         seen = set()
@@ -420,6 +430,10 @@ class Runner:
         if dev is None:
             dev = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
             self._dev_meta[key[:3]] = dev
+        # This copy is also what separates steps on the stream: it is not a kernel, so no
+        # kernel of this step, however early programmatic dependent launch lets it start, runs
+        # before every kernel of the step before has ended.  The decode attention relies on it
+        # when it prefetches keys of earlier positions before its dependency wait.
         dev.copy_(host[:lay.total], non_blocking=True)
         if self.cuda:
             if self._copy_done is None:
@@ -438,13 +452,19 @@ class Runner:
             if plan_shape is not None:
                 from ..kernels.ops import AttentionPlan
                 ctx.plan = AttentionPlan(dev[lay.plan:lay.plan + lay.plan_ints], T, *plan_shape)
-            if self.use_graphs and not self.model.state_shapes and self.model.capturable:
+            if self.use_graphs and self.model.capturable:
                 # run once eagerly (loads kernels, sizes buffers), then capture and replay.  The
                 # replay must see the same inputs as the eager run: all of them come from the
-                # metadata block except the tokens kept on the device, which sampling overwrites
+                # metadata block except the tokens kept on the device, which sampling
+                # overwrites, and the per-request state of stateful mixers, which the eager run
+                # has already advanced (the state tensors have fixed addresses, so a captured
+                # step reads and writes them like any other)
                 kept = self.feedback.clone()
+                kept_state = {k: st.clone() for k, st in self.storage.states.items()}
                 self._forward(ctx, sample)
                 self.feedback.copy_(kept)
+                for k, st in kept_state.items():
+                    self.storage.states[k].copy_(st)
                 torch.cuda.synchronize(self.device)
                 graph = torch.cuda.CUDAGraph()
                 # An object freed by the garbage collector in the middle of a capture (an

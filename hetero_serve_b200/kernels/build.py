@@ -30,6 +30,8 @@ CSRC = Path(__file__).resolve().parent.parent / "csrc"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
+if os.environ.get("HETERO_SERVE_PHASE_MARKS") == "1":      # a tuning build (see common.cuh)
+    NVCC_FLAGS = NVCC_FLAGS + ["-DHS_PHASE_MARKS"]
 LIB_STEM = "libhetero_serve_b200"
 
 
@@ -137,4 +139,35 @@ def build(force: bool = False, verbose: bool = True) -> Path:
             pass
     if verbose:
         _say(f"built {lib.name} in {time.time() - t0:.0f}s")
+    return lib
+
+
+def build_extension(name: str, srcs: list[str | Path], verbose: bool = False) -> Path:
+    """Compile CUDA sources that are not part of this package into a library of their own,
+    with the package's flags for sm_100a and ``csrc/`` on the include path (``common.cuh``
+    and ``tcgen05.cuh`` are there for them).  This is how a part defined elsewhere — another
+    architecture's mixer, a test's toy part — brings its kernels: it builds them here and
+    opens them with :meth:`CudaOps.load_extension`; nothing in this package changes.
+
+    The library is named after a hash of its sources and kept in the build folder, so a
+    second call returns at once."""
+    nvcc = find_nvcc()
+    paths = [Path(s) for s in srcs]
+    h = hashlib.sha256()
+    for p in paths:
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    for p in sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
+        h.update(p.read_bytes())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    bdir = _build_dir()
+    lib = bdir / f"lib{name}-{h.hexdigest()[:16]}.so"
+    if lib.is_file():
+        return lib
+    if verbose:
+        _say(f"compiling extension {name} ({len(paths)} files) for sm_100a ...")
+    tmp = bdir / f".{lib.name}.{os.getpid()}"
+    _run([nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-I", str(CSRC), "-shared", "-o", str(tmp),
+          *map(str, paths)], f"compiling extension {name}")
+    os.replace(tmp, lib)
     return lib

@@ -231,6 +231,41 @@ class CudaOps:
     def _stream(self):
         return torch.cuda.current_stream(self.device).cuda_stream
 
+    # -- kernels that parts bring themselves -------------------------------------------
+    def stream(self) -> int:
+        """The raw CUDA stream (of this object's device) kernels are to be launched on."""
+        return self._stream()
+
+    def register_kernel(self, symbol: str, argtypes, lib=None):
+        """Declare an ``extern "C"`` entry point (returning int in the convention of this
+        library: 0, a negative HS_ERR_* code or a positive cudaError_t) and return a function
+        that calls it, counts the launch and raises :class:`KernelError` on a non-zero code.
+        ``lib`` is a library opened with :meth:`load_extension`; by default the package's
+        own.  A part calls this once (in ``bind``) and the returned function in ``forward``
+        with raw pointers (``tensor.data_ptr()``), sizes and ``ops.stream()``."""
+        lib = lib or self.lib
+        try:
+            fn = getattr(lib, symbol)
+        except AttributeError:
+            raise KernelError(f"the library exports no symbol {symbol!r}") from None
+        fn.argtypes = list(argtypes)
+        fn.restype = c_int
+
+        def call(*args):
+            self.launches += 1
+            _check(fn(*args), symbol)
+        call.__name__ = symbol
+        return call
+
+    def load_extension(self, name: str, sources):
+        """Build (once) and open a library of CUDA sources from outside the package; see
+        :func:`hetero_serve_b200.kernels.build.build_extension`."""
+        path = _build.build_extension(name, sources)
+        try:
+            return ctypes.CDLL(str(path))
+        except OSError as exc:
+            raise KernelError(f"cannot load {path}: {exc}") from None
+
     @property
     def pdl(self) -> bool:
         """Programmatic dependent launch: kernels are launched so that their set-up (and what
@@ -599,21 +634,35 @@ class CudaOps:
                                            torch.int32)
             self.launches += 1
             if use_mma:
-                _check(self.lib.hs_attention_decode_mma(
+                code = self.lib.hs_attention_decode_mma(
                     _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(dec_info), _ptr(head),
                     plan.decode_cap, g.n_heads, g.n_kv_heads, g.head_dim, g.page_size,
                     g.num_pages, g.max_pages, g.q_off, g.k_off, g.v_off, g.qkv_stride, scale,
                     splits, int(bool(fuse)), int(self.pdl), _ptr(acc), _ptr(ml), _ptr(cnt),
-                    _ptr(status), st), f"attention_decode_mma(head_dim={g.head_dim})")
+                    _ptr(status), st)
+                what = f"attention_decode_mma(head_dim={g.head_dim})"
             else:
-                _check(self.lib.hs_attention_decode_append(
+                code = self.lib.hs_attention_decode_append(
                     _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req),
                     _ptr(dec_info), _ptr(head), plan.decode_cap, g.n_heads, g.n_kv_heads,
                     g.head_dim, g.page_size, g.num_pages, g.max_pages, g.q_off, g.k_off, g.v_off,
                     g.qkv_stride, g.window, scale, splits, int(bool(fuse)),
                     int(self.decode_wide(plan.decode_cap, g.n_heads)), int(self.pdl), _ptr(acc),
-                    _ptr(ml), _ptr(cnt),
-                    _ptr(status), st), f"attention_decode(head_dim={g.head_dim})")
+                    _ptr(ml), _ptr(cnt), _ptr(status), st)
+                what = f"attention_decode(head_dim={g.head_dim})"
+            if code == -1:
+                # a shape the decode kernels do not take: the general kernel serves every token
+                # of the batch (it needs no work list); a fused append is done first
+                if fuse:
+                    self.kv_append(pool, qkv, table, tok_pos, tok_req, g, status)
+                _check(self.lib.hs_attention_simt(
+                    _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req),
+                    out.shape[0], g.n_heads, g.n_kv_heads, g.head_dim, g.page_size, g.num_pages,
+                    g.max_pages, g.q_off, g.k_off, g.v_off, g.qkv_stride, g.window, scale,
+                    _DT[qkv.dtype], _ptr(status), st),
+                    f"attention(head_dim={g.head_dim}, heads={g.n_heads})")
+                return
+            _check(code, what)
         if plan.tile_cap:
             self.launches += 1
             counter = self._scratch_buffer("prefill_counter", 1, torch.int32)

@@ -16,17 +16,36 @@ from .spec import LayerCall, LayerSpec, ModelSpec
 
 
 class Block:
-    """A layer: its parts and the way they are wired."""
+    """A layer: its parts and the way they are wired.
+
+    An arrangement is a subclass that names its parts and their families in ``slots`` and
+    wires them in ``forward``.  The parts are built from the layer's spec and become
+    attributes of the same names.  At most one part of the mixer family may ask for a cache
+    entry or a state slot (a :class:`LayerCall` addresses one of each)."""
+
+    slots: Mapping[str, str] = {}          # part name -> family ("mixer", "feed_forward", "norm")
 
     def __init__(self, spec: LayerSpec):
         self.spec = spec
-        self.mixer = build_part("mixer", spec.mixer)
-        self.feed_forward = build_part("feed_forward", spec.feed_forward)
-        self.norm1 = build_part("norm", spec.norm1)
-        self.norm2 = build_part("norm", spec.norm2)
+        missing = [n for n in self.slots if n not in spec.parts]
+        extra = [n for n in spec.parts if n not in self.slots]
+        if missing or extra:
+            raise ValueError(f"arrangement {spec.arrangement!r} has the parts "
+                             f"{sorted(self.slots)}; missing {missing}, unknown {extra}")
+        self.named = {name: build_part(family, spec.parts[name])
+                      for name, family in self.slots.items()}
+        for name, part in self.named.items():
+            setattr(self, name, part)
+        holders = [p for n, p in self.named.items() if self.slots[n] == "mixer"
+                   and (p.cache_request() is not None or p.state_shape() is not None)]
+        if len(holders) > 1:
+            raise ValueError("a layer has two mixers that keep a cache or state; a layer call "
+                             "addresses one cache entry and one state slot")
+        mixers = [p for n, p in self.named.items() if self.slots[n] == "mixer"]
+        self.cache_holder = holders[0] if holders else (mixers[0] if mixers else None)
 
     def parts(self):
-        return (self.norm1, self.mixer, self.norm2, self.feed_forward)
+        return tuple(self.named.values())
 
     def forward(self, ctx, x, cache) -> None:
         raise NotImplementedError
@@ -35,6 +54,8 @@ class Block:
 class PreNormBlock(Block):
     """x += mixer(norm1(x)); x += feed_forward(norm2(x))
     (heteroserve/model/torch_engine.py:297-317)."""
+
+    slots = {"norm1": "norm", "mixer": "mixer", "norm2": "norm", "feed_forward": "feed_forward"}
 
     def forward(self, ctx, x, cache):
         h = ctx.buffer("normed", (x.shape[0], x.shape[1]), ctx.dtype)
@@ -111,7 +132,9 @@ class Model:
         entry_req: dict[int, CacheRequest] = {}
         self.state_shapes: dict[int, tuple[int, ...]] = {}     # schedule index -> shape
         for idx, call in enumerate(self.schedule):
-            mixer = self.blocks[call.layer].mixer
+            mixer = self.blocks[call.layer].cache_holder
+            if mixer is None:
+                continue
             req = mixer.cache_request()
             if req is not None:
                 if call.cache in entry_req and entry_req[call.cache] != req:

@@ -17,6 +17,7 @@ cache entry; ``writes_cache=False`` makes the call a reader only).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+from types import MappingProxyType
 from typing import Any, Mapping
 
 
@@ -29,18 +30,51 @@ class PartSpec:
         return hash((self.kind, tuple(sorted((k, repr(v)) for k, v in self.params.items()))))
 
 
-@dataclass(frozen=True)
 class LayerSpec:
-    """One block.  ``arrangement`` names how its parts are wired:
+    """One block: named parts and the arrangement that wires them.
 
-    ``pre_norm``:  x += mixer(norm1(x));  x += feed_forward(norm2(x))
+    ``parts`` maps a name to a :class:`PartSpec`.  Which names exist, and which family
+    (mixer, feed_forward, norm) each belongs to, is decided by the arrangement: the
+    ``pre_norm`` arrangement built here has ``norm1``, ``mixer``, ``norm2`` and
+    ``feed_forward``,
+
+        x += mixer(norm1(x));  x += feed_forward(norm2(x))
+
+    another arrangement may have others (one shared norm for a parallel block, norms after
+    the parts, no second norm).  Parts may be given as keywords:
+    ``LayerSpec(norm1=..., mixer=..., norm2=..., feed_forward=...)``.
     """
 
-    mixer: PartSpec
-    feed_forward: PartSpec
-    norm1: PartSpec
-    norm2: PartSpec
-    arrangement: str = "pre_norm"
+    __slots__ = ("arrangement", "parts")
+
+    def __init__(self, arrangement: str = "pre_norm",
+                 parts: Mapping[str, PartSpec] | None = None, **named: PartSpec):
+        merged = dict(parts or {})
+        merged.update(named)
+        for name, spec in merged.items():
+            if not isinstance(spec, PartSpec):
+                raise TypeError(f"part {name!r} of a layer must be a PartSpec, got {spec!r}")
+        object.__setattr__(self, "arrangement", arrangement)
+        object.__setattr__(self, "parts", MappingProxyType(merged))
+
+    def __setattr__(self, name, value):
+        raise AttributeError("a LayerSpec is immutable")
+
+    def __getattr__(self, name):            # ls.mixer, ls.norm1, ...: the part of that name
+        try:
+            return object.__getattribute__(self, "parts")[name]
+        except KeyError:
+            raise AttributeError(f"this layer has no part named {name!r}") from None
+
+    def __eq__(self, other):
+        return (isinstance(other, LayerSpec) and self.arrangement == other.arrangement
+                and dict(self.parts) == dict(other.parts))
+
+    def __hash__(self):
+        return hash((self.arrangement, tuple(sorted((k, hash(v)) for k, v in self.parts.items()))))
+
+    def __repr__(self):
+        return f"LayerSpec({self.arrangement!r}, {dict(self.parts)!r})"
 
 
 @dataclass(frozen=True)

@@ -4,7 +4,8 @@ import json
 
 import pytest
 
-from hetero_serve_b200.config import (Architecture, ConfigError, EngineConfig, GPT2Config,
+from hetero_serve_b200.architectures.gpt2 import GPT2Config
+from hetero_serve_b200.config import (Architecture, ConfigError, EngineConfig,
                                       architecture_of, load_model_config, preset,
                                       register_architecture, registered_architectures,
                                       unregister_architecture)

@@ -20,14 +20,14 @@ def _requests(tiny):
     return {f"r{i}": tiny.tokens(n, 100 + i) for i, n in enumerate(lens)}
 
 
-def _replay(tiny, steps, tmp_path, max_tokens):
+def _replay(tiny, steps, tmp_path, max_tokens, **kw):
     out = tmp_path / "out"
     out.mkdir(exist_ok=True)
     import io
     rep = io.StringIO()
     assert replay(model_dir=tiny.dir, dtype="float32", out_dir=out, max_tokens=max_tokens,
                   lines=traces.lines_of(steps), report=rep, device="cpu",
-                  ops=plain_ops.PlainOps()) == 0
+                  ops=plain_ops.PlainOps(), **kw) == 0
     assert rep.getvalue().split() == [w for s in steps for w in ("done", str(s["step"]))]
     return out
 
@@ -53,6 +53,33 @@ def test_mixed_batches_with_page_reuse(tiny, tmp_path):
     assert len(got) > 40
     err, where = traces.worst_error(got, {r: tiny.logits(t) for r, t in reqs.items()})
     assert err < TOL, (err, where)
+
+
+def test_prefix_hit_in_a_replay_changes_no_logit(tiny_models, tmp_path):
+    """Tiny B's prompts of 16 and 70 tokens share their first 16: the second request's first
+    page comes from the cache, and every logit behind it equals the plain model's."""
+    import json
+    tiny = tiny_models["tiny_b"]
+    p2 = tiny.tokens(16, 31)
+    reqs = {"p2": p2, "p4": p2 + tiny.tokens(54, 32), "n": tiny.tokens(9, 33)}
+    steps, index = traces.shared_prefix(reqs, "p2", "p4", 16)
+    out = _replay(tiny, steps, tmp_path, max_tokens=192, prefix_cache=True)
+    stats = json.loads((out / "replay_stats.json").read_text())
+    assert stats["hit_tokens"] == 16 and stats["run_tokens"] == 16 + 54 + 3
+    got = traces.collect(out, index, tiny.config["vocab_size"])
+    err, where = traces.worst_error(got, {r: tiny.logits(t) for r, t in reqs.items()})
+    assert err < TOL, (err, where)
+
+
+def test_dropped_request_is_recomputed_in_a_replay(tiny, tmp_path):
+    reqs = {"a": tiny.tokens(60, 41), "v": tiny.tokens(50, 42), "c": tiny.tokens(33, 43)}
+    steps, index = traces.drop_and_recompute(reqs, "v")
+    assert any("drop" in s for s in steps)
+    for cache in (False, True):
+        out = _replay(tiny, steps, tmp_path, max_tokens=192, prefix_cache=cache)
+        got = traces.collect(out, index, tiny.config["vocab_size"])
+        err, where = traces.worst_error(got, {r: tiny.logits(t) for r, t in reqs.items()})
+        assert err < TOL, (cache, err, where)
 
 
 def _runner(tiny, pages=8, **kw):

@@ -75,3 +75,39 @@ def test_real_widths_every_cut_agrees_with_the_plain_model(real_model, dtype):
         worst = max(worst, float((row.float().cpu() - ref).abs().max()))
     assert worst < tol, (name, dtype, worst)
     rn.manager.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_depth_medium_long_prompt_then_decoding(tmp_path_factory, dtype):
+    """GPT-2 medium at its full depth of 24 layers: one prompt of 1,016 tokens in one step,
+    then 8 tokens decoded one by one up to the end of the position table, against the plain
+    model in float64 on the CPU (first, middle and last place of the prompt, every decoded
+    place).  Depth is what the few-layer tests above leave out: 24 layers of accumulated
+    rounding on a residual stream that grows."""
+    cfg = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", vocab_size=50257,
+               n_positions=1024, n_inner=None, layer_norm_epsilon=1e-5,
+               activation_function="gelu_new", scale_attn_by_inverse_layer_idx=False,
+               tie_word_embeddings=True, n_layer=24, n_embd=1024, n_head=16)
+    d = tmp_path_factory.mktemp("medium_full_" + dtype)
+    write_model_dir(d, cfg, 5, "float32")
+    raw = read_safetensors(d / "model.safetensors")
+    cfg = json.loads((d / "config.json").read_text())
+    g = torch.Generator().manual_seed(21)
+    toks = torch.randint(0, 50257, (1024,), generator=g).tolist()
+    w = plain_gpt2.prepare_weights(raw, dtype=torch.float64,
+                                   round_to=torch.bfloat16 if dtype == "bfloat16" else None)
+    places = [0, 511, 1015] + list(range(1016, 1024))
+    ref = plain_gpt2.forward(cfg, w, toks, dtype=torch.float64, rows=places)
+    del w
+    model, _ = load_model(str(d), dtype, "cuda:0")
+    rn = Runner(model, num_pages=66, page_size=16, max_requests=2, dtype=model.dtype,
+                device="cuda:0", cuda_graphs=(dtype == "bfloat16"))
+    got = [rn.step([StepEntry("a", toks[:1016], want=[0, 511, 1015])]).logits.double().cpu()]
+    for p in range(1016, 1024):
+        got.append(rn.step([StepEntry("a", [toks[p]], want=[0])]).logits.double().cpu())
+    got = torch.cat(got)
+    err = (got - ref).abs().max(dim=1).values
+    # float32: 24 layers of float32 sums against float64; bfloat16: activations rounded to 8
+    # bits between kernels, 24 layers deep
+    tol = 5e-4 if dtype == "float32" else 1e-1
+    assert float(err.max()) < tol, [round(float(e), 6) for e in err]

@@ -20,6 +20,8 @@ DECAY = 0.8
 class RunningMeanMixer(Mixer):
     """y_t = W (s_t),  s_t = DECAY * s_{t-1} + h_t  with s carried across steps in a state slot."""
 
+    capturable = False      # it walks the batch on the host: no CUDA graph for its model
+
     def __init__(self, *, width, weight):
         self.width, self.name = width, weight
         self.w = None

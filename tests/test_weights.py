@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from hetero_serve_b200.architectures.gpt2 import build_spec
-from hetero_serve_b200.config import GPT2Config
+from hetero_serve_b200.architectures.gpt2 import GPT2Config
 from hetero_serve_b200.parts import Model
 from hetero_serve_b200.weights import (SafetensorsError, WeightError, load_checkpoint,
                                        random_weights, read_safetensors, write_model_dir,

@@ -103,6 +103,68 @@ def mixed(requests, seed=0, max_live=4, sizes=(1, 1, 2, 5, 1, 17, 3, 1, 9, 2, 30
     return steps, index, peak
 
 
+def shared_prefix(requests, first: str, second: str, shared: int, portion=24):
+    """``second`` begins with the first ``shared`` tokens of ``first`` (a multiple of the page
+    size).  ``first`` runs whole and ends; ``second`` then comes in portions of ``portion``:
+    with prefix reuse its first ``shared`` tokens are served from the pages ``first`` left, so
+    only places behind them are wanted.  A third request, if any, runs beside it."""
+    a, b = requests[first], requests[second]
+    assert a[:shared] == b[:shared]
+    steps = [{"step": 0, "entries": [{"id": first, "tokens": a, "want": list(range(len(a)))}],
+              "end": [first]}]
+    index = {0: [(first, p) for p in range(len(a))]}
+    others = [r for r in requests if r not in (first, second)]
+    at, n = 0, 1
+    while at < len(b):
+        size = min(portion, len(b) - at)
+        want = [w for w in range(size) if at + w >= shared]
+        entries = [{"id": second, "tokens": b[at:at + size], "want": want}]
+        rows = [(second, at + w) for w in want]
+        for r in others:                                  # a neighbour decoding token by token
+            k = n - 1
+            if k < len(requests[r]):
+                entries.append({"id": r, "tokens": [requests[r][k]], "want": [0]})
+                rows.append((r, k))
+        steps.append({"step": n, "entries": entries, "end": []})
+        index[n] = rows
+        at += size
+        n += 1
+    steps.append({"step": n, "entries": [], "end": [second] + others})
+    return steps, index
+
+
+def drop_and_recompute(requests, victim: str, drop_after=2, portion=24):
+    """Every request is prefilled in portions side by side; after ``drop_after`` steps the
+    victim is dropped (preempted) and, one step later, fed again from its first token while
+    the others go on: its pages were given back and are taken again."""
+    at = {r: 0 for r in requests}
+    steps, index = [], {}
+    n = 0
+    dropped = False
+    while any(at[r] < len(t) for r, t in requests.items()):
+        entries, rows = [], []
+        sit_out = victim if (dropped and n == drop_after + 1) else None
+        for r, toks in requests.items():
+            if at[r] >= len(toks) or r == sit_out:
+                continue
+            size = min(portion if r != victim else portion // 2 + 1, len(toks) - at[r])
+            want = sorted({0, size - 1})
+            entries.append({"id": r, "tokens": toks[at[r]:at[r] + size], "want": want})
+            rows += [(r, at[r] + w) for w in want]
+            at[r] += size
+        rec = {"step": n, "entries": entries, "end": []}
+        if n == drop_after and not dropped:
+            rec["drop"] = [victim]
+            at[victim] = 0
+            dropped = True
+        steps.append(rec)
+        if rows:
+            index[n] = rows
+        n += 1
+    steps.append({"step": n, "entries": [], "end": list(requests)})
+    return steps, index
+
+
 def lines_of(steps) -> io.StringIO:
     return io.StringIO("".join(json.dumps(s) + "\n" for s in steps))
 
