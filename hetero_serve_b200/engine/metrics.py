@@ -1,25 +1,36 @@
-"""Per-request records and a run summary, in the manner of the reference's
-``RequestRecord`` / ``summarise`` (heteroserve/metrics.py:17-87, 123-180):
-time to first token, time per output token, end-to-end latency."""
+"""What the engine reports about finished requests: one :class:`RequestRecord` per request
+and a summary of a run.
+
+The field and key names are the reference's (heteroserve/metrics.py:31-87 ``RequestRecord``,
+:123-180 ``summarise``), so that its dashboards and result files read the same: ``ttft`` is
+the time from submission to the first generated token, ``tpot`` the mean time per generated
+token after the first, ``e2e`` the time from submission to the end.  Times are seconds on the
+scheduler's clock; a span with a missing end is NaN.
+"""
 
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass, field
 
+NAN = float("nan")
 
-def percentile(values: list[float], p: float) -> float:
-    """Linear interpolation between closest ranks (heteroserve/metrics.py:17-28)."""
-    if not values:
-        return float("nan")
-    s = sorted(values)
-    if len(s) == 1:
-        return s[0]
-    k = (len(s) - 1) * p
-    lo, hi = math.floor(k), math.ceil(k)
-    if lo == hi:
-        return s[int(k)]
-    return s[lo] * (hi - k) + s[hi] * (k - lo)
+
+def _span(start: float, end: float) -> float:
+    """end - start, or NaN while the end has not happened (its stamp is still 0)."""
+    return end - start if end else NAN
+
+
+def percentile(values, p: float) -> float:
+    """The p-quantile (0 <= p <= 1) with linear interpolation between the two nearest order
+    statistics; NaN for no values."""
+    ordered = sorted(values)
+    if not ordered:
+        return NAN
+    rank = p * (len(ordered) - 1)
+    below = int(rank)
+    above = min(below + 1, len(ordered) - 1)
+    weight = rank - below
+    return ordered[below] + (ordered[above] - ordered[below]) * weight
 
 
 @dataclass
@@ -39,36 +50,34 @@ class RequestRecord:
 
     @property
     def ttft(self) -> float:
-        return self.t_first_token - self.t_submit if self.t_first_token else float("nan")
+        return _span(self.t_submit, self.t_first_token)
 
     @property
     def e2e(self) -> float:
-        return self.t_done - self.t_submit if self.t_done else float("nan")
+        return _span(self.t_submit, self.t_done)
 
     @property
     def tpot(self) -> float:
-        n = self.generated_tokens - 1
-        if n <= 0 or not self.t_first_token or not self.t_done:
-            return float("nan")
-        return (self.t_done - self.t_first_token) / n
+        later = self.generated_tokens - 1           # tokens after the first
+        if later < 1 or not self.t_first_token:
+            return NAN
+        return _span(self.t_first_token, self.t_done) / later
 
     @property
     def cache_hit_rate(self) -> float:
-        return self.cached_prefix_tokens / self.prompt_tokens if self.prompt_tokens else 0.0
+        return self.cached_prefix_tokens / max(1, self.prompt_tokens)
 
     def as_dict(self) -> dict:
-        return {
-            "req_id": self.req_id, "prompt_tokens": self.prompt_tokens,
-            "generated_tokens": self.generated_tokens,
-            "cached_prefix_tokens": self.cached_prefix_tokens,
-            "prefill_tokens_computed": self.prefill_tokens_computed,
-            "preemptions": self.preemptions, "finish_reason": self.finish_reason,
-            "ttft": round(self.ttft, 5), "tpot": round(self.tpot, 6), "e2e": round(self.e2e, 5),
-            "cache_hit_rate": round(self.cache_hit_rate, 4), "output_ids": list(self.output_ids),
-        }
+        out = {name: getattr(self, name) for name in (
+            "req_id", "prompt_tokens", "generated_tokens", "cached_prefix_tokens",
+            "prefill_tokens_computed", "preemptions", "finish_reason")}
+        out.update(ttft=round(self.ttft, 5), tpot=round(self.tpot, 6), e2e=round(self.e2e, 5),
+                   cache_hit_rate=round(self.cache_hit_rate, 4), output_ids=list(self.output_ids))
+        return out
 
     @classmethod
     def of(cls, seq) -> "RequestRecord":
+        """The record of a scheduler's sequence state."""
         return cls(req_id=seq.req_id, prompt_tokens=len(seq.request.prompt_ids),
                    generated_tokens=len(seq.output_ids),
                    cached_prefix_tokens=seq.cached_prefix_tokens,
@@ -79,20 +88,22 @@ class RequestRecord:
 
 
 def summarise(records: list[RequestRecord], wall_s: float) -> dict:
-    ok = [r for r in records if r.t_done]
-    gen = sum(r.generated_tokens for r in ok)
-    ttft = [r.ttft for r in ok if not math.isnan(r.ttft)]
-    tpot = [r.tpot for r in ok if not math.isnan(r.tpot)]
-    e2e = [r.e2e for r in ok]
-    prompt = sum(r.prompt_tokens for r in ok)
+    """Totals and latency quantiles over the requests that finished within ``wall_s`` seconds."""
+    done = [r for r in records if r.t_done]
+    per_second = (lambda n: n / wall_s) if wall_s > 0 else (lambda n: 0.0)
+    known = lambda xs: [x for x in xs if x == x]            # noqa: E731  (drops NaN)
+    ttft, tpot, e2e = (known(getattr(r, name) for r in done) for name in ("ttft", "tpot", "e2e"))
+    prompt = sum(r.prompt_tokens for r in done)
+    saved = sum(r.cached_prefix_tokens for r in done)
     return {
-        "n_requests": len(ok), "wall_s": round(wall_s, 4),
-        "throughput_tok_s": round(gen / wall_s, 2) if wall_s > 0 else 0.0,
-        "request_throughput": round(len(ok) / wall_s, 3) if wall_s > 0 else 0.0,
+        "n_requests": len(done),
+        "wall_s": round(wall_s, 4),
+        "throughput_tok_s": round(per_second(sum(r.generated_tokens for r in done)), 2),
+        "request_throughput": round(per_second(len(done)), 3),
         "ttft_p50": percentile(ttft, 0.5), "ttft_p95": percentile(ttft, 0.95),
-        "tpot_p50": percentile(tpot, 0.5), "e2e_p50": percentile(e2e, 0.5),
-        "e2e_p95": percentile(e2e, 0.95),
-        "cache_hit_rate": round(sum(r.cached_prefix_tokens for r in ok) / prompt, 4) if prompt else 0.0,
-        "prefill_tokens_saved": sum(r.cached_prefix_tokens for r in ok),
-        "preemptions": sum(r.preemptions for r in ok),
+        "tpot_p50": percentile(tpot, 0.5),
+        "e2e_p50": percentile(e2e, 0.5), "e2e_p95": percentile(e2e, 0.95),
+        "cache_hit_rate": round(saved / prompt, 4) if prompt else 0.0,
+        "prefill_tokens_saved": saved,
+        "preemptions": sum(r.preemptions for r in done),
     }

@@ -1,0 +1,287 @@
+"""Each kernel of a decode step and of a prefill step alone, at the step's shapes, against its
+roofline — in the manner of the reference's kernel benchmark (scripts/bench_kernel.py:61-221:
+time each kernel, print GB/s against a peak, and refuse to time a kernel whose output is off
+its torch reference, :193-201).
+
+How a kernel is timed.  Its weights (or cache pages) are allocated in as many copies as it
+takes to exceed twice the L2 (126 MB), one launch per copy is captured into a CUDA graph, and
+the graph is replayed: every launch reads operands no earlier launch left in the L2, as in a
+real step, where the layers' weights stream through once.  Small activations stay in the L2,
+as they do in a step.  The time of a launch is the graph's time divided by its launches
+(device time, CUDA events, median of the replays) and so includes the gap between
+back-to-back launches, which is part of what a kernel costs in a step.
+
+Rooflines: kernels that stream weights or cache pages are held against the HBM peak with the
+bytes they must read (weights once, the live requests' pages, large activations), the
+contractions of a prefill step against the bfloat16 tensor peak with their FLOPs.  Before a
+kernel is timed its output is compared with plain PyTorch arithmetic in float32 on the same
+operands; if it is off, the row carries the difference and no time.
+"""
+
+from __future__ import annotations
+
+import math
+import statistics
+
+import torch
+
+from .ops import AttentionGeometry, CudaOps
+
+L2_BYTES = 126 * 2 ** 20
+GATE_TOL = {torch.bfloat16: 4e-2, torch.float32: 2e-3}
+
+
+def _copies(nbytes: int, lo: int = 2, hi: int = 160) -> int:
+    return max(lo, min(hi, math.ceil(2 * L2_BYTES / max(1, nbytes))))
+
+
+def _time_graph(launch, n: int, replays: int = 7) -> float:
+    """Microseconds per launch: ``launch(i)`` for i in range(n) captured once, replayed."""
+    for i in range(min(n, 3)):
+        launch(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(n):
+            launch(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(replays):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3 / n)
+    return statistics.median(times)
+
+
+def _act(v, act):
+    if act == "gelu_tanh":
+        return torch.nn.functional.gelu(v, approximate="tanh")
+    if act == "gelu_erf":
+        return torch.nn.functional.gelu(v)
+    return v
+
+
+def _layernorm(x, g, b, eps):
+    mu = x.mean(-1, keepdim=True)
+    c = x - mu
+    return c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * g + b
+
+
+class _Bench:
+    def __init__(self, cfg, peaks, dtype, device):
+        self.cfg, self.peaks = cfg, peaks
+        self.dt = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+        self.item = 2 if self.dt == torch.bfloat16 else 4
+        self.dev = torch.device(device)
+        self.ops = CudaOps(self.dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.ops.status = self.status
+        self.E, self.H = cfg["n_embd"], cfg["n_head"]
+        self.D = self.E // self.H
+        self.I = cfg["n_inner"] or 4 * self.E
+        self.V = cfg["vocab_size"]
+        self.eps = cfg.get("layer_norm_epsilon", 1e-5)
+        self.gen = torch.Generator(device=self.dev).manual_seed(0)
+        self.rows: list[dict] = []
+
+    def rand(self, *shape, scale=1.0, dtype=None):
+        t = torch.randn(*shape, device=self.dev, generator=self.gen) * scale
+        return t.to(dtype or self.dt)
+
+    def record(self, step, kernel, us, gate, *, nbytes=0, flops=0, bound):
+        row = {"step": step, "kernel": kernel, "gate_max_diff": round(gate, 5)}
+        if us is None:
+            row["refused"] = "output is off the plain reference: not timed"
+        else:
+            row["us"] = round(us, 2)
+            if bound == "hbm":
+                ach = nbytes / (us * 1e-6) / 1e9
+                row.update(bound="hbm", bytes=int(nbytes), achieved_gbs=round(ach, 1),
+                           frac=round(ach / self.peaks["hbm_gbs"], 4))
+            else:
+                ach = flops / (us * 1e-6) / 1e12
+                row.update(bound="tensor", flops=int(flops), achieved_tflops=round(ach, 1),
+                           frac=round(ach / self.peaks["bf16_tflops"], 4))
+        self.rows.append(row)
+
+    def gate_ok(self, got, want) -> tuple[bool, float]:
+        diff = float((got.float() - want.float()).abs().max())
+        ok = math.isfinite(diff) and diff <= GATE_TOL[self.dt] * max(1.0, float(want.abs().max()))
+        return ok, diff
+
+    # -- linears ------------------------------------------------------------------------
+    def linear(self, step, kernel, M, N, K, *, act="none", norm=False, residual=False,
+               out_dtype=None, bound="hbm"):
+        ops = self.ops
+        out_dtype = out_dtype or (torch.float32 if residual else self.dt)
+        n = _copies(N * K * self.item) if bound == "hbm" else 4
+        w = self.rand(n, N, K, scale=K ** -0.5)
+        bias = self.rand(N, dtype=torch.float32)
+        out = torch.zeros(M, N, device=self.dev, dtype=out_dtype)
+        res0 = self.rand(M, N, dtype=torch.float32) if residual else None
+        if norm:
+            x = self.rand(M, K, dtype=torch.float32) * 3 + 1
+            g, b = self.rand(K, dtype=torch.float32), self.rand(K, dtype=torch.float32)
+            h = torch.empty(M, K, device=self.dev, dtype=self.dt)
+            a_ref = _layernorm(x, g, b, self.eps).to(self.dt).float()
+
+            def launch(i):
+                ops.norm_linear(out, h, x, g, b, self.eps, w[i % n], bias, act)
+        else:
+            a = self.rand(M, K)
+            a_ref = a.float()
+
+            def launch(i):
+                if residual:
+                    ops.linear(out, a, w[i % n], bias, act=act, residual=out)
+                else:
+                    ops.linear(out, a, w[i % n], bias, act=act)
+        if residual:
+            out.copy_(res0)
+        launch(0)
+        want = _act(a_ref @ w[0].float().T + bias, act)
+        if residual:
+            want = want + res0
+        ok, diff = self.gate_ok(out, want)
+        us = _time_graph(launch, n) if ok else None
+        act_bytes = M * K * (4 if norm else self.item) + M * N * out.element_size() * (2 if residual else 1)
+        self.record(step, kernel, us, diff, nbytes=N * K * self.item + act_bytes,
+                    flops=2 * M * N * K, bound=bound)
+
+    # -- attention ----------------------------------------------------------------------
+    def _cache(self, lens, new, n_entries):
+        """Pools [entries, pages, 2, H, 16, D] with random keys and values for the cached
+        positions, a block table, and the step's qkv rows."""
+        PS, H, D = 16, self.H, self.D
+        pages_per = [-(-n // PS) for n in lens]
+        n_pages = sum(pages_per) + 1
+        max_pages = max(pages_per) + 1
+        table = torch.full((len(lens), max_pages), -1, dtype=torch.int32)
+        at = 0
+        for r, k in enumerate(pages_per):
+            table[r, :k] = torch.arange(at, at + k, dtype=torch.int32)
+            at += k
+        pool = self.rand(n_entries, n_pages, 2, H, PS, D)
+        T = sum(new)
+        qkv = self.rand(T, 3 * self.E)
+        pos, req = [], []
+        for r, (n, k) in enumerate(zip(lens, new)):
+            pos += list(range(n - k, n))
+            req += [r] * k
+        geom = AttentionGeometry(H, H, D, PS, n_pages, max_pages, 0, self.E, 2 * self.E, 3 * self.E)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=self.dev)   # noqa: E731
+        host = [(f"r{r}", r, n - k, k) for r, (n, k) in enumerate(zip(lens, new))]
+        return geom, qkv, pool, table.to(self.dev), i32(pos), i32(req), host
+
+    def _attention_reference(self, qkv, pool, table, lens, new, geom, scale):
+        H, D, PS = geom.n_heads, geom.head_dim, geom.page_size
+        out, t = [], 0
+        for r, (n, k) in enumerate(zip(lens, new)):
+            pos = torch.arange(n, device=self.dev)
+            pages = table[r, pos // PS].long()
+            keys = pool[pages, 0, :, pos % PS, :].float()
+            vals = pool[pages, 1, :, pos % PS, :].float()
+            q = qkv[t:t + k, :H * D].view(k, H, D).float()
+            s = torch.einsum("qhd,nhd->hqn", q, keys) * scale
+            qpos = torch.arange(n - k, n, device=self.dev)
+            s = s.masked_fill((pos[None, :] > qpos[:, None])[None], float("-inf"))
+            out.append(torch.einsum("hqn,nhd->qhd", torch.softmax(s, -1), vals).reshape(k, H * D))
+            t += k
+        return torch.cat(out)
+
+    def attention(self, step, kernel, lens, new, bound):
+        ops = self.ops
+        kv_bytes = sum(lens) * 2 * self.E * self.item
+        n = _copies(kv_bytes, hi=48) if bound == "hbm" else 2
+        geom, qkv, pool, table, pos, req, host = self._cache(lens, new, n)
+        T = qkv.shape[0]
+        plan = ops.make_plan(host, T, 16) if self.dt == torch.bfloat16 else None
+        out = torch.zeros(T, self.E, device=self.dev, dtype=self.dt)
+        scale = 1.0 / math.sqrt(self.D)
+
+        def launch(i):
+            ops.attention_append(out, qkv, pool[i % n], table, pos, req, geom, scale, self.status,
+                                 plan, True)
+        launch(0)
+        want = self._attention_reference(qkv, pool[0], table, lens, new, geom, scale)
+        ok, diff = self.gate_ok(out, want)
+        us = _time_graph(launch, n) if ok else None
+        flops = sum(4 * self.E * (k * (n_ - k) + k * (k + 1) // 2) for n_, k in zip(lens, new))
+        self.record(step, kernel, us, diff, nbytes=kv_bytes + T * 4 * self.E * self.item,
+                    flops=flops, bound=bound)
+
+    # -- the rest -----------------------------------------------------------------------
+    def layernorm(self, step, kernel, M):
+        x = self.rand(4, M, self.E, dtype=torch.float32) * 3 + 1
+        g, b = self.rand(self.E, dtype=torch.float32), self.rand(self.E, dtype=torch.float32)
+        out = torch.empty(M, self.E, device=self.dev, dtype=self.dt)
+
+        def launch(i):
+            self.ops.layernorm(out, x[i % 4], g, b, self.eps)
+        launch(0)
+        ok, diff = self.gate_ok(out, _layernorm(x[0], g, b, self.eps))
+        us = _time_graph(launch, 8) if ok else None
+        self.record(step, kernel, us, diff, nbytes=M * self.E * (4 + self.item), bound="hbm")
+
+    def head_and_sample(self, step, B):
+        ops = self.ops
+        n = _copies(self.V * self.E * self.item, hi=4)
+        w = self.rand(n, self.V, self.E, scale=self.E ** -0.5)
+        hf = self.rand(B, self.E)
+        logits = torch.empty(B, self.V, device=self.dev, dtype=torch.float32)
+
+        def launch(i):
+            ops.linear(logits, hf, w[i % n])
+        launch(0)
+        ok, diff = self.gate_ok(logits, hf.float() @ w[0].float().T)
+        us = _time_graph(launch, n) if ok else None
+        self.record(step, "head", us, diff, nbytes=self.V * self.E * self.item + B * self.V * 4,
+                    flops=2 * B * self.V * self.E, bound="hbm")
+        tokens = torch.empty(B + 1, dtype=torch.int32, device=self.dev)
+        zeros = torch.zeros(B, dtype=torch.int32, device=self.dev)
+        temp = torch.zeros(B, dtype=torch.float32, device=self.dev)
+
+        def sample(i):
+            ops.sample(tokens, logits, temp, zeros, zeros, zeros, zeros)
+        sample(0)
+        same = bool((tokens[:B].long() == logits.argmax(-1)).all())
+        us = _time_graph(sample, 8) if same else None
+        self.record(step, "sample (greedy)", us, 0.0 if same else float("inf"),
+                    nbytes=B * self.V * 4, bound="hbm")
+
+
+def table(model, cfg, peaks, dtype="bfloat16", batches=(8,), context=768, device="cuda:0"):
+    """Rows (dictionaries) for the kernels of a decode step at each batch size and of a prefill
+    step of 2 x 1,024 tokens.  ``model`` is not used for its weights (operands are allocated
+    here, in copies); it is accepted so that callers pass what they have."""
+    b = _Bench(cfg, peaks, dtype, device)
+    E, I = b.E, b.I
+    fast = b.dt == torch.bfloat16
+    for B in batches:
+        s = f"decode_b{B}"
+        b.linear(s, "layernorm + qkv", B, 3 * E, E, norm=fast)
+        b.attention(s, "attention (+ append)", [context] * B, [1] * B, "hbm")
+        b.linear(s, "attention out + residual", B, E, E, residual=True)
+        b.linear(s, "layernorm + fc + gelu", B, I, E, act="gelu_tanh", norm=fast)
+        b.linear(s, "mlp out + residual", B, E, I, residual=True)
+        b.head_and_sample(s, B)
+    s, T = "prefill_2048", 2048
+    bound = "tensor" if fast else "hbm"
+    b.layernorm(s, "layernorm", T)
+    b.linear(s, "qkv", T, 3 * E, E, bound=bound)
+    b.attention(s, "attention (+ append)", [1024, 1024], [1024, 1024], bound)
+    b.linear(s, "attention out + residual", T, E, E, residual=True, bound=bound)
+    b.linear(s, "fc + gelu", T, I, E, act="gelu_tanh", bound=bound)
+    b.linear(s, "mlp out + residual", T, E, I, residual=True, bound=bound)
+    return b.rows
+
+
+def fractions(model, cfg, peaks, dtype="bfloat16", device="cuda:0") -> dict:
+    """Flat ``{"step.kernel": fraction of its peak}`` for a decode step at batch 8 and a
+    prefill step (a kernel that failed its comparison carries ``None``)."""
+    return {f"{r['step']}.{r['kernel']}": r.get("frac") for r in
+            table(model, cfg, peaks, dtype, batches=(8,), device=device)}
