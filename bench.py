@@ -255,7 +255,8 @@ def time_prefill(runner, torch, n_seqs, seq_len, vocab, seed, reps=5, warmup=3):
     return statistics.median(times)
 
 
-def time_e2e(model_dir, torch, batch, windows, warmup, vocab, seed, num_blocks, dtype):
+def time_e2e(model_dir, torch, batch, windows, warmup, vocab, seed, num_blocks, dtype,
+             fused_decode=False):
     """The same windows through the public entry point: LLMEngine.step(), which packs the
     step's host-side inputs into pinned memory and copies them to the device, and brings
     sampled ids back to the host, every call.  The engine pipelines: a call launches one step
@@ -263,7 +264,7 @@ def time_e2e(model_dir, torch, batch, windows, warmup, vocab, seed, num_blocks, 
     from hetero_serve_b200 import EngineConfig, LLMEngine, Request
     eng = LLMEngine(model_dir, EngineConfig(
         dtype=dtype, num_blocks=num_blocks, max_batch=batch, max_prefill_tokens=2048,
-        max_requests=batch, prefix_cache=False, cuda_graphs=True))
+        max_requests=batch, prefix_cache=False, cuda_graphs=True, fused_decode=fused_decode))
     g = torch.Generator().manual_seed(seed)
     total = 0.0
     for first, k, reps in windows:
@@ -460,7 +461,8 @@ def run_ours(args):
         page = 16
         pages_per_req = context // page
         runner = Runner(model, num_pages=64 * pages_per_req + 8, page_size=page, max_requests=64,
-                        dtype=tdt, device="cuda:0", prefix_cache=False, cuda_graphs=True)
+                        dtype=tdt, device="cuda:0", prefix_cache=False, cuda_graphs=True,
+                        fused_decode=args.fused_decode)
         sampler = ClockSampler()
         sampler.start()
         ms, launches, per_window = time_decode(runner, torch, batch, windows, warmup, vocab, 1, "d")
@@ -485,7 +487,7 @@ def run_ours(args):
         del runner
         torch.cuda.empty_cache()
         e2e_val, h2d, d2h = time_e2e(d, torch, batch, windows, warmup, vocab, 1,
-                                     batch * pages_per_req + 8, dtype)
+                                     batch * pages_per_req + 8, dtype, args.fused_decode)
         kernels = None
         if not args.no_kernels:
             from hetero_serve_b200.kernels import microbench
@@ -516,7 +518,7 @@ def run_ours(args):
             "seq_len": context, "prompt_len": prompt_len, "kv_block_size": 16,
             "parallelism": "single GPU", "residual_stream": "fp32",
             "windows": "x".join(str(f) for f, _k, _r in windows),
-            "mean_context": round(mean_ctx, 1),
+            "mean_context": round(mean_ctx, 1), "fused_decode": bool(args.fused_decode),
             "l2": "each step reads 0.7 GB of weights (> 126 MB L2); no flush needed",
             "peaks": pk_src,
         },
@@ -708,6 +710,9 @@ def main() -> int:
                          "(comma-separated: large, xl; 'none' skips them)")
     ap.add_argument("--workload-layers", dest="workload_layers", type=int, default=0,
                     help="fewer layers for the workloads (0: all)")
+    ap.add_argument("--fused-decode", dest="fused_decode", action="store_true",
+                    help="decode steps of up to 16 tokens as one persistent kernel (off by "
+                         "default: it measures slower than the layer-by-layer path)")
     ap.add_argument("--no-kernels", dest="no_kernels", action="store_true",
                     help="skip the per-kernel roofline fractions")
     ap.add_argument("--kernels", action="store_true",

@@ -41,6 +41,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--no-cuda-graphs", dest="cuda_graphs", action="store_false")
     ap.add_argument("--no-pipeline", dest="pipeline", action="store_false",
                     help="read every step's tokens before the next step is launched")
+    ap.add_argument("--fused-decode", dest="fused_decode", action="store_true",
+                    help="run pure decode steps of up to 16 tokens as one persistent kernel "
+                         "(where the model has the shape it serves)")
     ap.add_argument("--prompt-ids", dest="prompt_ids", action="append", default=[],
                     help="comma-separated token ids; may be given several times")
     ap.add_argument("--random-prompts", dest="random_prompts", default="",
@@ -57,7 +60,8 @@ def make_engine(args) -> LLMEngine:
     cfg = EngineConfig(dtype=args.dtype, block_size=args.block_size, num_blocks=args.num_blocks,
                        max_batch=args.max_batch, max_prefill_tokens=args.max_prefill_tokens,
                        max_ctx=args.max_ctx, policy=args.policy, prefix_cache=args.prefix_cache,
-                       cuda_graphs=args.cuda_graphs, pipeline=args.pipeline, seed=args.seed, device=args.device)
+                       cuda_graphs=args.cuda_graphs, pipeline=args.pipeline,
+                       fused_decode=args.fused_decode, seed=args.seed, device=args.device)
     if args.weights:
         return LLMEngine(args.weights, cfg)
     return LLMEngine.random(args.model, seed=args.seed, config=cfg)

@@ -39,6 +39,7 @@ class EngineConfig:
     prefix_cache: bool = True         # reuse pages of equal prompt prefixes
     cuda_graphs: bool = True          # replay captured steps for repeated shapes
     pipeline: bool = True             # launch a step before the previous step's tokens are read
+    fused_decode: bool = False        # pure decode steps of up to 16 tokens as one persistent kernel
     seed: int = 0
     device: str = "cuda:0"
 

@@ -38,7 +38,8 @@ class LLMEngine:
         self.runner = Runner(
             self.model, num_pages=cfg.num_blocks, page_size=cfg.block_size,
             max_requests=cfg.live_requests, dtype=TORCH_DTYPES[cfg.dtype], device=cfg.device,
-            ops=ops, prefix_cache=cfg.prefix_cache, cuda_graphs=cfg.cuda_graphs)
+            ops=ops, prefix_cache=cfg.prefix_cache, cuda_graphs=cfg.cuda_graphs,
+            fused_decode=cfg.fused_decode)
         max_ctx = min(cfg.max_ctx or spec.max_positions, spec.max_positions)
         self.scheduler = Scheduler(
             self.runner.manager, self._run_step, max_batch=cfg.max_batch,

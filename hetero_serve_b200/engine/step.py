@@ -161,6 +161,9 @@ class StepContext:
         self.feedback = runner.feedback
         self.tables = [meta[o:o + L.R * mp].view(L.R, mp)
                        for o, mp in zip(L.tables, L.max_pages)]
+        self.fused = runner.fused   # the whole-step decode kernel's plan for this model, if any
+        self.fused_tokens = None   # greedy tokens a fused step left (with the status word)
+        self.greedy_only = False   # no wanted row of this step samples with a temperature
         self.plan = None          # work lists for the specialised attention kernels, if any
         self.position = None      # the model's position encoding (set by Model.forward)
         self.call_index: int | None = None
@@ -224,7 +227,7 @@ class Runner:
 
     def __init__(self, model, *, num_pages: int, page_size: int, max_requests: int,
                  dtype: torch.dtype, device, ops=None, prefix_cache: bool = False,
-                 cuda_graphs: bool = False):
+                 cuda_graphs: bool = False, fused_decode: bool = False):
         self.device = torch.device(device)
         if self.device.type == "cuda" and self.device.index is None:
             self.device = torch.device("cuda", torch.cuda.current_device())
@@ -241,6 +244,13 @@ class Runner:
             max_requests, prefix_cache=prefix_cache, has_state=bool(model.state_shapes))
         self.storage = CacheStorage(model, self.manager, dtype, self.device)
         self.manager.on_open = self._clear_slot
+        # The whole-step decode kernel is opt-in: on this model family it measured slower than
+        # the layer-by-layer path (its phases are serial instruction chains on nine warps an SM).
+        self.fused = None
+        if self.device.type == "cuda" and (fused_decode or getattr(self.ops, "fused_decode_on", False)):
+            from ..parts.fused import plan_fused_decode
+            self.ops.fused_decode_on = True
+            self.fused = plan_fused_decode(model, self.ops, self.storage, page_size)
         self.workspace = Workspace(self.device)
         self.max_positions = model.spec.max_positions
         self.max_pages = [self.manager.pages_for(self.max_positions) for _ in model.cache_groups]
@@ -425,7 +435,8 @@ class Runner:
                                                  host_batch, T, R, mgr.page_size, self.use_graphs)
 
         # ---- device side -------------------------------------------------------------
-        key = (T, R, W, bool(sample), plan_shape)
+        greedy = all(e.temperature <= 0.0 for e in entries)
+        key = (T, R, W, bool(sample), plan_shape, greedy)
         dev = self._dev_meta.get(key[:3])
         if dev is None:
             dev = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
@@ -449,6 +460,7 @@ class Runner:
         else:
             ctx = StepContext(self, lay, dev)
             ctx.host = host_batch
+            ctx.greedy_only = greedy
             if plan_shape is not None:
                 from ..kernels.ops import AttentionPlan
                 ctx.plan = AttentionPlan(dev[lay.plan:lay.plan + lay.plan_ints], T, *plan_shape)
@@ -501,12 +513,17 @@ class Runner:
             _with_status=None if tokens is None else tokens, _runner=self)
 
     def _forward(self, ctx: StepContext, sample: bool):
+        ctx.fused_tokens = None
         logits = self.model.forward(ctx)
         tokens = None
         if sample and logits is not None:
             # one extra element carries the status word, so that one copy brings both back
             W = ctx.n_logit_rows
             tokens = ctx.buffer("sampled", (W + 1,), torch.int32)
+            if ctx.fused_tokens is not None and ctx.greedy_only:
+                # the step ran as one kernel, which also chose the tokens (argmax, lowest
+                # index on ties), kept them for the requests and stored the status word
+                return logits, ctx.fused_tokens
             more = {}
             if getattr(self.ops, "takes_status_word", False):
                 more["status_word"] = self.status          # stored to tokens[W] by the kernel

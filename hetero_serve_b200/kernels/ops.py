@@ -71,6 +71,44 @@ class AttentionPlan:
         return plan_tile_slots(self.n_rows)
 
 
+def pack_weight_units(w: torch.Tensor) -> torch.Tensor:
+    """A [features, k] bfloat16 matrix (k contiguous, k a multiple of 64) in the layout the
+    persistent decode kernel streams: features padded with zero rows to a multiple of 16; tile j
+    (rows 16 j .. 16 j + 15) is k / 64 boxes of [16 rows x 64 k] one behind the other, so that
+    any run of boxes of a tile is contiguous; inside a box the 16-byte piece c of row r lies at
+    piece c ^ (r & 7) of the row (the 128-byte XOR swizzle)."""
+    n, k = w.shape
+    if k % 64:
+        raise KernelError(f"pack_weight_units: k = {k} is not a multiple of 64")
+    n16 = -(-n // 16) * 16
+    if n16 != n:
+        w = torch.cat([w, w.new_zeros(n16 - n, k)])
+    t = w.contiguous().view(n16 // 16, 16, k // 64, 8, 8)      # tile, row, box, piece, element
+    out = torch.empty_like(t)
+    for r in range(16):
+        perm = [c ^ (r & 7) for c in range(8)]
+        out[:, r] = t[:, r][:, :, perm]
+    return out.permute(0, 2, 1, 3, 4).contiguous().view(-1)
+
+
+@dataclass
+class FusedTables:
+    """Device records of a model for the persistent decode kernel (see ``fused_decode_build``)."""
+
+    data: torch.Tensor            # uint8 on the device: layer records, then head and cache maps
+    n_layers: int
+    layer_bytes: int
+    keep: list                    # the tensors the records point at
+
+    @property
+    def layers_ptr(self) -> int:
+        return self.data.data_ptr()
+
+    @property
+    def tables_ptr(self) -> int:
+        return self.data.data_ptr() + self.n_layers * self.layer_bytes
+
+
 DECODE_MAX_NEW = 4        # requests bringing at most this many tokens use the decode kernel
 PREFILL_TILE = 128
 
@@ -147,6 +185,21 @@ def _declare(lib) -> None:
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int
+    LL = ctypes.c_longlong
+    lib.hs_decode_persistent_layer_bytes.restype = c_int
+    lib.hs_decode_persistent_tables_bytes.restype = c_int
+    lib.hs_decode_persistent_grid.restype = c_int
+    lib.hs_decode_persistent_slices.argtypes = [I, I]
+    lib.hs_decode_persistent_slices.restype = c_int
+    lib.hs_decode_persistent_supports.argtypes = [I] * 7
+    lib.hs_decode_persistent_supports.restype = c_int
+    lib.hs_decode_persistent_layer.argtypes = [P] * 13 + [F, F, F, I, I, I, LL]
+    lib.hs_decode_persistent_layer.restype = c_int
+    lib.hs_decode_persistent_tables.argtypes = [P, P, I, I, P, LL]
+    lib.hs_decode_persistent_tables.restype = c_int
+    lib.hs_decode_persistent.argtypes = ([P, P, I, P, P, P, P, F] + [I] * 5 + [P, I, I]
+                                         + [P] * 11 + [I] + [P] * 7 + [I] * 4 + [P, P, I, P])
+    lib.hs_decode_persistent.restype = c_int
     lib.hs_set_pdl.argtypes = [I]
     lib.hs_set_pdl.restype = None
     lib.hs_set_split_clusters.argtypes = [I]
@@ -222,6 +275,8 @@ class CudaOps:
         #                            0: never; 1: always
         self.split_clusters = True  # few rows split over k: the splits of a tile exchange their
         #                            shares inside a thread-block cluster (False: through scratch)
+        self.fused_decode_on = False  # pure decode steps of up to 16 tokens as ONE persistent kernel
+        #                             (measured slower than the layer-by-layer path: off)
         self.skinny_max_rows = 16  # up to this many rows the weight-streaming kernel is used
         #                            (measured: from 17 rows on the tcgen05 kernel's split over k wins)
         # pipeline time-outs of the TMA/tcgen05 kernels are ORed into this word; the runner
@@ -681,6 +736,118 @@ class CudaOps:
                 _ptr(self._scratch_buffer("prefill_counter", 1, torch.int32)), g.n_heads, g.n_kv_heads,
                 g.head_dim, g.page_size, g.num_pages, g.max_pages, g.q_off, g.qkv_stride, scale,
                 _ptr(status), st), f"attention_prefill(head_dim={g.head_dim})")
+
+    # -- the whole decode step in one kernel ----------------------------------------
+    FUSED_MAX_TOKENS = 16
+
+    def fused_decode_supports(self, *, width, inner, n_heads, head_dim, n_kv_heads, page_size,
+                              window) -> bool:
+        """Whether the persistent decode kernel serves a model of these sizes at all (bfloat16,
+        heads of 64 without grouping, pages of 16, widths in multiples of 64 up to 2,048)."""
+        return bool(self.fused_decode_on and self.lib.hs_decode_persistent_supports(
+            int(width), int(inner), int(n_heads), int(head_dim), int(n_kv_heads),
+            int(page_size), int(window)))
+
+    def fused_decode_build(self, layers, *, head_weight, pool, width, inner, vocab):
+        """Descriptor records of a model for :meth:`fused_decode`: per layer call its four
+        matrices (repacked here, see :func:`pack_weight_units`: the kernel keeps its own copy of
+        every matrix, laid out so that what a CTA streams is contiguous), its vectors and
+        constants, and once the head and the tensor map of the cache storage.  ``layers`` is a list of dictionaries with the keys ``w_qkv w_out
+        w_fc w_mlp`` ([features, k] bfloat16), ``b_qkv b_out b_fc b_mlp ln1_g ln1_b ln2_g ln2_b``
+        (float32 or None for the biases), ``eps1 eps2 scale act entry``; ``pool`` is the cache
+        group's storage ``[entries, pages, 2, heads, 16, 64]``."""
+        lib = self.lib
+        lb, tb = lib.hs_decode_persistent_layer_bytes(), lib.hs_decode_persistent_tables_bytes()
+        host = torch.zeros(len(layers) * lb + tb, dtype=torch.uint8)
+        base = host.data_ptr()
+        _want(pool, "pool", torch.bfloat16, 6)
+        rows_per_entry = pool.shape[1] * pool.shape[2] * pool.shape[3] * pool.shape[4]
+        keep = [pool]
+        packs: dict[int, torch.Tensor] = {}
+        for i, L in enumerate(layers):
+            for nm in ("w_qkv", "w_out", "w_fc", "w_mlp"):
+                _want(L[nm], nm, torch.bfloat16, 2)
+            for nm in ("ln1_g", "ln1_b", "ln2_g", "ln2_b"):
+                _want(L[nm], nm, torch.float32, 1)
+            for nm in ("b_qkv", "b_out", "b_fc", "b_mlp"):
+                if L[nm] is not None:
+                    _want(L[nm], nm, torch.float32, 1)
+            if (tuple(L["w_qkv"].shape) != (3 * width, width) or tuple(L["w_out"].shape) != (width, width)
+                    or tuple(L["w_fc"].shape) != (inner, width) or tuple(L["w_mlp"].shape) != (width, inner)):
+                raise KernelError("fused_decode_build: matrix shapes do not fit the sizes")
+            keep += [L[k] for k in L if isinstance(L[k], torch.Tensor) and not k.startswith("w_")]
+            packed = [packs.setdefault(L[nm].data_ptr(), pack_weight_units(L[nm]))
+                      for nm in ("w_qkv", "w_out", "w_fc", "w_mlp")]      # a shared layer: once
+            _check(lib.hs_decode_persistent_layer(
+                c_void_p(base + i * lb), _ptr(packed[0]), _ptr(packed[1]), _ptr(packed[2]),
+                _ptr(packed[3]), _ptr(L["b_qkv"]), _ptr(L["b_out"]), _ptr(L["b_fc"]),
+                _ptr(L["b_mlp"]), _ptr(L["ln1_g"]), _ptr(L["ln1_b"]), _ptr(L["ln2_g"]),
+                _ptr(L["ln2_b"]), float(L["eps1"]), float(L["eps2"]), float(L["scale"]),
+                int(ACTIVATIONS[L["act"]]), int(width), int(inner),
+                ctypes.c_longlong(int(L["entry"]) * rows_per_entry)), "decode_persistent_layer")
+        _want(head_weight, "head_weight", torch.bfloat16, 2)
+        head_packed = pack_weight_units(head_weight)
+        keep += list(packs.values()) + [head_packed]
+        _check(lib.hs_decode_persistent_tables(
+            c_void_p(base + len(layers) * lb), _ptr(head_packed), int(vocab), int(width),
+            _ptr(pool), ctypes.c_longlong(pool.shape[0] * rows_per_entry)),
+            "decode_persistent_tables")
+        dev = host.to(self.device)
+        return FusedTables(dev, len(layers), lb, keep)
+
+    def fused_decode(self, tables, *, wte, wpe, lnf_g, lnf_b, eps_f, width, inner, vocab,
+                     n_heads, pool, num_pages, max_pages, x, qkv, att, u, logits, tokens,
+                     feedback, tok_ids, tok_pos, tok_req, table, logit_rows, samp_slot,
+                     plan_head, n_tokens, n_requests, n_logit_rows, status, stop_after=0):
+        """One decode step of up to 16 single-query tokens in one persistent kernel: embedding,
+        every layer, final norm, head, greedy tokens (``tokens[:n_logit_rows]``, the status
+        word behind them).  Buffers are the caller's; scratch is this object's."""
+        M, W = int(n_tokens), int(n_logit_rows)
+        if not 0 < M <= self.FUSED_MAX_TOKENS or W > self.FUSED_MAX_TOKENS:
+            raise KernelError(f"fused_decode: {M} tokens / {W} wanted rows exceed "
+                              f"{self.FUSED_MAX_TOKENS}")
+        _want(x, "x", torch.float32, 2)
+        for t, nm, wd in ((qkv, "qkv", 3 * width), (att, "att", width), (u, "u", inner)):
+            _want(t, nm, torch.bfloat16, 2)
+            if t.shape[0] < M or t.shape[1] != wd:
+                raise KernelError(f"fused_decode: {nm} has shape {tuple(t.shape)}")
+        if x.shape[0] < M or x.shape[1] != width:
+            raise KernelError("fused_decode: x does not fit")
+        if W:
+            _want(logits, "logits", torch.float32, 2)
+            if logits.shape[0] < W or logits.shape[1] != vocab:
+                raise KernelError("fused_decode: logits do not fit")
+        _want(tokens, "tokens", torch.int32, 1)
+        if tokens.shape[0] < W + 1:
+            raise KernelError("fused_decode: tokens has no room for the status word")
+        for t, nm in ((tok_ids, "tok_ids"), (tok_pos, "tok_pos"), (tok_req, "tok_req")):
+            _want(t, nm, torch.int32, 1)
+            if t.shape[0] < M:
+                raise KernelError(f"fused_decode: {nm} shorter than the tokens")
+        _want(table, "table", torch.int32, 2)
+        if table.shape[1] != max_pages:
+            raise KernelError("fused_decode: block table width != max_pages")
+        grid = self.lib.hs_decode_persistent_grid()
+        if grid <= 0:
+            raise KernelError("fused_decode: the kernel does not fit this device")
+        S = self.lib.hs_decode_persistent_slices(int(n_requests), int(n_heads))
+        acc = ml = None
+        if S > 1:
+            acc = self._scratch_buffer("fused_att_acc", M * n_heads * S * 64, torch.float32)
+            ml = self._scratch_buffer("fused_att_ml", M * n_heads * S * 2, torch.float32)
+        amax_v = self._scratch_buffer("fused_amax_val", grid * 16, torch.float32)
+        amax_i = self._scratch_buffer("fused_amax_idx", grid * 16, torch.int32)
+        sync = self._scratch_buffer("fused_sync", 4, torch.int32)
+        self.launches += 1
+        _check(self.lib.hs_decode_persistent(
+            tables.layers_ptr, tables.tables_ptr, tables.n_layers, _ptr(wte), _ptr(wpe),
+            _ptr(lnf_g), _ptr(lnf_b), float(eps_f), int(width), int(inner), int(vocab),
+            int(n_heads), int(wpe.shape[0]), _ptr(pool), int(num_pages), int(max_pages), _ptr(x),
+            _ptr(qkv), _ptr(att), _ptr(u), _ptr(logits), _ptr(acc), _ptr(ml), _ptr(amax_v),
+            _ptr(amax_i), _ptr(tokens), _ptr(feedback), int(feedback.shape[0]), _ptr(tok_ids),
+            _ptr(tok_pos), _ptr(tok_req), _ptr(table), _ptr(logit_rows), _ptr(samp_slot),
+            _ptr(plan_head), M, W, W, S, _ptr(sync), _ptr(status), int(stop_after),
+            self._stream()), "decode_persistent")
 
     # -- sampling ---------------------------------------------------------------
     def argmax(self, out, logits):

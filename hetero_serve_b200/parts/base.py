@@ -65,6 +65,11 @@ class Part:
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         """Receive the requested tensors, converted and on the device."""
 
+    def fused_decode_params(self) -> dict | None:
+        """What the persistent decode kernel needs of this part (its bound tensors, sizes and
+        constants), or None when the part cannot run inside it.  See ``parts/fused.py``."""
+        return None
+
     # sizes of temporary buffers are taken from the step context, nothing is allocated here
 
 

@@ -192,6 +192,11 @@ class Model:
         """Run the tokens of ``ctx`` through the schedule; returns float32 logits
         ``[n_logit_rows, vocab]`` at ``ctx.logit_rows`` (None when none are wanted)."""
         spec = self.spec
+        fused = getattr(ctx, "fused", None)
+        if fused is not None and fused.applies(ctx):
+            # single decoded tokens only, and a model the persistent kernel serves: one launch
+            logits, ctx.fused_tokens = fused.run(ctx)
+            return logits
         T = ctx.n_rows
         x = ctx.buffer("residual", (T, spec.width), torch.float32)
         ctx.position = self.position          # mixers ask it whether it acts on queries and keys

@@ -36,6 +36,9 @@ class LearnedPositions(PositionEncoding):
     def max_positions(self):
         return self.n
 
+    def fused_decode_params(self):
+        return dict(table=self.table, width=self.width)
+
 
 class NoPositions(PositionEncoding):
     def __init__(self, **_):
@@ -56,6 +59,9 @@ class TokenEmbedding(Embedding):
     def forward(self, ctx, x, position):
         ctx.ops.embed(x, ctx.tok_ids, ctx.tok_pos, ctx.tok_req, self.table,
                       position.embedding_table(), ctx.status, feedback=ctx.feedback)
+
+    def fused_decode_params(self):
+        return dict(table=self.table, width=self.width)
 
 
 class LayerNorm(Norm):
@@ -78,6 +84,9 @@ class LayerNorm(Norm):
 
     def linear(self, ctx, out, h, x, w, bias=None, act="none"):
         ctx.ops.norm_linear(out, h, x, self.weight, self.bias, self.eps, w, bias, act)
+
+    def fused_decode_params(self):
+        return dict(weight=self.weight, bias=self.bias, eps=self.eps, width=self.width)
 
 
 class CausalAttention(Mixer):
@@ -140,6 +149,11 @@ class CausalAttention(Mixer):
 
     takes_norm = True
 
+    def fused_decode_params(self):
+        return dict(w_qkv=self.w_qkv, b_qkv=self.b_qkv, w_out=self.w_out, b_out=self.b_out,
+                    width=self.width, n_heads=self.H, n_kv_heads=self.HK, head_dim=self.D,
+                    window=self.window, scale=self.scale)
+
     def forward(self, ctx, h, x, cache, norm=None):
         T = h.shape[0]
         qkv = ctx.buffer("qkv", (T, self.qkv_width), ctx.dtype)
@@ -193,6 +207,10 @@ class DenseFeedForward(FeedForward):
 
     takes_norm = True
 
+    def fused_decode_params(self):
+        return dict(w_in=self.w_in, b_in=self.b_in, w_out=self.w_out, b_out=self.b_out,
+                    width=self.width, inner=self.inner, activation=self.act)
+
     def forward(self, ctx, h, x, norm=None):
         T = h.shape[0]
         u = ctx.buffer("ff_inner", (T, self.inner), ctx.dtype)
@@ -219,6 +237,9 @@ class LinearHead(Head):
 
     def forward(self, ctx, logits, h):
         ctx.ops.linear(logits, h, self.weight)
+
+    def fused_decode_params(self):
+        return dict(weight=self.weight, vocab=self.vocab, width=self.width)
 
 
 register_position("learned", LearnedPositions)
