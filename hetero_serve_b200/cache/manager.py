@@ -289,6 +289,39 @@ class CacheManager:
             self.on_open(req.slot)
         return Opened(req.slot, req.cached_tokens)
 
+    def rematch(self, req_id, token_ids: Sequence[int]) -> int:
+        """Try the prefix match again for a request that has computed nothing since it was
+        opened: pages published meanwhile (by requests admitted with it that were prefilled
+        first) replace the fresh pages reserved for the same positions.  Returns the number of
+        leading tokens now served from the cache."""
+        req = self._get(req_id)
+        if not self.prefix_cache or req.length != req.cached_tokens or len(token_ids) < 2:
+            return req.cached_tokens
+        usable = (len(token_ids) - 1) // self.page_size
+        have = req.cached_tokens // self.page_size
+        if usable <= have:
+            return req.cached_tokens
+        hashes = chain_hashes(token_ids[:usable * self.page_size], self.page_size)
+        n = min(len(pool.match(hashes)) for pool in self.pools)
+        if n <= have:
+            return req.cached_tokens
+        for gi, pool in enumerate(self.pools):
+            found = pool.match(hashes)
+            table = req.tables[gi]
+            for i in range(have, n):
+                pool.hold(found[i])
+                if i < len(table):
+                    pool.drop(table[i])          # the fresh page reserved for this position
+                    table[i] = found[i]
+                else:
+                    table.append(found[i])
+        gained = (n - have) * self.page_size
+        req.cached_tokens = req.length = n * self.page_size
+        req.published = max(req.published, n)
+        self.hit_tokens += gained
+        self.miss_tokens -= gained
+        return req.cached_tokens
+
     def pages_needed(self, req_id, new_len: int) -> list[int]:
         """Fresh pages each group must supply so that positions < new_len have a page."""
         req = self._get(req_id)

@@ -252,6 +252,17 @@ class Scheduler:
         return planned
 
     def _portion(self, seq: SequenceState, budget: int) -> Planned:
+        if seq.prefill_tokens_computed == 0 and self.manager.prefix_cache:
+            # nothing of it has run yet: pages published since its admission (by requests
+            # admitted together with it) may cover more of its prompt by now
+            before = seq.n_kv
+            got = min(self.manager.rematch(seq.req_id, seq.ctx[:seq.prefill_target]),
+                      seq.prefill_target)
+            if got > before:
+                seq.n_kv = got
+                if not seq.preemptions:
+                    seq.cached_prefix_tokens = got
+                self.stats.tokens_saved_by_cache += got - before
         start = seq.n_kv
         end = min(start + budget, seq.prefill_target)
         toks = seq.ctx[start:end]

@@ -180,3 +180,29 @@ def test_random_orders_keep_the_invariants(seed):
     m.check()
     assert all(m.pages_free(g) == 24 for g in range(len(windows)))
     assert m.free_slots() == 5
+
+
+def test_rematch_picks_up_pages_published_after_admission():
+    """Two requests with the same first 32 tokens are admitted together (nothing published yet,
+    so neither matches); the first is prefilled and publishes; the second, before it runs
+    anything, matches again and trades its fresh pages for the published ones."""
+    from hetero_serve_b200.cache import CacheManager, GroupSpec
+    m = CacheManager([GroupSpec()], num_pages=12, page_size=16, max_requests=4, prefix_cache=True)
+    a = list(range(40))
+    b = list(range(32)) + [99] * 20
+    for rid, toks in (("a", a), ("b", b)):
+        assert m.open(rid, toks).cached_tokens == 0
+        m.reserve(rid, len(toks))
+    free = m.pages_free()
+    m.commit("a", len(a))
+    m.publish("a", a)
+    old_table = list(m.table("b"))
+    assert m.rematch("b", b) == 32
+    assert m.table("b")[:2] == m.table("a")[:2] and m.table("b")[2:] == old_table[2:]
+    assert m.length("b") == 32 and m.pages_free() == free + 2      # two fresh pages came back
+    assert m.rematch("b", b) == 32                                  # nothing more to gain
+    m.check()
+    m.commit("b", len(b))
+    assert m.rematch("b", b) == 32                                  # it has run: no rematch
+    m.close("a"); m.close("b")
+    m.check()

@@ -371,3 +371,23 @@ def test_abort_while_a_token_is_in_flight():
     assert a.finish_reason == "aborted"
     assert b.output_ids == expected_outputs(prompt(5, base=9), 5)
     assert mgr.pages_free() == 64 and mgr.free_slots() == 8
+
+
+@pytest.mark.parametrize("policy", ["prefill_first", "mixed"])
+def test_requests_admitted_together_still_share_a_prefix(policy):
+    """Three requests with the same first 12 tokens are submitted at once: nothing is published
+    when they are admitted, so admission finds no match; the first one's prompt pages are
+    published when its prefill ends, and the others pick them up before they run anything."""
+    sch, fake, mgr = make(page_size=4, budget=24, policy=policy)
+    shared = prompt(12, base=5)
+    reqs = [shared + prompt(9, base=40 + 7 * i) for i in range(3)]
+    seqs = [sch.add(Request(p, max_new_tokens=3)) for p in reqs]
+    run(sch, mgr)
+    assert seqs[0].cached_prefix_tokens == 0
+    if policy == "prefill_first":           # one prompt a step: the later ones see the first's pages
+        assert [s.cached_prefix_tokens for s in seqs[1:]] == [12, 12]
+        assert [s.prefill_tokens_computed for s in seqs] == [21, 9, 9]
+    for s, p in zip(seqs, reqs):
+        assert s.output_ids == expected_outputs(p, 3)
+    assert sch.stats.tokens_saved_by_cache == sum(s.cached_prefix_tokens for s in seqs)
+    mgr.check()
