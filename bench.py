@@ -571,7 +571,8 @@ def run_one_step(args):
         write_model_dir(d, cfg, seed=0, dtype="bfloat16")
         model, _ = load_model(d, "bfloat16", "cuda:0")
         runner = Runner(model, num_pages=args.batch * 64 + 136, page_size=16, max_requests=64,
-                        dtype=torch.bfloat16, device="cuda:0", cuda_graphs=False)
+                        dtype=torch.bfloat16, device="cuda:0", cuda_graphs=False,
+                        fused_decode=args.fused_decode)
         g = torch.Generator().manual_seed(0)
         if args.one_step == "decode":
             ids = [f"r{i}" for i in range(args.batch)]
