@@ -46,11 +46,15 @@ def build_parser() -> argparse.ArgumentParser:
                          "(where the model has the shape it serves)")
     ap.add_argument("--prompt-ids", dest="prompt_ids", action="append", default=[],
                     help="comma-separated token ids; may be given several times")
+    ap.add_argument("--prompt-file", dest="prompt_file", default="",
+                    help="a file with one prompt per line: token ids separated by commas or blanks")
     ap.add_argument("--random-prompts", dest="random_prompts", default="",
                     help="N:LEN — N random prompts of LEN tokens")
     ap.add_argument("--max-new-tokens", dest="max_new_tokens", type=int, default=32)
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--top-k", dest="top_k", type=int, default=0)
+    ap.add_argument("--sample-seed", dest="sample_seed", type=int, default=None,
+                    help="seed of the sampling draws (request i uses seed + i); default: --seed")
     ap.add_argument("--no-eos-stop", dest="stop_at_eos", action="store_false")
     ap.add_argument("--json", action="store_true", help="one JSON object per request")
     return ap
@@ -82,14 +86,22 @@ def main(argv=None) -> int:
     engine = make_engine(args)
     vocab = engine.model.spec.vocab_size
     prompts = [[int(t) for t in p.replace(" ", "").split(",") if t] for p in args.prompt_ids]
+    if args.prompt_file:
+        with open(args.prompt_file) as fh:
+            for line in fh:
+                ids = [int(t) for t in line.replace(",", " ").split()]
+                if ids:
+                    prompts.append(ids)
     if args.random_prompts:
         import torch
         n, length = (int(x) for x in args.random_prompts.split(":"))
         g = torch.Generator().manual_seed(args.seed)
         prompts += torch.randint(0, vocab, (n, length), generator=g).tolist()
 
+    sample_seed = args.seed if args.sample_seed is None else args.sample_seed
+
     def req(p, i=0):
-        return Request(p, args.max_new_tokens, args.temperature, args.top_k, args.seed + i,
+        return Request(p, args.max_new_tokens, args.temperature, args.top_k, sample_seed + i,
                        args.stop_at_eos)
 
     t0 = time.perf_counter()

@@ -207,6 +207,29 @@ def test_command_line(lively):
     assert lines[-1]["n_requests"] == 1
 
 
+def test_command_line_prompt_file_and_sample_seed(lively, tmp_path):
+    """Prompts from a file (one a line, commas or blanks), and a sampling seed of its own:
+    request i draws with seed + i, as the plain sampler does."""
+    d, cfg, w = lively["tiny_b"]
+    prompts = _prompts(cfg, (9, 20), 23)
+    f = tmp_path / "prompts.txt"
+    f.write_text(",".join(map(str, prompts[0])) + "\n\n" + " ".join(map(str, prompts[1])) + "\n")
+    res = subprocess.run(
+        [sys.executable, "-m", "hetero_serve_b200", "--weights", d, "--dtype", "float32",
+         "--num-blocks", "16", "--max-new-tokens", "5", "--no-eos-stop", "--json",
+         "--temperature", "0.8", "--sample-seed", "41", "--seed", "3", "--prompt-file", str(f)],
+        capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [json.loads(l) for l in res.stdout.strip().splitlines()]
+    assert lines[-1]["n_requests"] == 2
+    for i, p in enumerate(prompts):
+        ctx = list(p)
+        for tok in lines[i]["output_ids"]:
+            row = plain_gpt2.forward(cfg, w, ctx)[-1]
+            assert tok == plain_gpt2.sample_token(row, 0.8, 0, plain_gpt2.uniform_for(41 + i, len(ctx)))
+            ctx.append(tok)
+
+
 def test_command_line_and_demo_with_random_weights():
     """`--model NAME` builds seeded random weights for a named configuration (no folder given)."""
     res = subprocess.run(
