@@ -551,7 +551,8 @@ def run_kernels(args):
     with tempfile.TemporaryDirectory(prefix="hsb200-bench-") as d:
         write_model_dir(d, cfg, seed=0, dtype=args.dtype)
         model, _ = load_model(d, args.dtype, "cuda:0")
-        rows = microbench.table(model, cfg, pk, dtype=args.dtype, batches=(1, 8, 64))
+        rows = microbench.table(model, cfg, pk, dtype=args.dtype, batches=(1, 8, 64),
+                                context=args.kernel_context)
     for r in rows:
         print(json.dumps(r))
     print(json.dumps({"peaks": pk_src, "hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"]}))
@@ -716,6 +717,8 @@ def main() -> int:
                          "default: it measures slower than the layer-by-layer path)")
     ap.add_argument("--no-kernels", dest="no_kernels", action="store_true",
                     help="skip the per-kernel roofline fractions")
+    ap.add_argument("--kernel-context", dest="kernel_context", type=int, default=768,
+                    help="context length of the decode attention in the --kernels table")
     ap.add_argument("--kernels", action="store_true",
                     help="print the per-kernel table (one JSON object a kernel) and exit")
     ap.add_argument("--one-step", dest="one_step", default="", choices=["", "decode", "prefill"],
