@@ -10,11 +10,13 @@
 // Order inside a layer, as in the reference (torch_engine.py:306-314): the new keys and values
 // are written first, then attention reads positions 0..p from the pages, the new ones included.
 //
-// attention_simt_kernel: one warp per (token, head).  Keys are taken 32 at a time in position
-// order, one key per lane; scores = (q . k) * scale with the multiply after the dot product
-// (torch_engine.py:135); the running maximum, the running sum and the output accumulators are
-// float32 (online softmax, as heteroserve/model/paged_attn_v2.py:124-156).  The order of every
-// sum depends only on the key positions, never on the batch.
+// attention_simt_kernel: one CTA of four warps per (token, head).  Keys are taken 32 at a time
+// in position order, one key per lane; chunk c of a token's keys belongs to stream c mod 4, and
+// warp s walks stream s with an online softmax (running maximum, running sum and output
+// accumulators in float32, as heteroserve/model/paged_attn_v2.py:124-156); the four streams are
+// then folded in stream order.  scores = (q . k) * scale with the multiply after the dot
+// product (torch_engine.py:135).  The order of every sum depends only on the key positions,
+// never on the batch, the cut of the prompt or the pages.
 #include "common.cuh"
 
 namespace hs {
@@ -70,61 +72,135 @@ __global__ void kv_append_kernel(T* __restrict__ pool, const T* __restrict__ qkv
   }
 }
 
-constexpr int AS_WARPS = 4;
 constexpr int AS_MAX_D = 256;
+constexpr int AS_CHUNK = 32;          // keys per step: one per lane
 
+__device__ __forceinline__ void as_copy16(void* smem_dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void as_copies_done() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+// dot += q[e..] . k[e..] over the elements of one 16-byte piece, in index order
+__device__ __forceinline__ float as_dot_piece(const float* q, uint4 raw, float dot, float) {
+  dot = fmaf(q[0], __uint_as_float(raw.x), dot);
+  dot = fmaf(q[1], __uint_as_float(raw.y), dot);
+  dot = fmaf(q[2], __uint_as_float(raw.z), dot);
+  return fmaf(q[3], __uint_as_float(raw.w), dot);
+}
+__device__ __forceinline__ float as_dot_piece(const float* q, uint4 raw, float dot, __nv_bfloat16) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    dot = fmaf(q[2 * i], __uint_as_float(w[i] << 16), dot);
+    dot = fmaf(q[2 * i + 1], __uint_as_float(w[i] & 0xffff0000u), dot);
+  }
+  return dot;
+}
+
+constexpr int AS_STREAMS = 4;         // warps per CTA; chunk c of a token belongs to stream c % 4
+
+// A step of 32 keys: every lane looks up its own key's page; the warp copies the 32 key rows
+// and the 32 value rows into its shared memory with 16-byte cp.async copies (all in flight
+// together: with a lane reading its key's row straight from the pool, and the value rows
+// fetched one after the other behind a shuffle, a step was 32 dependent trips to the L2),
+// 16-byte pieces swizzled by the key's index so that lane-per-key reads are free of bank
+// conflicts; then lane j forms key j's score as one chain of fused multiply-adds over
+// d = 0..D-1, the chunk joins the stream's running softmax, and lane d accumulates the values
+// of dimension d, d+32, ... key by key.  `both` false (large heads): keys and values take
+// turns in one buffer.
 template <typename T>
-__global__ void __launch_bounds__(AS_WARPS * 32)
+__global__ void __launch_bounds__(AS_STREAMS * 32)
 attention_simt_kernel(T* __restrict__ out, const T* __restrict__ qkv, const T* __restrict__ pool,
                       const int* __restrict__ table, const int* __restrict__ tok_pos,
-                      const int* __restrict__ tok_req, AttnGeom g, float scale, int* status) {
-  extern __shared__ float sq_all[];
+                      const int* __restrict__ tok_req, AttnGeom g, float scale, int both,
+                      int* status) {
+  extern __shared__ __align__(16) uint8_t as_smem[];
+  constexpr int VEC = 16 / (int)sizeof(T);             // elements per 16-byte piece
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x;
-  const int h = blockIdx.y * AS_WARPS + warp;
-  if (h >= g.n_heads) return;
+  const int t = blockIdx.x, h = blockIdx.y;
   const int D = g.head_dim;
-  float* sq = sq_all + warp * D;
+  const int pieces = D / VEC;                          // 16-byte pieces per row: 2 .. 64
+  // pieces are permuted inside groups of 8, or of the largest power of two that divides a row
+  int swz = 8;
+  while (pieces % swz) swz >>= 1;
+  swz -= 1;
+  // this warp's shared memory: q as float [D] | keys [32][D] T | values [32][D] T (if `both`)
+  const size_t rows_bytes = (size_t)AS_CHUNK * D * sizeof(T);
+  const size_t per_warp = (size_t)D * sizeof(float) + (both ? 2 : 1) * rows_bytes;
+  uint8_t* base = as_smem + (size_t)warp * per_warp;
+  float* sq = (float*)base;
+  T* sk = (T*)(base + (size_t)D * sizeof(float));
+  T* sv = both ? sk + (size_t)AS_CHUNK * D : sk;
   T* orow = out + (size_t)t * g.n_heads * D + (size_t)h * D;
   const int r = tok_req[t];
   const int p = tok_pos[t];
-  if (r < 0 || p < 0 || p / g.page_size >= g.max_pages) {
-    for (int d = lane; d < D; d += 32) orow[d] = from_f<T>(0.f);
+  if (r < 0 || p < 0 || p / g.page_size >= g.max_pages) {   // the same for the whole CTA
+    for (int d = threadIdx.x; d < D; d += blockDim.x) orow[d] = from_f<T>(0.f);
     return;
   }
   const int hk = h / (g.n_heads / g.n_kv_heads);
   const T* qrow = qkv + (size_t)t * g.qkv_stride + g.q_off + (size_t)h * D;
   for (int d = lane; d < D; d += 32) sq[d] = to_f(qrow[d]);
-  __syncwarp();
 
   const size_t tile = (size_t)g.page_size * D;
   const size_t page_stride = 2 * (size_t)g.n_kv_heads * tile;
+  const long long v_off = (long long)g.n_kv_heads * (long long)tile;
   const int* trow = table + (size_t)r * g.max_pages;
   const int lo = (g.window > 0 && p - g.window + 1 > 0) ? p - g.window + 1 : 0;
+  // piece i = lane + 32 * trip of a chunk: key i / pieces, piece i % pieces of its row
+  const int key0 = lane / pieces, pc0 = lane - key0 * pieces;
+  const int dkey = 32 / pieces, dpc = 32 - dkey * pieces;
 
   float m = -INFINITY, l = 0.f;
   float acc[AS_MAX_D / 32];
 #pragma unroll
   for (int i = 0; i < AS_MAX_D / 32; ++i) acc[i] = 0.f;
 
-  for (int j0 = lo; j0 <= p; j0 += 32) {
+  for (int j0 = lo + warp * AS_CHUNK; j0 <= p; j0 += AS_STREAMS * AS_CHUNK) {
     const int j = j0 + lane;
-    const bool valid = j <= p;
-    float s = -INFINITY;
-    long long voff = -1;
-    if (valid) {
+    long long koff = -1;                               // this lane's key row in the pool
+    if (j <= p) {
       const int page = trow[j / g.page_size];
-      if (page < 0 || page >= g.num_pages) {
+      if (page < 0 || page >= g.num_pages)
         atomicOr(status, HS_STATUS_BAD_PAGE);
-      } else {
-        const size_t koff = (size_t)page * page_stride + (size_t)hk * tile +
-                            (size_t)(j % g.page_size) * D;
-        voff = (long long)(koff + (size_t)g.n_kv_heads * tile);
-        const T* krow = pool + koff;
-        float dot = 0.f;
-        for (int d = 0; d < D; ++d) dot = fmaf(sq[d], to_f(krow[d]), dot);
-        s = dot * scale;
+      else
+        koff = (long long)((size_t)page * page_stride + (size_t)hk * tile +
+                           (size_t)(j % g.page_size) * D);
+    }
+    const int cnt = (p - j0 + 1) < AS_CHUNK ? (p - j0 + 1) : AS_CHUNK;
+    const unsigned live = __ballot_sync(0xffffffffu, koff >= 0);
+    __syncwarp();                                      // the step before is done with sk / sv
+    auto stage = [&](T* dst_rows, long long extra) {
+      int key = key0, pc = pc0;
+      for (int i0 = 0; i0 < cnt * pieces; i0 += 32) {  // the same trips for every lane
+        const long long ko = __shfl_sync(0xffffffffu, koff, key & 31);
+        if (key < cnt && ko >= 0)
+          as_copy16(dst_rows + key * D + ((pc & ~swz) | ((pc ^ key) & swz)) * VEC,
+                    pool + ko + extra + pc * VEC);
+        key += dkey;
+        pc += dpc;
+        if (pc >= pieces) { pc -= pieces; ++key; }
       }
+    };
+    stage(sk, 0);
+    if (both) stage(sv, v_off);
+    as_copies_done();
+    __syncwarp();
+    float s = -INFINITY;
+    if (koff >= 0) {
+      float dot = 0.f;
+      const uint4* krow = (const uint4*)(sk + (size_t)lane * D);
+      for (int pc = 0; pc < pieces; ++pc)
+        dot = as_dot_piece(sq + pc * VEC, krow[(pc & ~swz) | ((pc ^ lane) & swz)], dot, T());
+      s = dot * scale;
+    }
+    if (!both) {                                       // the values take the keys' place
+      __syncwarp();
+      stage(sv, v_off);
+      as_copies_done();
+      __syncwarp();
     }
     const float cm = warp_max(s);
     const float m_new = fmaxf(m, cm);
@@ -135,21 +211,52 @@ attention_simt_kernel(T* __restrict__ out, const T* __restrict__ qkv, const T* _
     l = l * corr + warp_sum(pj);
 #pragma unroll
     for (int i = 0; i < AS_MAX_D / 32; ++i) acc[i] *= corr;
-    const int cnt = (p - j0 + 1) < 32 ? (p - j0 + 1) : 32;
     for (int jj = 0; jj < cnt; ++jj) {
       const float pv = __shfl_sync(0xffffffffu, pj, jj);
-      const long long vo = __shfl_sync(0xffffffffu, voff, jj);
-      if (vo < 0) continue;
-      const T* vrow = pool + vo;
+      if (!((live >> jj) & 1u)) continue;
+      const T* vrow = sv + (size_t)jj * D;
 #pragma unroll
       for (int i = 0; i < AS_MAX_D / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < D) acc[i] = fmaf(pv, to_f(vrow[d]), acc[i]);
+        if (d < D) {
+          const int pc = d / VEC;
+          acc[i] = fmaf(pv, to_f(vrow[((pc & ~swz) | ((pc ^ jj) & swz)) * VEC + (d - pc * VEC)]),
+                        acc[i]);
+        }
       }
     }
     m = m_new;
   }
-  const float inv = l > 0.f ? 1.0f / l : 0.f;
+
+  // fold the streams in stream order: each warp leaves (m, l, acc) in its own shared memory
+  __syncwarp();
+  float* st = (float*)(base + (size_t)D * sizeof(float));   // the key rows' place: >= 2 + D floats
+  if (lane == 0) { st[0] = m; st[1] = l; }
+#pragma unroll
+  for (int i = 0; i < AS_MAX_D / 32; ++i) {
+    const int d = lane + 32 * i;
+    if (d < D) st[2 + d] = acc[i];
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float M = -INFINITY, L = 0.f;
+#pragma unroll
+  for (int i = 0; i < AS_MAX_D / 32; ++i) acc[i] = 0.f;
+  for (int sidx = 0; sidx < AS_STREAMS; ++sidx) {
+    const float* ss = (const float*)(as_smem + (size_t)sidx * per_warp + (size_t)D * sizeof(float));
+    const float ms = ss[0];
+    if (ms == -INFINITY) continue;                     // a stream without keys
+    const float m_new = fmaxf(M, ms);
+    const float c0 = expf(M - m_new), c1 = expf(ms - m_new);
+    L = L * c0 + ss[1] * c1;
+#pragma unroll
+    for (int i = 0; i < AS_MAX_D / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) acc[i] = fmaf(ss[2 + d], c1, acc[i] * c0);
+    }
+    M = m_new;
+  }
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
 #pragma unroll
   for (int i = 0; i < AS_MAX_D / 32; ++i) {
     const int d = lane + 32 * i;
@@ -206,16 +313,33 @@ HS_EXPORT int hs_attention_simt(void* out, const void* qkv, const void* pool, co
   if (int e = check_geom(g)) return e;
   if (n_tokens <= 0) return HS_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  dim3 grid(n_tokens, (n_heads + hs::AS_WARPS - 1) / hs::AS_WARPS);
-  size_t smem = (size_t)hs::AS_WARPS * head_dim * sizeof(float);
-  if (dtype == HS_DT_F32)
-    hs::attention_simt_kernel<float><<<grid, hs::AS_WARPS * 32, smem, st>>>(
-        (float*)out, (const float*)qkv, (const float*)pool, table, tok_pos, tok_req, g, scale,
-        status);
-  else if (dtype == HS_DT_BF16)
-    hs::attention_simt_kernel<__nv_bfloat16><<<grid, hs::AS_WARPS * 32, smem, st>>>(
-        (__nv_bfloat16*)out, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)pool, table,
-        tok_pos, tok_req, g, scale, status);
+  if ((uintptr_t)pool & 15) return HS_ERR_UNSUPPORTED;   // rows are copied 16 bytes at a time
+  if (n_heads > 65535) return HS_ERR_UNSUPPORTED;
+  // keys and values side by side in shared memory while four warps of them fit in 160 KB
+  const size_t esz = dtype == HS_DT_F32 ? 4 : 2;
+  const size_t rows_bytes = (size_t)hs::AS_CHUNK * head_dim * esz;
+  const int both = hs::AS_STREAMS * ((size_t)head_dim * 4 + 2 * rows_bytes) <= 160 * 1024 ? 1 : 0;
+  const size_t smem = hs::AS_STREAMS * ((size_t)head_dim * 4 + (both ? 2 : 1) * rows_bytes);
+  dim3 grid(n_tokens, n_heads);
+  if (dtype == HS_DT_F32) {
+    auto* k = hs::attention_simt_kernel<float>;
+    static cudaError_t state = cudaErrorUnknown;
+    if (state != cudaSuccess)
+      state = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 164 * 1024);
+    if (state != cudaSuccess) return (int)state;
+    k<<<grid, hs::AS_STREAMS * 32, smem, st>>>((float*)out, (const float*)qkv,
+                                                (const float*)pool, table, tok_pos, tok_req, g,
+                                                scale, both, status);
+  } else if (dtype == HS_DT_BF16) {
+    auto* k = hs::attention_simt_kernel<__nv_bfloat16>;
+    static cudaError_t state = cudaErrorUnknown;
+    if (state != cudaSuccess)
+      state = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 164 * 1024);
+    if (state != cudaSuccess) return (int)state;
+    k<<<grid, hs::AS_STREAMS * 32, smem, st>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)qkv,
+                                                (const __nv_bfloat16*)pool, table, tok_pos,
+                                                tok_req, g, scale, both, status);
+  }
   else
     return HS_ERR_UNSUPPORTED;
   HS_LAUNCH_CHECK();

@@ -77,6 +77,125 @@ linear_simt_kernel(TO* out, const TI* __restrict__ a, const TI* __restrict__ w,
   }
 }
 
+// ---- few rows (decode): the same chains, laid out for a weight stream -------------------------
+// With M <= 16 the tile kernel above leaves most of the machine idle (N / 64 CTAs, each walking
+// all of K behind two barriers per 16 columns).  Here a CTA owns 16 output features and all
+// rows; thread (feature f, row group g) runs the chains of rows g and g + 8 for feature f over
+// k = 0..K-1 in index order - the same chain of fused multiply-adds, so the same bits, as the
+// tile kernel gives that element.  The weight rows and the activation rows arrive through a
+// ring of four 128-column stages of 16-byte cp.async copies.
+constexpr int LF_BN = 16, LF_BK = 128, LF_THREADS = 128, LF_STAGES = 4, LF_MAX_M = 16;
+
+template <typename TI>
+struct LfShape {
+  static constexpr int VEC = 16 / (int)sizeof(TI);           // elements per 16-byte copy
+  static constexpr int WS = LF_BK + VEC;                     // weight row stride: no bank conflicts
+  static constexpr int STAGE = LF_BN * WS + LF_MAX_M * LF_BK;  // elements per stage
+  static constexpr size_t SMEM = (size_t)LF_STAGES * STAGE * sizeof(TI);
+};
+
+__device__ __forceinline__ void lf_copy16(void* smem_dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;                              // 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src),
+               "r"(n)
+               : "memory");
+}
+__device__ __forceinline__ void lf_load4(const float* p, float (&v)[4]) {
+  const float4 x = *(const float4*)p;
+  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+__device__ __forceinline__ void lf_load4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 x = *(const uint2*)p;
+  v[0] = __uint_as_float(x.x << 16); v[1] = __uint_as_float(x.x & 0xffff0000u);
+  v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
+}
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(LF_THREADS)
+linear_simt_few_rows_kernel(TO* out, const TI* __restrict__ a, const TI* __restrict__ w,
+                            const float* __restrict__ bias, const float* residual, int M, int N,
+                            int K, int act) {
+  using S = LfShape<TI>;
+  extern __shared__ __align__(16) uint8_t lf_smem[];
+  TI* ring = (TI*)lf_smem;
+  const int tid = threadIdx.x;
+  const int f = tid & 15, grp = tid >> 4;                    // rows grp and grp + 8
+  const int n0 = blockIdx.x * LF_BN;
+  const int num_kt = (K + LF_BK - 1) / LF_BK;
+  constexpr int CPR = LF_BK / S::VEC;                        // copies per row of a stage
+
+  auto issue = [&](int kt) {
+    if (kt < num_kt) {
+      TI* sw = ring + (size_t)(kt % LF_STAGES) * S::STAGE;
+      TI* sa = sw + LF_BN * S::WS;
+      for (int c = tid; c < LF_BN * CPR; c += LF_THREADS) {
+        const int row = c / CPR, kc = (c - row * CPR) * S::VEC;
+        const int gk = kt * LF_BK + kc, gn = n0 + row;
+        const bool ok = gn < N && gk < K;
+        lf_copy16(sw + row * S::WS + kc, ok ? w + (size_t)gn * K + gk : w, ok);
+      }
+      for (int c = tid; c < LF_MAX_M * CPR; c += LF_THREADS) {
+        const int row = c / CPR, kc = (c - row * CPR) * S::VEC;
+        const int gk = kt * LF_BK + kc;
+        const bool ok = row < M && gk < K;
+        lf_copy16(sa + row * LF_BK + kc, ok ? a + (size_t)row * K + gk : a, ok);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");   // one group per call, empty or not
+  };
+
+  for (int s = 0; s < LF_STAGES - 1; ++s) issue(s);
+  float acc0 = 0.f, acc1 = 0.f;
+  for (int kt = 0; kt < num_kt; ++kt) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(LF_STAGES - 2) : "memory");
+    __syncthreads();                 // stage kt has landed; stage kt - 1 is free for every thread
+    issue(kt + LF_STAGES - 1);
+    const TI* sw = ring + (size_t)(kt % LF_STAGES) * S::STAGE + f * S::WS;
+    const TI* sa0 = ring + (size_t)(kt % LF_STAGES) * S::STAGE + LF_BN * S::WS + grp * LF_BK;
+    const TI* sa1 = sa0 + 8 * LF_BK;
+    const int kmax = min(LF_BK, K - kt * LF_BK);             // a multiple of 4
+#pragma unroll 4
+    for (int k = 0; k < kmax; k += 4) {
+      float wv[4], x0[4], x1[4];
+      lf_load4(sw + k, wv);
+      lf_load4(sa0 + k, x0);
+      lf_load4(sa1 + k, x1);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc0 = fmaf(x0[i], wv[i], acc0);
+        acc1 = fmaf(x1[i], wv[i], acc1);
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  const int gn = n0 + f;
+  if (gn >= N) return;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int gm = grp + 8 * half;
+    if (gm >= M) continue;
+    float v = half ? acc1 : acc0;
+    if (bias) v += bias[gn];
+    v = apply_act(v, act);
+    if (residual) v += residual[(size_t)gm * N + gn];
+    out[(size_t)gm * N + gn] = from_f<TO>(v);
+  }
+}
+
+template <typename TI, typename TO>
+static int launch_few_rows(void* out, const void* a, const void* w, const float* bias,
+                           const float* residual, int M, int N, int K, int act, cudaStream_t st) {
+  auto* k = linear_simt_few_rows_kernel<TI, TO>;
+  static cudaError_t state = cudaErrorUnknown;
+  if (state != cudaSuccess)
+    state = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)LfShape<TI>::SMEM);
+  if (state != cudaSuccess) return (int)state;
+  k<<<(N + LF_BN - 1) / LF_BN, LF_THREADS, LfShape<TI>::SMEM, st>>>(
+      (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act);
+  return HS_OK;
+}
+
 }  // namespace hs
 
 HS_EXPORT int hs_linear_simt(void* out, const void* a, const void* w, const float* bias,
@@ -90,6 +209,20 @@ HS_EXPORT int hs_linear_simt(void* out, const void* a, const void* w, const floa
   if (grid.y > 65535) return HS_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
   using bf16 = __nv_bfloat16;
+  // few rows: the weight-stream kernel (rows and pointers that 16-byte copies can take)
+  const int vec = in_dtype == HS_DT_F32 ? 4 : 8;
+  if (M <= hs::LF_MAX_M && K % vec == 0 && !((uintptr_t)a & 15) && !((uintptr_t)w & 15)) {
+    int rc = HS_ERR_UNSUPPORTED;
+    if (in_dtype == HS_DT_F32 && out_dtype == HS_DT_F32)
+      rc = hs::launch_few_rows<float, float>(out, a, w, bias, residual, M, N, K, act, st);
+    else if (in_dtype == HS_DT_BF16 && out_dtype == HS_DT_BF16)
+      rc = hs::launch_few_rows<bf16, bf16>(out, a, w, bias, residual, M, N, K, act, st);
+    else if (in_dtype == HS_DT_BF16 && out_dtype == HS_DT_F32)
+      rc = hs::launch_few_rows<bf16, float>(out, a, w, bias, residual, M, N, K, act, st);
+    if (rc != HS_OK) return rc;
+    HS_LAUNCH_CHECK();
+    return HS_OK;
+  }
 #define HS_LS_LAUNCH(TI, TO)                                                                  \
   hs::linear_simt_kernel<TI, TO><<<grid, hs::LS_THREADS, 0, st>>>(                             \
       (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act)
