@@ -63,6 +63,14 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 N_WINDOWS = 5
 METRIC = ("decode tokens/s at batch 8, GPT-2 medium, 512-token prompts decoding to 1,024 "
           "(K steps spread over the whole trajectory)")
+MODEL_NAMES = {"gpt2": "GPT-2 small", "gpt2-medium": "GPT-2 medium", "gpt2-large": "GPT-2 large",
+               "gpt2-xl": "GPT-2 XL"}
+
+
+def metric_name(args):
+    """The headline metric's name; other presets of the family (--model) say which they are."""
+    name = MODEL_NAMES.get(args.model, args.model)
+    return METRIC.replace("GPT-2 medium", name).replace("batch 8", f"batch {args.batch}")
 
 
 def peaks():
@@ -159,7 +167,7 @@ def windows_mean_context(windows) -> float:
 
 def model_config(args):
     from hetero_serve_b200.config import preset
-    cfg = preset("gpt2-medium")
+    cfg = preset(args.model)
     full_layers = cfg["n_layer"]
     if args.layers:
         cfg["n_layer"] = args.layers
@@ -505,13 +513,13 @@ def run_ours(args):
                     points[f"{name}_{short}_{k}"] = v
 
     line = {
-        "metric": METRIC,
+        "metric": metric_name(args),
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
         "warmup": warmup, "ms_per_step": round(ms / steps, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if dtype == "bfloat16" else "fp32",
         "data": "synthetic", "impl": "ours",
         "config": {
-            "model": "gpt2-medium (random weights, seed 0)", "n_layer": cfg["n_layer"],
+            "model": f"{args.model} (random weights, seed 0)", "n_layer": cfg["n_layer"],
             "n_layer_full": full_layers, "n_embd": cfg["n_embd"], "n_head": cfg["n_head"],
             "head_dim": cfg["n_embd"] // cfg["n_head"], "n_inner": cfg["n_inner"],
             "vocab_size": vocab, "n_positions": cfg["n_positions"], "global_batch": batch,
@@ -621,6 +629,10 @@ def reference_root() -> str | None:
 
 
 def run_reference(args):
+    if args.model != "gpt2-medium":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference arm is set up for the headline's gpt2-medium only"}))
+        return 0
     ref = reference_root()
     if ref is None:
         print(json.dumps({"impl": "reference", "unavailable":
@@ -700,6 +712,9 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--model", default="gpt2-medium",
+                    help="preset of the architecture to time (this engine's arm; default: the "
+                         "headline's gpt2-medium)")
     ap.add_argument("--prompt-len", dest="prompt_len", type=int, default=512)
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],

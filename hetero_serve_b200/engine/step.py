@@ -164,6 +164,7 @@ class StepContext:
         self.fused = runner.fused   # the whole-step decode kernel's plan for this model, if any
         self.fused_tokens = None   # greedy tokens a fused step left (with the status word)
         self.greedy_only = False   # no wanted row of this step samples with a temperature
+        self.sampling = False      # the step chooses tokens (a head may then choose them itself)
         self.plan = None          # work lists for the specialised attention kernels, if any
         self.position = None      # the model's position encoding (set by Model.forward)
         self.call_index: int | None = None
@@ -514,6 +515,7 @@ class Runner:
 
     def _forward(self, ctx: StepContext, sample: bool):
         ctx.fused_tokens = None
+        ctx.sampling = bool(sample)
         logits = self.model.forward(ctx)
         tokens = None
         if sample and logits is not None:

@@ -13,6 +13,7 @@ signature; the kernel tests compare the two.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_void_p
 from dataclasses import dataclass
 
@@ -170,6 +171,8 @@ def _declare(lib) -> None:
         "hs_linear_tcgen05_scratch": [I, I, I, I, I, P, P],
         "hs_linear_skinny": [P, P, P, P, P, F, P, P, P, I, I, I, I, I, P, P, I, P],
         "hs_linear_skinny_scratch": [I, I, I, I, P, P],
+        "hs_linear_skinny_argmax": [P, P, P, I, I, I, P, P, P, P, P, P, P, I, P],
+        "hs_linear_skinny_argmax_scratch": [I, I, I, P],
         "hs_kv_append": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "hs_attention_simt": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
         "hs_attention_decode_append": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I,
@@ -260,6 +263,7 @@ class CudaOps:
         self.tc_attention = True    # head size 64: prompt portions on the tcgen05 attention kernel
         self.sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
         self.fuse_norm = True      # LayerNorm fused into the few-row linear kernel
+        self.fuse_argmax = os.environ.get("HS_FUSE_ARGMAX", "1") != "0"    # greedy choice fused into the few-row head (linear_argmax)
         self.fuse_append = True    # key/value append fused into the decode attention
         self.pdl = True            # programmatic dependent launch (see the property below)
         self._skinny_need: dict = {}
@@ -476,6 +480,58 @@ class CudaOps:
         if code == -1:
             return False
         _check(code, f"linear_skinny(M={M},N={N},K={K})")
+        return True
+
+    def linear_argmax(self, out, a, w, tokens, feedback=None, feedback_slot=None,
+                      status_word=None) -> bool:
+        """out = a @ w.T as float32 logits AND tokens[m] = argmax of row m (lowest index on
+        ties), in the one few-row kernel: its CTAs keep their best per row while they stream
+        the table, the last to finish picks.  ``tokens`` has a word more than rows, which
+        receives ``status_word``; ``feedback[feedback_slot[m]]`` gets row m's token as in
+        `sample`.  False (nothing done) for shapes or types the kernel does not take: the
+        caller then runs `linear` and `sample`."""
+        if not (self.tensor_cores and self.fuse_argmax and a.dtype == torch.bfloat16
+                and w.dtype == torch.bfloat16 and out.dtype == torch.float32):
+            return False
+        _want(a, "a", torch.bfloat16, 2)
+        _want(w, "w", torch.bfloat16, 2)
+        _want(out, "out", torch.float32, 2)
+        _want(tokens, "tokens", torch.int32, 1)
+        M, K = a.shape
+        N = w.shape[0]
+        if M > self.skinny_max_rows or w.shape[1] != K or tuple(out.shape) != (M, N):
+            return False
+        if tokens.shape[0] < M + 1:
+            raise KernelError("linear_argmax: tokens needs a word more than rows")
+        if (feedback is None) != (feedback_slot is None):
+            raise KernelError("linear_argmax: feedback and feedback_slot come together")
+        if feedback is not None:
+            _want(feedback, "feedback", torch.int32, 1)
+            _want(feedback_slot, "feedback_slot", torch.int32, 1)
+            if feedback_slot.shape[0] < M:
+                raise KernelError("linear_argmax: feedback_slot shorter than the rows")
+        if status_word is not None:
+            _want(status_word, "status_word", torch.int32, 1)
+        key = ("argmax", M, N, K)
+        need = self._skinny_need.get(key)
+        if need is None:
+            entries = ctypes.c_int(0)
+            code = self.lib.hs_linear_skinny_argmax_scratch(M, N, K, ctypes.byref(entries))
+            need = entries.value if code == 0 else False
+            self._skinny_need[key] = need
+        if need is False:
+            return False
+        val = self._scratch_buffer("argmax_val", need, torch.float32)
+        idx = self._scratch_buffer("argmax_idx", need, torch.int32)
+        cnt = self._scratch_buffer("argmax_counter", 1, torch.int32)
+        code = self.lib.hs_linear_skinny_argmax(
+            _ptr(out), _ptr(a), _ptr(w), M, N, K, _ptr(tokens), _ptr(feedback),
+            _ptr(feedback_slot), _ptr(status_word), _ptr(val), _ptr(idx), _ptr(cnt),
+            int(self.pdl), self._stream())
+        if code == -1:
+            return False
+        _check(code, f"linear_argmax(M={M},N={N},K={K})")
+        self.launches += 1
         return True
 
     def norm_linear(self, out, h, x, gamma, beta, eps, w, bias=None, act="none"):

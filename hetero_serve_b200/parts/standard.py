@@ -236,6 +236,16 @@ class LinearHead(Head):
         self.weight = tensors[self.name]
 
     def forward(self, ctx, logits, h):
+        # a step that samples and whose rows all take the argmax: the few-row kernel picks the
+        # tokens while it streams the table (and stores the status word behind them)
+        fused = getattr(ctx.ops, "linear_argmax", None)
+        if fused is not None and getattr(ctx, "sampling", False) \
+                and getattr(ctx, "greedy_only", False):
+            tokens = ctx.buffer("sampled", (logits.shape[0] + 1,), torch.int32)
+            if fused(logits, h, self.weight, tokens, feedback=ctx.feedback,
+                     feedback_slot=ctx.samp_slot, status_word=ctx.status):
+                ctx.fused_tokens = tokens
+                return
         ctx.ops.linear(logits, h, self.weight)
 
     def fused_decode_params(self):

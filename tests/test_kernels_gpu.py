@@ -487,6 +487,51 @@ def test_argmax_lowest_index_on_ties(ops, vocab):
     assert out.tolist() == want
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 50257, 1024), (8, 50257, 1024), (16, 50257, 1600),
+                                   (3, 517, 64), (8, 1000, 128), (13, 40000, 768), (5, 17, 32)])
+def test_head_with_the_greedy_choice_fused_in(ops, M, N, K):
+    """linear_argmax: the logits equal those of `linear`, the tokens are the lowest index of
+    each row's maximum (ties planted across feature blocks and CTAs, and a row whose values
+    are all equal), the status word follows the tokens, feedback slots receive their tokens
+    and slots below zero are skipped; a second launch finds the counter at zero again."""
+    torch.manual_seed(M * N + K)
+    a = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.5).bfloat16()
+    if N > 600:                                 # equal rows of the table give equal logits
+        w[N - 1] = w[3]
+        w[N // 2] = w[3]
+    a[M - 1] = 0 if M > 1 else a[M - 1]          # a row of zeros: every logit equal -> token 0
+    plain_out = torch.empty(M, N, device=DEV)
+    ops.linear(plain_out, a, w)
+    for _ in range(2):
+        out = torch.full((M, N), float("nan"), device=DEV)
+        tokens = torch.full((M + 1,), -7, dtype=torch.int32, device=DEV)
+        feedback = torch.full((M + 2,), -1, dtype=torch.int32, device=DEV)
+        slot = torch.arange(M, dtype=torch.int32, device=DEV) + 1
+        slot[0] = -1
+        status = torch.tensor([1234], dtype=torch.int32, device=DEV)
+        assert ops.linear_argmax(out, a, w, tokens, feedback=feedback, feedback_slot=slot,
+                                 status_word=status)
+        assert torch.equal(out, plain_out)
+        ref = out.double()
+        want = [int((ref[m] == ref[m].max()).nonzero()[0]) for m in range(M)]
+        assert tokens[:M].tolist() == want
+        assert int(tokens[M]) == 1234
+        assert feedback[0].item() == -1 and feedback[1].item() == -1     # slot -1 and no row for 1
+        assert feedback[2:M + 1].tolist() == want[1:]
+    if M > 1:
+        assert want[M - 1] == 0
+
+
+def test_head_with_the_greedy_choice_refuses_what_it_does_not_take(ops):
+    a = torch.randn(40, 64, device=DEV).bfloat16()
+    w = torch.randn(100, 64, device=DEV).bfloat16()
+    out = torch.empty(40, 100, device=DEV)
+    tokens = torch.zeros(41, dtype=torch.int32, device=DEV)
+    assert ops.linear_argmax(out, a, w, tokens) is False                 # too many rows
+    assert ops.linear_argmax(out[:4].float(), a[:4].float(), w.float(), tokens) is False
+
+
 @pytest.mark.parametrize("vocab,top_k", [(1000, 0), (1000, 1), (1000, 40), (50257, 0),
                                          (50257, 50), (37, 36), (37, 100)])
 def test_sample_matches_the_plain_sampler(ops, plain, vocab, top_k):
