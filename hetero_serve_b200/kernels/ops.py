@@ -13,7 +13,6 @@ signature; the kernel tests compare the two.
 from __future__ import annotations
 
 import ctypes
-import os
 from ctypes import c_float, c_int, c_void_p
 from dataclasses import dataclass
 
@@ -263,7 +262,7 @@ class CudaOps:
         self.tc_attention = True    # head size 64: prompt portions on the tcgen05 attention kernel
         self.sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
         self.fuse_norm = True      # LayerNorm fused into the few-row linear kernel
-        self.fuse_argmax = os.environ.get("HS_FUSE_ARGMAX", "1") != "0"    # greedy choice fused into the few-row head (linear_argmax)
+        self.fuse_argmax = True    # greedy choice fused into the few-row head (linear_argmax)
         self.fuse_append = True    # key/value append fused into the decode attention
         self.pdl = True            # programmatic dependent launch (see the property below)
         self._skinny_need: dict = {}
