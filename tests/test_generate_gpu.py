@@ -77,6 +77,36 @@ def test_bfloat16_generation_follows_the_plain_argmax(lively, policy):
         _check_greedy_path(cfg, wb, p, o, margin=0.15)
 
 
+@pytest.mark.parametrize("graphs", [False, True], ids=["eager", "graphs"])
+def test_greedy_rows_are_chosen_by_the_head_kernel_itself(lively, graphs):
+    """A bfloat16 step whose rows all take the argmax has no sampling launch: the few-row head
+    picks while it streams the table.  Its tokens are the argmax of the logits it returns
+    (lowest index on ties), a temperature in the batch brings the sampler back, and a prompt's
+    last row is chosen the same way."""
+    from hetero_serve_b200.engine.loading import load_model
+    from hetero_serve_b200.engine.step import Runner, StepEntry
+    d, cfg, _ = lively["tiny_b"]
+    model, _ = load_model(d, "bfloat16", "cuda:0")
+    rn = Runner(model, num_pages=16, page_size=16, max_requests=4, dtype=torch.bfloat16,
+                device="cuda:0", cuda_graphs=graphs)
+    prompts = _prompts(cfg, (9, 20, 5), 77)
+    res = rn.step([StepEntry(f"r{i}", p, want=[len(p) - 1]) for i, p in enumerate(prompts)],
+                  sample=True)
+    assert res.tokens_host() == [int(torch.argmax(r)) for r in res.logits]
+    counts = {}
+    for temp in (0.0, 0.0, 0.7, 0.0):
+        before = rn.kernel_launches
+        res = rn.step([StepEntry(f"r{i}", [3 + i], want=[0], temperature=temp if i == 1 else 0.0,
+                                 seed=5) for i in range(3)], sample=True)
+        counts.setdefault(temp, []).append(rn.kernel_launches - before)
+        toks = res.tokens_host()
+        for i in (0, 2):
+            assert toks[i] == int(torch.argmax(res.logits[i]))
+    assert len(set(counts[0.0])) == 1
+    assert counts[0.7][0] == counts[0.0][0] + 1              # the sampler is a launch of its own
+    rn.check_status()
+
+
 def test_temperature_and_top_k_sampling_match_the_plain_sampler(lively):
     d, cfg, w = lively["tiny_b"]
     prompts = _prompts(cfg, (9, 40), 13)
