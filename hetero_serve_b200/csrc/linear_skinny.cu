@@ -81,6 +81,11 @@ struct WBatch {
   uint4 a[4], b[4];
 };
 
+// A warp's partial tile in shared memory: [row of the batch][feature], 17 floats a row, so that
+// the epilogue's threads (consecutive features of one row) read consecutive words and the
+// writers' lanes spread over the banks.  (As [feature][row] a read of 16-row tiles hit two banks:
+// 1 us of a 7.5 us launch at 16 rows.)
+constexpr int SK_RED_ROW = 17;
 constexpr int SK_LN_ROW_F4 = 8;       // a row of up to 8 * 128 = 1024 floats is normalised from registers
                                       // two rows at a time, up to 2048 floats one row at a time;
                                       // longer rows take the three-pass route
@@ -310,18 +315,26 @@ linear_skinny_kernel(const typename SkinnyParamsOf<ARGMAX>::type p) {
     }
   } else if (kn > 0) {
     // ---- stage this CTA's k range of the bfloat16 activations [MP][kn] (rows past M are zero)
-#pragma unroll 4
+    // by 16-byte cp.async copies, all in flight together (through registers, four at a time,
+    // 16 rows of a 4,096-wide layer were four trips to the L2: 3.0 us; eight rows 1.3 us)
     for (int i = threadIdx.x; i < MP * (kn / 8); i += THREADS) {
       const int m = i / (kn / 8), kk = (i % (kn / 8)) * 8;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (m < M) v = *(const uint4*)(p.a + (size_t)m * K + k0 + kk);
-      *(uint4*)(sx + (size_t)m * p.stride + kk) = v;
+      __nv_bfloat16* dst = sx + (size_t)m * p.stride + kk;
+      if (m < M) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                         (uint32_t)__cvta_generic_to_shared(dst)),
+                     "l"(p.a + (size_t)m * K + k0 + kk)
+                     : "memory");
+      } else {
+        *(uint4*)dst = make_uint4(0, 0, 0, 0);
+      }
     }
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
   }
   __syncthreads();
   mark_time(p.timing, cta_id, 2);
 
-  float* red = (float*)(sk_smem + (LOOP ? p.red_offset : 0));   // [NW][16][MP]
+  float* red = (float*)(sk_smem + (LOOP ? p.red_offset : 0));   // [NW][MP][SK_RED_ROW]
   // output elements of a feature block per thread: up to 128 features x MP rows over the CTA
   constexpr int SLOTS = (128 * MP + THREADS - 1) / THREADS;
   float best_v[ARGMAX ? SLOTS : 1];
@@ -367,10 +380,10 @@ linear_skinny_kernel(const typename SkinnyParamsOf<ARGMAX>::type p) {
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
     const int m = mt * 8 + t * 2;
-    red[(warp * 16 + g) * MP + m] = c[mt][0];
-    red[(warp * 16 + g) * MP + m + 1] = c[mt][1];
-    red[(warp * 16 + g + 8) * MP + m] = c[mt][2];
-    red[(warp * 16 + g + 8) * MP + m + 1] = c[mt][3];
+    red[(warp * MP + m) * SK_RED_ROW + g] = c[mt][0];
+    red[(warp * MP + m + 1) * SK_RED_ROW + g] = c[mt][1];
+    red[(warp * MP + m) * SK_RED_ROW + g + 8] = c[mt][2];
+    red[(warp * MP + m + 1) * SK_RED_ROW + g + 8] = c[mt][3];
   }
   __syncthreads();
   if (ksplit > 1) {
@@ -383,7 +396,7 @@ linear_skinny_kernel(const typename SkinnyParamsOf<ARGMAX>::type p) {
       if (n >= p.N) continue;
       const int grp = ff / 16, f = ff % 16;
       float v = 0.f;
-      for (int k8 = 0; k8 < n_kg; ++k8) v += red[((k8 * p.ng + grp) * 16 + f) * MP + m];
+      for (int k8 = 0; k8 < n_kg; ++k8) v += red[((k8 * p.ng + grp) * MP + m) * SK_RED_ROW + f];
       mine[(size_t)m * p.N + n] = v;
     }
     __threadfence();
@@ -405,7 +418,7 @@ linear_skinny_kernel(const typename SkinnyParamsOf<ARGMAX>::type p) {
         v += __ldcg(p.partial + ((size_t)ks * MP + m) * p.N + n);
     } else {
       const int grp = ff / 16, f = ff % 16;
-      for (int k8 = 0; k8 < n_kg; ++k8) v += red[((k8 * p.ng + grp) * 16 + f) * MP + m];
+      for (int k8 = 0; k8 < n_kg; ++k8) v += red[((k8 * p.ng + grp) * MP + m) * SK_RED_ROW + f];
     }
     const bool first = first_fb && i == my_e;            // bias (and residual) already in registers
     if (p.bias) v += first ? my_bias : p.bias[n];
@@ -426,7 +439,7 @@ linear_skinny_kernel(const typename SkinnyParamsOf<ARGMAX>::type p) {
       if (i < feats * MP && m < M && n < p.N) {
         const int grp = ff / 16, f = ff % 16;
         float v = 0.f;
-        for (int k8 = 0; k8 < n_kg; ++k8) v += red[((k8 * p.ng + grp) * 16 + f) * MP + m];
+        for (int k8 = 0; k8 < n_kg; ++k8) v += red[((k8 * p.ng + grp) * MP + m) * SK_RED_ROW + f];
         ((float*)p.out)[(size_t)m * p.N + n] = v;
         if (v > best_v[j] || best_i[j] == 0x7fffffff) {
           best_v[j] = v;
@@ -577,7 +590,7 @@ static bool plan_skinny(int M, int N, int K, bool with_norm, SkinnyPlan& pl) {
     // them, or behind them when a CTA walks several feature blocks
     size_t sm = (size_t)pl.mp * stride * 2 + (with_norm ? (size_t)kper * 8 : 0);
     sm = (sm + 15) / 16 * 16;
-    const size_t red = (size_t)16 * 16 * pl.mp * 4;
+    const size_t red = (size_t)16 * SK_RED_ROW * pl.mp * 4;
     pl.red_offset = (int)sm;
     pl.smem_loop = sm + red;
     return sm > red ? sm : red;
