@@ -577,10 +577,11 @@ def run_one_step(args):
     cfg, _ = model_config(args)
     vocab = cfg["vocab_size"]
     with tempfile.TemporaryDirectory(prefix="hsb200-bench-") as d:
-        write_model_dir(d, cfg, seed=0, dtype="bfloat16")
-        model, _ = load_model(d, "bfloat16", "cuda:0")
+        tdt = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+        write_model_dir(d, cfg, seed=0, dtype=args.dtype)
+        model, _ = load_model(d, args.dtype, "cuda:0")
         runner = Runner(model, num_pages=args.batch * 64 + 136, page_size=16, max_requests=64,
-                        dtype=torch.bfloat16, device="cuda:0", cuda_graphs=False,
+                        dtype=tdt, device="cuda:0", cuda_graphs=False,
                         fused_decode=args.fused_decode)
         g = torch.Generator().manual_seed(0)
         if args.one_step == "decode":
