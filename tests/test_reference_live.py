@@ -1,5 +1,5 @@
 """Live anchors on the reference itself, when its checkout is on this machine
-(``HETEROSERVE_SOURCE``, default ``/root/reference``; skipped otherwise — the committed golden
+(the folder named by ``HETEROSERVE_SOURCE``, or the default below; skipped otherwise — the committed golden
 file under tests/golden/ then stands alone).  The reference's CPU code is imported from that
 path and run beside this repository's: nothing of it is copied here.
 
