@@ -48,9 +48,11 @@ struct PrefillParams {
 template <int D>
 __device__ __forceinline__ int swz(int row, int chunk) {
   constexpr int CPR = D / 8;                       // 16-byte chunks per row
-  constexpr int RPL = CPR >= 8 ? 1 : 8 / CPR;      // rows per 128-byte line
-  constexpr int MASK = (CPR >= 8 ? 8 : CPR) - 1;
-  return row * CPR + (chunk ^ ((row / RPL) & MASK));
+  constexpr int RPL = CPR >= 8 ? 1 : (8 / CPR > 0 ? 8 / CPR : 1);   // rows per 128-byte line
+  // chunks are permuted inside groups of 8, or of the largest power of two that divides a row
+  // (head sizes 48, 80, 96, 112: groups of 2 or 4, some bank conflicts, the same result)
+  constexpr int GROUP = CPR % 8 == 0 ? 8 : (CPR % 4 == 0 ? 4 : (CPR % 2 == 0 ? 2 : 1));
+  return row * CPR + (chunk ^ ((row / RPL) & (GROUP - 1)));
 }
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -306,7 +308,7 @@ static int launch_prefill(const PrefillParams& p, cudaStream_t st) {
   constexpr int smem = (AP_BQ + 2 * AP_STAGES * AP_BKV) * D * 2;
   static int ctas = 0;                 // persistent CTAs: as many as are resident at once
   if (ctas == 0) {
-    if (smem > 48 * 1024) {
+    if (smem > 40 * 1024) {      // with the kernel's static shared memory: beyond the default 48 KB
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       if (e != cudaSuccess) return (int)e;
     }
@@ -357,7 +359,11 @@ HS_EXPORT int hs_attention_prefill(void* out, const void* qkv, const void* pool,
   switch (head_dim) {
     case 16: return launch_prefill<16>(p, st);
     case 32: return launch_prefill<32>(p, st);
+    case 48: return launch_prefill<48>(p, st);
     case 64: return launch_prefill<64>(p, st);
+    case 80: return launch_prefill<80>(p, st);
+    case 96: return launch_prefill<96>(p, st);
+    case 112: return launch_prefill<112>(p, st);
     case 128: return launch_prefill<128>(p, st);
     default: return HS_ERR_UNSUPPORTED;
   }

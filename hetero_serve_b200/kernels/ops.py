@@ -687,7 +687,7 @@ class CudaOps:
         need = -(-max_context // per_warp)
         return max(1, need, min(want, max(1, max_context // 64), 32))
 
-    FAST_HEAD_DIMS = (16, 32, 64, 128)
+    FAST_HEAD_DIMS = (16, 32, 48, 64, 80, 96, 112, 128)
     _lib_split_clusters = True     # what the library's switch was last set to
 
     def _fast_ok(self, qkv, g, plan, n, scale=1.0) -> bool:

@@ -311,6 +311,12 @@ FAST_CASES = [
     (2, 1, 128, 32, [300, 64, 129], [130, 1, 129]),              # pages of 32, head size 128
     (5, 5, 32, 48, [100, 130], [100, 2]),                        # pages of 48
     (2, 2, 64, 16, [64, 63, 65, 128, 1, 300], [64, 63, 65, 64, 1, 129]),   # tile edges
+    # head sizes that are no power of two: prompt portions only (the single-query kernels do not
+    # take them; a batch that has such tokens goes to the general kernel whole)
+    (3, 3, 48, 16, [70, 130, 9, 200], [70, 130, 9, 66]),
+    (2, 1, 80, 16, [150, 64, 30], [150, 20, 30]),
+    (4, 2, 96, 16, [129, 300, 40], [129, 65, 40]),
+    (2, 2, 112, 32, [200, 65], [200, 5]),
 ]
 
 
