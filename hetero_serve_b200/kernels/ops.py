@@ -733,8 +733,15 @@ class CudaOps:
             group = g.n_heads // g.n_kv_heads
             use_mma = (self.decode_mma and self.decode_force is None
                        and g.head_dim in (32, 64, 128) and group <= 16)
-            splits = (max(1, -(-max_ctx // 2048)) if use_mma
-                      else self.decode_splits(plan.decode_cap, g.n_heads, max_ctx))
+            if use_mma:
+                # slices of at most 2,048 keys; a long table and so few (token, head) pairs that
+                # they leave SMs idle: more, shorter slices (of 512 keys or more), a CTA an SM
+                splits = max(1, -(-max_ctx // 2048))
+                pairs = plan.decode_cap * g.n_kv_heads
+                if max_ctx >= 2048 and pairs * splits <= self.sm_count:
+                    splits = max(splits, min(-(-max_ctx // 512), self.sm_count // pairs))
+            else:
+                splits = self.decode_splits(plan.decode_cap, g.n_heads, max_ctx)
             acc = ml = cnt = None
             if splits > 1:
                 rows = plan.decode_cap * g.n_heads * splits
