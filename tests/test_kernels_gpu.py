@@ -366,6 +366,9 @@ DECODE_ONLY = [
     (8, 8, 32, 16, [150, 33] * 12),                                # the same for head size 32
     (8, 8, 32, 16, [70] * 40),
     (16, 16, 64, 16, [90, 17, 160, 33] * 8),                       # 512 pairs: four CTAs an SM
+    (16, 16, 64, 16, [5000, 2049, 100]),                           # beyond 2,048 keys: slices, merged
+    (4, 2, 64, 16, [6000]),                                        # a long table, two pairs: many slices
+    (2, 2, 128, 32, [4100, 33, 2048, 2047]),
 ]
 
 
@@ -396,6 +399,27 @@ def test_decode_attention_with_the_append_fused_in(ops, plain, case, decode_kern
     pool2 = pool_ref.clone()
     ops.attention_append(out, qkv, pool2, table, tok_pos, tok_req, geom, 0.11, st, plan, False)
     assert torch.equal(torch.nan_to_num(pool2, nan=9.0), torch.nan_to_num(pool_ref, nan=9.0))
+
+
+@pytest.mark.parametrize("far", [0, 700, 2047, 2048, 3500, 4999])
+def test_far_key_in_every_slice_of_a_long_context(ops, far):
+    """One request of 5,000 keys: its context is cut into slices between CTAs.  A planted key
+    decides the output wherever it lies (a slice dropped, or merged with a wrong weight, shows)."""
+    H, D, PS, n = 4, 64, 16, 5000
+    geom, qkv, pool, table, tok_pos, tok_req = _attention_case(H, H, D, PS, [n], [1], 0,
+                                                               torch.bfloat16, 5)
+    st = _status()
+    ops.kv_append(pool, qkv, table, tok_pos, tok_req, geom, st)
+    pv = pool.view(geom.num_pages, 2, H, PS, D)
+    q = qkv[-1, :H * D].view(H, D).float()
+    page, slot = int(table[0, far // PS]), far % PS
+    pv[page, 0, :, slot, :] = (q / q.norm(dim=-1, keepdim=True) * 40).to(torch.bfloat16)
+    out = torch.empty(1, H * D, device=DEV, dtype=torch.bfloat16)
+    plan = ops.make_plan(_host_batch([n], [1]), 1, PS)
+    ops.attention(out, qkv, pool, table, tok_pos, tok_req, geom, 1.0, st, plan)
+    want = pv[page, 1, :, slot, :].reshape(H * D).float()
+    assert st.item() == 0
+    assert (out[-1].float() - want).abs().max() < 2e-2
 
 
 @pytest.mark.parametrize("far", [0, 63, 64, 500, 1000])
