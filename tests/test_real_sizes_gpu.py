@@ -111,3 +111,45 @@ def test_full_depth_medium_long_prompt_then_decoding(tmp_path_factory, dtype):
     # bits between kernels, 24 layers deep
     tol = 5e-4 if dtype == "float32" else 1e-1
     assert float(err.max()) < tol, [round(float(e), 6) for e in err]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_table_of_4096_positions(tmp_path, dtype):
+    """A configuration with a longer table than the family's 1,024: a prompt of 2,900 tokens
+    in two portions (prefill tiles that look back over thousands of keys, a portion starting
+    mid-context), then single tokens whose context is cut into slices between CTAs (beyond
+    2,048 keys), beside a short request.  Compared with the plain model on the rows kept."""
+    cfg = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", vocab_size=331,
+               n_positions=4096, n_layer=2, n_embd=128, n_head=2, n_inner=None,
+               layer_norm_epsilon=1e-5, activation_function="gelu_new",
+               scale_attn_by_inverse_layer_idx=False, tie_word_embeddings=True)
+    write_model_dir(tmp_path, cfg, 5, "float32")
+    raw = read_safetensors(tmp_path / "model.safetensors")
+    cfg = json.loads((tmp_path / "config.json").read_text())
+    g = torch.Generator().manual_seed(21)
+    a = torch.randint(0, 331, (2906,), generator=g).tolist()
+    b = torch.randint(0, 331, (40,), generator=g).tolist()
+    w = plain_gpt2.prepare_weights(raw, dtype=torch.float32,
+                                   round_to=torch.bfloat16 if dtype == "bfloat16" else None)
+    ref_a = plain_gpt2.forward(cfg, w, a, dtype=torch.float32, rows=[1499, 2899, 2900, 2905])
+    ref_b = plain_gpt2.forward(cfg, w, b, dtype=torch.float32, rows=[33, 39])
+    model, _ = load_model(str(tmp_path), dtype, "cuda:0")
+    rn = Runner(model, num_pages=200, page_size=16, max_requests=4, dtype=model.dtype,
+                device="cuda:0", cuda_graphs=(dtype == "bfloat16"))
+    got = []
+    got.append(rn.step([StepEntry("a", a[:1500], want=[1499])]).logits[0].clone())
+    r = rn.step([StepEntry("a", a[1500:2900], want=[1399]),
+                 StepEntry("b", b[:34], want=[33])]).logits.clone()
+    got.append(r[0]); keep_b = [r[1]]
+    for i in range(6):
+        r = rn.step([StepEntry("a", a[2900 + i:2901 + i], want=[0]),
+                     StepEntry("b", b[34 + i:35 + i], want=[0])]).logits.clone()
+        if i in (0, 5):
+            got.append(r[0])
+        if i == 5:
+            keep_b.append(r[1])
+    tol = 2e-3 if dtype == "float32" else 6e-2
+    for row, ref in zip(got + keep_b, list(ref_a) + list(ref_b)):
+        assert torch.isfinite(row).all()
+        assert float((row.float().cpu() - ref).abs().max()) < tol
+    rn.manager.check()
