@@ -889,6 +889,29 @@ linear_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_a,
   const int rows_here = min(TC_BM, p.M - m0);
   const int rpo = (rows_here + splits - 1) / splits;
   const int et = threadIdx.x - 4 * 32;                   // 0..255 among the epilogue threads
+  // What this thread's first two output pieces need besides the sums - bias and residual - is
+  // requested now, while the MMAs run: behind the cluster's barrier it would be a trip to the
+  // L2 on the launch's critical path.
+  constexpr int CL_PIECES = CL_BN / 4;
+  constexpr int CL_EARLY = 2;
+  const int cl_first = rank * rpo;
+  const int cl_rows = max(0, min(rpo, rows_here - cl_first));
+  const bool cl_vec4 = (p.N % 4 == 0);
+  float4 early_b[CL_EARLY], early_r[CL_EARLY];
+#pragma unroll
+  for (int i = 0; i < CL_EARLY; ++i) {
+    early_b[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    early_r[i] = early_b[i];
+    const int e = et + i * TC_EPI_WARPS * 32;
+    if (warp >= 4 && cl_vec4 && e < cl_rows * CL_PIECES) {
+      const int lr = e / CL_PIECES, n = n0 + (e % CL_PIECES) * 4;
+      if (n < p.N) {
+        if (p.bias) early_b[i] = __ldg((const float4*)(p.bias + n));
+        if (p.residual)
+          early_r[i] = *(const float4*)(p.residual + (size_t)(m0 + cl_first + lr) * p.N + n);
+      }
+    }
+  }
   if (warp >= 4) {
     // ---------------- send: warp (w % 4) owns TMEM lanes 32*(w%4) .. +31 = rows of the tile,
     // the two groups of four warps take the two halves of the 64 columns
@@ -917,20 +940,27 @@ linear_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_a,
 
   if (warp >= 4) {
     // ---------------- this CTA's rows: shares added in split order, then the epilogue
-    const int my_first = rank * rpo;
-    const int my_rows = max(0, min(rpo, rows_here - my_first));
+    const int my_first = cl_first;
+    const int my_rows = cl_rows;
     TO* out = (TO*)p.out;
-    const bool vec4 = (p.N % 4 == 0);
-    constexpr int PIECES = CL_BN / 4;
-    for (int e = et; e < my_rows * PIECES; e += TC_EPI_WARPS * 32) {
+    const bool vec4 = cl_vec4;
+    constexpr int PIECES = CL_PIECES;
+    int it = 0;
+    for (int e = et; e < my_rows * PIECES; e += TC_EPI_WARPS * 32, ++it) {
       const int lr = e / PIECES, c = (e % PIECES) * 4;
       const int n = n0 + c;
       if (n >= p.N) continue;
       const size_t off = (size_t)(m0 + my_first + lr) * p.N + n;
       float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), r4 = b4;
       if (vec4) {
-        if (p.bias) b4 = __ldg((const float4*)(p.bias + n));
-        if (p.residual) r4 = *(const float4*)(p.residual + off);
+        if (it == 0) {
+          b4 = early_b[0]; r4 = early_r[0];
+        } else if (it == 1) {
+          b4 = early_b[1]; r4 = early_r[1];
+        } else {
+          if (p.bias) b4 = __ldg((const float4*)(p.bias + n));
+          if (p.residual) r4 = *(const float4*)(p.residual + off);
+        }
       } else {
         float* bb = (float*)&b4;
         float* rr = (float*)&r4;
