@@ -43,6 +43,7 @@ class StepError(RuntimeError):
 # the step reads from device memory.  It lets a decode step be launched before the host has
 # read the previous step's tokens.
 FROM_DEVICE = -1
+HOT_SHAPE_USES = 32     # steps of one shape before it gets a second metadata block and graph
 
 
 @dataclass
@@ -274,6 +275,8 @@ class Runner:
         # then idles for a graph launch (about 5 us) instead of 11-15 us (the copy, and the
         # launch behind it).  Every captured graph exists once per block.
         self._parity = 0
+        self.hot_shape_uses = HOT_SHAPE_USES
+        self._shape_uses: dict[tuple, int] = {}   # steps run per shape (a graph's key, less the block)
         self._copy_stream = (torch.cuda.Stream(device=self.device)
                              if self.use_graphs and self.model.capturable else None)
         self._copy_done = [None, None]     # the upload from this pinned block has run
@@ -384,7 +387,14 @@ class Runner:
         else:
             T, R, W = n_tok, len(entries), n_want
         lay = self._layout(T, R, W)
-        parity = self._parity if self._copy_stream is not None else 0
+        # The second block (and the second graph of a shape) is for shapes that keep coming
+        # back, such as a decode batch of a fixed size: capturing a graph costs what a
+        # thousand overlapped uploads save, so a shape earns it with use.
+        shape = (T, R, W, bool(sample))
+        uses = self._shape_uses.get(shape, 0) + 1
+        self._shape_uses[shape] = uses
+        hot = self._copy_stream is not None and uses > self.hot_shape_uses
+        parity = self._parity if hot else 0
         self._parity ^= 1
         host = self._host_buffer(lay.total, parity)
         if self._copy_done[parity] is not None:
@@ -454,7 +464,7 @@ class Runner:
         if fresh:
             dev = torch.zeros(lay.total, dtype=torch.int32, device=self.device)
             self._dev_meta[(T, R, W, parity)] = dev
-        if self._copy_stream is None:
+        if not hot:
             # This copy is also what separates steps on the stream: it is not a kernel, so no
             # kernel of this step, however early programmatic dependent launch lets it start,
             # runs before every kernel of the step before has ended.  The decode attention
@@ -505,12 +515,16 @@ class Runner:
                 # overwrites, and the per-request state of stateful mixers, which the eager run
                 # has already advanced (the state tensors have fixed addresses, so a captured
                 # step reads and writes them like any other)
-                kept = self.feedback.clone()
-                kept_state = {k: st.clone() for k, st in self.storage.states.items()}
-                self._forward(ctx, sample)
-                self.feedback.copy_(kept)
-                for k, st in kept_state.items():
-                    self.storage.states[k].copy_(st)
+                # (the shape's graph over the other metadata block, if there is one, has done
+                # that already)
+                ran_eagerly = self._graphs.get(key[:-1] + (parity ^ 1,)) is None
+                if ran_eagerly:
+                    kept = self.feedback.clone()
+                    kept_state = {k: st.clone() for k, st in self.storage.states.items()}
+                    self._forward(ctx, sample)
+                    self.feedback.copy_(kept)
+                    for k, st in kept_state.items():
+                        self.storage.states[k].copy_(st)
                 torch.cuda.synchronize(self.device)
                 graph = torch.cuda.CUDAGraph()
                 # An object freed by the garbage collector in the middle of a capture (an
@@ -529,7 +543,7 @@ class Runner:
                 n_launch = getattr(self.ops, "launches", 0) - before
                 self._graphs[key] = _Captured(graph, ctx, logits, tokens, n_launch)
                 graph.replay()
-                self.kernel_launches += 2 * n_launch
+                self.kernel_launches += (2 if ran_eagerly else 1) * n_launch
             else:
                 before = getattr(self.ops, "launches", 0)
                 logits, tokens = self._forward(ctx, sample)

@@ -109,6 +109,50 @@ def test_greedy_rows_are_chosen_by_the_head_kernel_itself(lively, graphs):
     rn.check_status()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_shape_that_keeps_coming_back_alternates_between_two_metadata_blocks(lively, dtype):
+    """With CUDA graphs a shape used often enough uploads its metadata on a side stream into
+    one of two device blocks, with a graph for each.  Twenty decode steps of three requests
+    (the threshold lowered to two uses) give the logits and tokens of a runner without
+    graphs, step by step; a prompt in between, and a request that ends, change the shape and
+    come back to it."""
+    from hetero_serve_b200.engine.loading import load_model
+    from hetero_serve_b200.engine.step import Runner, StepEntry
+    d, cfg, _ = lively["tiny_a"]
+    prompts = _prompts(cfg, (9, 20, 5, 12), 31)
+    outs = []
+    for graphs in (False, True):
+        model, _ = load_model(d, dtype, "cuda:0")
+        rn = Runner(model, num_pages=24, page_size=16, max_requests=4, dtype=model.dtype,
+                    device="cuda:0", cuda_graphs=graphs)
+        rn.hot_shape_uses = 2
+        live = ["r0", "r1", "r2"]
+        last = {}
+        for i, r in enumerate(live):
+            res = rn.step([StepEntry(r, prompts[i], want=[len(prompts[i]) - 1])], sample=True)
+            last[r] = res.tokens_host()[0]
+        seen = []
+        for n in range(20):
+            if n == 7:                                   # another shape in between
+                res = rn.step([StepEntry("r3", prompts[3], want=[len(prompts[3]) - 1])], sample=True)
+                last["r3"] = res.tokens_host()[0]
+            if n == 12:
+                rn.close("r1")
+                live = ["r0", "r2", "r3"]
+            res = rn.step([StepEntry(r, [last[r]], want=[0]) for r in live], sample=True)
+            toks = res.tokens_host()
+            seen.append((res.logits.float().cpu().clone(), list(toks)))
+            for r, t in zip(live, toks):
+                last[r] = t
+        if graphs:
+            assert sum(1 for k in rn._graphs if k[-1] == 1) >= 1      # the second block was used
+        rn.check_status()
+        outs.append(seen)
+    for (la, ta), (lb, tb) in zip(*outs):
+        assert ta == tb
+        assert torch.equal(la, lb)
+
+
 def test_temperature_and_top_k_sampling_match_the_plain_sampler(lively):
     d, cfg, w = lively["tiny_b"]
     prompts = _prompts(cfg, (9, 40), 13)
