@@ -340,6 +340,7 @@ class Runner:
         starts = []
         n_tok = n_want = 0
         vocab = self.model.spec.vocab_size
+        token_arrays: list[np.ndarray] = []
         for e in entries:
             if e.req_id in seen:
                 raise StepError(f"request {e.req_id!r} appears twice in one step")
@@ -347,8 +348,10 @@ class Runner:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"request {e.req_id!r} brings no tokens")
-            known = e.tokens[1:] if e.tokens[0] == FROM_DEVICE else e.tokens
-            if len(known) and not (0 <= min(known) and max(known) < vocab):
+            toks = np.asarray(e.tokens, dtype=np.int64)     # once: checked here, packed below
+            token_arrays.append(toks)
+            known = toks[1:] if int(toks[0]) == FROM_DEVICE else toks
+            if known.size and not (0 <= int(known.min()) and int(known.max()) < vocab):
                 raise StepError(f"request {e.req_id!r}: token id outside [0, {vocab})")
             start = mgr.length(e.req_id) if e.req_id in mgr else 0
             if start + n > self.max_positions:
@@ -421,7 +424,7 @@ class Runner:
         t = w_i = 0
         for r, (e, start) in enumerate(zip(entries, starts)):
             n = len(e.tokens)
-            toks = np.asarray(e.tokens, dtype=np.int64)
+            toks = token_arrays[r]
             slot = mgr.slot(e.req_id)
             from_device = int(toks[0]) == FROM_DEVICE
             hm[lay.tok_ids + t:lay.tok_ids + t + n] = toks
