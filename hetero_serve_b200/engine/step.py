@@ -69,6 +69,7 @@ class StepResult:
     _runner: "Runner | None" = None
     _host: torch.Tensor | None = None
     _copied: "torch.cuda.Event | None" = None
+    _block: int | None = None            # the metadata block of a step whose copies use side streams
 
     def start_fetch(self) -> None:
         """Enqueue the device-to-host copy of the sampled tokens (and the status word) behind
@@ -76,7 +77,7 @@ class StepResult:
         device buffer is reused."""
         if self._with_status is None or self._host is not None:
             return
-        self._host, self._copied = self._runner._fetch(self._with_status)
+        self._host, self._copied = self._runner._fetch(self._with_status, self._block)
 
     def tokens_host(self) -> list[int]:
         """The sampled tokens as Python ints: one device-to-host copy that also brings the
@@ -166,6 +167,7 @@ class StepContext:
         self.fused_tokens = None   # greedy tokens a fused step left (with the status word)
         self.greedy_only = False   # no wanted row of this step samples with a temperature
         self.sampling = False      # the step chooses tokens (a head may then choose them itself)
+        self.tokens_name = "sampled"   # the workspace buffer the step's tokens go to
         self.plan = None          # work lists for the specialised attention kernels, if any
         self.position = None      # the model's position encoding (set by Model.forward)
         self.call_index: int | None = None
@@ -281,6 +283,12 @@ class Runner:
                              if self.use_graphs and self.model.capturable else None)
         self._copy_done = [None, None]     # the upload from this pinned block has run
         self._block_free = [None, None]    # the last step that read this device block has ended
+        # the sampled tokens of such a step come back on a side stream too (a copy between two
+        # graphs on the step's stream kept the GPU idle for 9-19 us); each block has a tokens
+        # buffer of its own, free again once its last fetch has run
+        self._fetch_stream = (torch.cuda.Stream(device=self.device)
+                              if self._copy_stream is not None else None)
+        self._tokens_free = [None, None]
         self.steps_run = 0
         self.kernel_launches = 0      # kernels of this package launched by steps so far
 
@@ -498,6 +506,9 @@ class Runner:
                     self._copy_done[parity].record(side)
                 main.wait_event(self._copy_done[parity])
 
+        if self._fetch_stream is not None and self._tokens_free[parity] is not None:
+            # the last fetch from the tokens buffer this step writes has run
+            torch.cuda.current_stream(self.device).wait_event(self._tokens_free[parity])
         cap = self._graphs.get(key) if self.use_graphs else None
         if cap is not None:
             cap.ctx.host = host_batch
@@ -508,6 +519,7 @@ class Runner:
             ctx = StepContext(self, lay, dev)
             ctx.host = host_batch
             ctx.greedy_only = greedy
+            ctx.tokens_name = "sampled" if parity == 0 else "sampled_b"
             if plan_shape is not None:
                 from ..kernels.ops import AttentionPlan
                 ctx.plan = AttentionPlan(dev[lay.plan:lay.plan + lay.plan_ints], T, *plan_shape)
@@ -565,7 +577,8 @@ class Runner:
             logits=None if logits is None else logits[:n_want],
             tokens=None if tokens is None else tokens[:n_want],
             rows=rows, n_tokens=n_tok,
-            _with_status=None if tokens is None else tokens, _runner=self)
+            _with_status=None if tokens is None else tokens, _runner=self,
+            _block=parity if hot else None)
 
     def _forward(self, ctx: StepContext, sample: bool):
         ctx.fused_tokens = None
@@ -575,7 +588,7 @@ class Runner:
         if sample and logits is not None:
             # one extra element carries the status word, so that one copy brings both back
             W = ctx.n_logit_rows
-            tokens = ctx.buffer("sampled", (W + 1,), torch.int32)
+            tokens = ctx.buffer(ctx.tokens_name, (W + 1,), torch.int32)
             if ctx.fused_tokens is not None and ctx.greedy_only:
                 # the step ran as one kernel, which also chose the tokens (argmax, lowest
                 # index on ties), kept them for the requests and stored the status word
@@ -590,10 +603,12 @@ class Runner:
                 tokens[W:].copy_(self.status)
         return logits, tokens
 
-    def _fetch(self, dev: torch.Tensor):
+    def _fetch(self, dev: torch.Tensor, block: int | None = None):
         """Start copying ``dev`` (int32) to pinned host memory behind the work enqueued so far;
         returns (host tensor, event).  Four buffers rotate: a result is to be read before four
-        later ones have been fetched."""
+        later ones have been fetched.  ``block``: the step ran over that metadata block with
+        its copies on side streams; the fetch then leaves the step's stream free for the next
+        graph."""
         n = dev.shape[0]
         if not self.cuda:
             return dev.clone(), None
@@ -604,9 +619,19 @@ class Runner:
         if self._fetch_ring[i].shape[0] < n:
             self._fetch_ring[i] = torch.empty(_bucket(n, 1024), dtype=torch.int32).pin_memory()
         host = self._fetch_ring[i][:n]
-        host.copy_(dev, non_blocking=True)
         ev = torch.cuda.Event()
-        ev.record()
+        if block is None or self._fetch_stream is None:
+            host.copy_(dev, non_blocking=True)
+            ev.record()
+        else:
+            done = torch.cuda.Event()
+            done.record()                                  # the step's work, on its own stream
+            side = self._fetch_stream
+            side.wait_event(done)
+            with torch.cuda.stream(side):
+                host.copy_(dev, non_blocking=True)
+                ev.record(side)
+            self._tokens_free[block] = ev
         return host, ev
 
     def check_status(self) -> None:

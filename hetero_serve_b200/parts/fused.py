@@ -43,7 +43,7 @@ class FusedDecodePlan:
         att = ctx.buffer("attn_out", (T, z["width"]), torch.bfloat16)
         u = ctx.buffer("ff_inner", (T, z["inner"]), torch.bfloat16)
         logits = ctx.buffer("logits", (W, z["vocab"]), torch.float32) if W else None
-        tokens = ctx.buffer("sampled", (W + 1,), torch.int32)
+        tokens = ctx.buffer(getattr(ctx, "tokens_name", "sampled"), (W + 1,), torch.int32)
         rn = ctx.runner
         pool = rn.storage.pools[0]
         self.ops.fused_decode(

@@ -241,7 +241,7 @@ class LinearHead(Head):
         fused = getattr(ctx.ops, "linear_argmax", None)
         if fused is not None and getattr(ctx, "sampling", False) \
                 and getattr(ctx, "greedy_only", False):
-            tokens = ctx.buffer("sampled", (logits.shape[0] + 1,), torch.int32)
+            tokens = ctx.buffer(getattr(ctx, "tokens_name", "sampled"), (logits.shape[0] + 1,), torch.int32)
             if fused(logits, h, self.weight, tokens, feedback=ctx.feedback,
                      feedback_slot=ctx.samp_slot, status_word=ctx.status):
                 ctx.fused_tokens = tokens
