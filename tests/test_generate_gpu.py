@@ -250,10 +250,14 @@ def test_pipelined_steps_change_no_token(lively, dtype, policy):
         shutil.copy(d + "/model.safetensors", t)
         pathlib.Path(t, "config.json").write_text(json.dumps(cfg2))
         outs = {}
-        for pipeline in (False, True):
+        for pipeline in (False, True, "side streams"):
             eng = LLMEngine(t, EngineConfig(dtype=dtype, num_blocks=10, max_batch=4,
                                             max_prefill_tokens=32, prefix_cache=False,
-                                            policy=policy, pipeline=pipeline))
+                                            policy=policy, pipeline=bool(pipeline)))
+            if pipeline == "side streams":
+                # every shape at once takes the route of shapes that keep coming back: metadata
+                # up and tokens down on side streams, two blocks, two graphs
+                eng.runner.hot_shape_uses = 0
             seqs = [eng.submit_nowait(Request(p, max_new_tokens=30, temperature=0.9 * (i % 2),
                                               top_k=12 * (i % 2), seed=3 + i,
                                               stop_at_eos=(i != 1)))
@@ -264,6 +268,7 @@ def test_pipelined_steps_change_no_token(lively, dtype, policy):
             eng.runner.manager.check()
             assert eng.runner.manager.free_slots() == eng.config.live_requests
         assert outs[True] == outs[False]
+        assert outs["side streams"] == outs[False]
         if dtype == "float32":
             assert outs[True][0] == (free[:k + 1], "eos")
         assert any(r == "max_new_tokens" for _, r in outs[True])
