@@ -143,8 +143,11 @@ def decode_windows(prompt_len: int, context: int, steps: int, n_windows: int = N
     """Cut the decode trajectory prompt_len -> context into windows and place the timed steps
     in the middle of each: ``[(first, k, repeats)]`` where the first timed step of a window
     attends over ``first`` keys, ``k`` steps make one repeat, and up to three repeats follow
-    one another while they fit the window.  The k of all windows add up to ``steps``."""
-    n = max(1, min(n_windows, steps))
+    one another while they fit the window.  The k of all windows add up to ``steps``.  A
+    timed repeat starts behind a synchronisation, i.e. from an idle GPU, so it is kept at 16
+    steps or more: few steps make fewer windows (one, around the trajectory's middle, below 32
+    steps), and the mean context of the timed steps stays that of the whole trajectory."""
+    n = max(1, min(n_windows, steps // 16, steps))
     per = (context - prompt_len) // n
     out = []
     for i in range(n):
