@@ -563,7 +563,8 @@ def test_head_with_the_greedy_choice_refuses_what_it_does_not_take(ops):
 
 
 @pytest.mark.parametrize("vocab,top_k", [(1000, 0), (1000, 1), (1000, 40), (50257, 0),
-                                         (50257, 50), (37, 36), (37, 100)])
+                                         (50257, 50), (37, 36), (37, 100), (50257, 50256),
+                                         (1025, 7), (60001, 0), (60001, 300)])   # 60001: too long for shared memory
 def test_sample_matches_the_plain_sampler(ops, plain, vocab, top_k):
     torch.manual_seed(vocab + top_k)
     rows = 8
