@@ -271,11 +271,11 @@ class Runner:
         self._host_meta: dict[tuple[int, int], torch.Tensor] = {}
         self._dev_meta: dict[tuple, torch.Tensor] = {}
         self._layouts: dict[tuple, Layout] = {}
-        # With CUDA graphs the metadata of a step is uploaded on a side stream into one of two
-        # device blocks (and from one of two pinned blocks) that alternate from step to step, so
-        # that the upload of step i + 1 runs while step i computes: between two graphs the GPU
-        # then idles for a graph launch (about 5 us) instead of 11-15 us (the copy, and the
-        # launch behind it).  Every captured graph exists once per block.
+        # With CUDA graphs, the metadata of a step whose shape keeps coming back is uploaded on
+        # a side stream into one of two device blocks (from one of two pinned blocks) that
+        # alternate from step to step, so that the upload of step i + 1 runs while step i
+        # computes: between two graphs the GPU then idles 2-3 us instead of 11-15 us (the copy,
+        # and the launch behind it).  Such a shape has a captured graph per block.
         self._parity = 0
         self.hot_shape_uses = HOT_SHAPE_USES
         self._shape_uses: dict[tuple, int] = {}   # steps run per shape (a graph's key, less the block)
