@@ -605,7 +605,8 @@ def run_one_step(args):
             ids = [f"r{i}" for i in range(args.batch)]
             for r in ids:
                 runner.step([StepEntry(r, torch.randint(0, vocab, (args.prompt_len,), generator=g).tolist())])
-            entries = [StepEntry(r, [5], want=[0]) for r in ids]
+            entries = [StepEntry(r, [5], want=[0], temperature=args.temperature, top_k=args.top_k,
+                                 seed=i) for i, r in enumerate(ids)]
             for _ in range(3):
                 runner.step(entries, sample=True)
             torch.cuda.synchronize()
@@ -754,6 +755,10 @@ def main() -> int:
                     help="context length of the decode attention in the --kernels table")
     ap.add_argument("--kernels", action="store_true",
                     help="print the per-kernel table (one JSON object a kernel) and exit")
+    ap.add_argument("--temperature", type=float, default=0.0,
+                    help="with --one-step decode: sample with this temperature (0: greedy)")
+    ap.add_argument("--top-k", dest="top_k", type=int, default=0,
+                    help="with --one-step decode: restrict sampling to the k largest")
     ap.add_argument("--one-step", dest="one_step", default="", choices=["", "decode", "prefill"],
                     help="for profilers: run a single eager step between cudaProfilerStart/Stop")
     args = ap.parse_args()
