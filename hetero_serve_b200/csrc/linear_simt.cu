@@ -77,6 +77,113 @@ linear_simt_kernel(TO* out, const TI* __restrict__ a, const TI* __restrict__ w,
   }
 }
 
+// ---- many rows (prompts): 128 x 128 tiles, an 8 x 8 patch of outputs per thread ---------------
+// The same chains again (every output one fmaf chain over k = 0..K-1 in index order), with
+// twice the outputs per shared-memory word read: a thread's 64 outputs take 16 words per k.
+// Tiles of both operands arrive k-major ([k][row]) through registers, two buffers.
+constexpr int LB_BM = 128, LB_BN = 128, LB_BK = 8, LB_THREADS = 256;
+
+// four consecutive elements of a row in one load (the rows are 16-byte / 8-byte aligned there)
+__device__ __forceinline__ void lb_load4(const float* p, float (&v)[4]) {
+  const float4 x = *(const float4*)p;
+  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+__device__ __forceinline__ void lb_load4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 x = *(const uint2*)p;
+  v[0] = __uint_as_float(x.x << 16); v[1] = __uint_as_float(x.x & 0xffff0000u);
+  v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
+}
+
+// VEC: K is a multiple of 4 and both matrices start on a 16-byte boundary, so a thread's four
+// k of a row come in one load (with one 4-byte load per element the load pipe, 16 sectors an
+// instruction, took as long as the products).
+template <typename TI, typename TO, bool VEC>
+__global__ void __launch_bounds__(LB_THREADS)
+linear_simt_big_kernel(TO* out, const TI* __restrict__ a, const TI* __restrict__ w,
+                       const float* __restrict__ bias, const float* residual, int M, int N, int K,
+                       int act) {
+  __shared__ __align__(16) float As[2][LB_BK][LB_BM];
+  __shared__ __align__(16) float Ws[2][LB_BK][LB_BN];
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;                 // 16 x 16 threads, 8 x 8 outputs each
+  const int m0 = blockIdx.y * LB_BM, n0 = blockIdx.x * LB_BN;
+  // loader: thread -> (row 0..127, 4 consecutive k of the 8)
+  const int lr = tid >> 1, lk = (tid & 1) * 4;
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  float ra[4], rw[4];
+  auto fetch = [&](int k0) {
+    const int gm = m0 + lr, gn = n0 + lr;
+    if (VEC) {
+      const int gk = k0 + lk;                             // K % 4 == 0: all four or none
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ra[j] = rw[j] = 0.f;
+      if (gm < M && gk < K) lb_load4(a + (size_t)gm * K + gk, ra);
+      if (gn < N && gk < K) lb_load4(w + (size_t)gn * K + gk, rw);
+      return;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gk = k0 + lk + j;
+      ra[j] = (gm < M && gk < K) ? to_f(a[(size_t)gm * K + gk]) : 0.f;
+      rw[j] = (gn < N && gk < K) ? to_f(w[(size_t)gn * K + gk]) : 0.f;
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      As[buf][lk + j][lr] = ra[j];
+      Ws[buf][lk + j][lr] = rw[j];
+    }
+  };
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = 0; k0 < K; k0 += LB_BK) {
+    const bool more = k0 + LB_BK < K;
+    if (more) fetch(k0 + LB_BK);                          // in flight during the products below
+#pragma unroll
+    for (int kk = 0; kk < LB_BK; ++kk) {
+      // rows ty*4..+3 and 64+ty*4..+3, columns tx*4..+3 and 64+tx*4..+3: 16-byte reads, no
+      // bank conflicts
+      const float4 a0 = *(const float4*)&As[buf][kk][ty * 4];
+      const float4 a1 = *(const float4*)&As[buf][kk][64 + ty * 4];
+      const float4 w0 = *(const float4*)&Ws[buf][kk][tx * 4];
+      const float4 w1 = *(const float4*)&Ws[buf][kk][64 + tx * 4];
+      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+    }
+    if (more) {
+      stash(buf ^ 1);
+      __syncthreads();
+      buf ^= 1;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int gn = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
+      if (gn >= N) continue;
+      float v = acc[i][j];
+      if (bias) v += bias[gn];
+      v = apply_act(v, act);
+      if (residual) v += residual[(size_t)gm * N + gn];
+      out[(size_t)gm * N + gn] = from_f<TO>(v);
+    }
+  }
+}
+
 // ---- few rows (decode): the same chains, laid out for a weight stream -------------------------
 // With M <= 16 the tile kernel above leaves most of the machine idle (N / 64 CTAs, each walking
 // all of K behind two barriers per 16 columns).  Here a CTA owns 16 output features and all
@@ -220,6 +327,27 @@ HS_EXPORT int hs_linear_simt(void* out, const void* a, const void* w, const floa
     else if (in_dtype == HS_DT_BF16 && out_dtype == HS_DT_F32)
       rc = hs::launch_few_rows<bf16, float>(out, a, w, bias, residual, M, N, K, act, st);
     if (rc != HS_OK) return rc;
+    HS_LAUNCH_CHECK();
+    return HS_OK;
+  }
+  if (M >= 256) {                    // prompts: the larger tile
+    dim3 big((N + hs::LB_BN - 1) / hs::LB_BN, (M + hs::LB_BM - 1) / hs::LB_BM);
+    if (big.y > 65535) return HS_ERR_UNSUPPORTED;
+    const bool vec4 = K % 4 == 0 && !((uintptr_t)a & 15) && !((uintptr_t)w & 15);
+#define HS_LB_LAUNCH(TI, TO)                                                                   \
+  do {                                                                                         \
+    if (vec4)                                                                                  \
+      hs::linear_simt_big_kernel<TI, TO, true><<<big, hs::LB_THREADS, 0, st>>>(                \
+          (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act);                 \
+    else                                                                                       \
+      hs::linear_simt_big_kernel<TI, TO, false><<<big, hs::LB_THREADS, 0, st>>>(               \
+          (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act);                 \
+  } while (0)
+    if (in_dtype == HS_DT_F32 && out_dtype == HS_DT_F32) HS_LB_LAUNCH(float, float);
+    else if (in_dtype == HS_DT_BF16 && out_dtype == HS_DT_BF16) HS_LB_LAUNCH(bf16, bf16);
+    else if (in_dtype == HS_DT_BF16 && out_dtype == HS_DT_F32) HS_LB_LAUNCH(bf16, float);
+    else return HS_ERR_UNSUPPORTED;
+#undef HS_LB_LAUNCH
     HS_LAUNCH_CHECK();
     return HS_OK;
   }
