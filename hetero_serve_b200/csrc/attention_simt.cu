@@ -110,157 +110,271 @@ constexpr int AS_STREAMS = 4;         // warps per CTA; chunk c of a token belon
 // d = 0..D-1, the chunk joins the stream's running softmax, and lane d accumulates the values
 // of dimension d, d+32, ... key by key.  `both` false (large heads): keys and values take
 // turns in one buffer.
-template <typename T>
+//
+// G > 1 (prompt portions): a CTA serves G tokens.  When they are consecutive positions of one
+// request (and there is no window) a staged chunk serves all of them, each with its own mask,
+// running softmax and accumulators - the arithmetic of a token is the same as alone, so its
+// result does not depend on its company; otherwise the CTA takes its tokens one after the other.
+template <typename T, int G>
 __global__ void __launch_bounds__(AS_STREAMS * 32)
 attention_simt_kernel(T* __restrict__ out, const T* __restrict__ qkv, const T* __restrict__ pool,
                       const int* __restrict__ table, const int* __restrict__ tok_pos,
-                      const int* __restrict__ tok_req, AttnGeom g, float scale, int both,
-                      int* status) {
+                      const int* __restrict__ tok_req, int n_tokens, AttnGeom g, float scale,
+                      int both, int* status) {
   extern __shared__ __align__(16) uint8_t as_smem[];
   constexpr int VEC = 16 / (int)sizeof(T);             // elements per 16-byte piece
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x, h = blockIdx.y;
+  const int h = blockIdx.y;
   const int D = g.head_dim;
   const int pieces = D / VEC;                          // 16-byte pieces per row: 2 .. 64
   // pieces are permuted inside groups of 8, or of the largest power of two that divides a row
   int swz = 8;
   while (pieces % swz) swz >>= 1;
   swz -= 1;
-  // this warp's shared memory: q as float [D] | keys [32][D] T | values [32][D] T (if `both`)
+  // this warp's shared memory: G queries as float [G][D] | keys [32][D] T | values (if `both`)
   const size_t rows_bytes = (size_t)AS_CHUNK * D * sizeof(T);
-  const size_t per_warp = (size_t)D * sizeof(float) + (both ? 2 : 1) * rows_bytes;
+  const size_t q_bytes = (size_t)G * D * sizeof(float);
+  const size_t per_warp = q_bytes + (both ? 2 : 1) * rows_bytes;
   uint8_t* base = as_smem + (size_t)warp * per_warp;
   float* sq = (float*)base;
-  T* sk = (T*)(base + (size_t)D * sizeof(float));
+  T* sk = (T*)(base + q_bytes);
   T* sv = both ? sk + (size_t)AS_CHUNK * D : sk;
-  T* orow = out + (size_t)t * g.n_heads * D + (size_t)h * D;
-  const int r = tok_req[t];
-  const int p = tok_pos[t];
-  if (r < 0 || p < 0 || p / g.page_size >= g.max_pages) {   // the same for the whole CTA
-    for (int d = threadIdx.x; d < D; d += blockDim.x) orow[d] = from_f<T>(0.f);
-    return;
-  }
   const int hk = h / (g.n_heads / g.n_kv_heads);
-  const T* qrow = qkv + (size_t)t * g.qkv_stride + g.q_off + (size_t)h * D;
-  for (int d = lane; d < D; d += 32) sq[d] = to_f(qrow[d]);
-
   const size_t tile = (size_t)g.page_size * D;
   const size_t page_stride = 2 * (size_t)g.n_kv_heads * tile;
   const long long v_off = (long long)g.n_kv_heads * (long long)tile;
-  const int* trow = table + (size_t)r * g.max_pages;
-  const int lo = (g.window > 0 && p - g.window + 1 > 0) ? p - g.window + 1 : 0;
   // piece i = lane + 32 * trip of a chunk: key i / pieces, piece i % pieces of its row
   const int key0 = lane / pieces, pc0 = lane - key0 * pieces;
   const int dkey = 32 / pieces, dpc = 32 - dkey * pieces;
 
-  float m = -INFINITY, l = 0.f;
-  float acc[AS_MAX_D / 32];
-#pragma unroll
-  for (int i = 0; i < AS_MAX_D / 32; ++i) acc[i] = 0.f;
+  // the CTA's tokens: one run of consecutive positions of a request, or one by one
+  const int t_first = blockIdx.x * G;
+  const int n_here = min(G, n_tokens - t_first);
+  bool run = G > 1 && n_here > 1 && g.window == 0;
+  if (run) {
+    const int r0 = tok_req[t_first], p0 = tok_pos[t_first];
+    run = r0 >= 0 && p0 >= 0;
+    for (int i = 1; i < n_here && run; ++i)
+      run = tok_req[t_first + i] == r0 && tok_pos[t_first + i] == p0 + i;
+  }
+  const int n_groups = run ? 1 : n_here;                // groups of n_q tokens each
+  const int n_q = run ? n_here : 1;
 
-  for (int j0 = lo + warp * AS_CHUNK; j0 <= p; j0 += AS_STREAMS * AS_CHUNK) {
-    const int j = j0 + lane;
-    long long koff = -1;                               // this lane's key row in the pool
-    if (j <= p) {
-      const int page = trow[j / g.page_size];
-      if (page < 0 || page >= g.num_pages)
-        atomicOr(status, HS_STATUS_BAD_PAGE);
-      else
-        koff = (long long)((size_t)page * page_stride + (size_t)hk * tile +
-                           (size_t)(j % g.page_size) * D);
-    }
-    const int cnt = (p - j0 + 1) < AS_CHUNK ? (p - j0 + 1) : AS_CHUNK;
-    const unsigned live = __ballot_sync(0xffffffffu, koff >= 0);
-    __syncwarp();                                      // the step before is done with sk / sv
-    auto stage = [&](T* dst_rows, long long extra) {
-      int key = key0, pc = pc0;
-      for (int i0 = 0; i0 < cnt * pieces; i0 += 32) {  // the same trips for every lane
-        const long long ko = __shfl_sync(0xffffffffu, koff, key & 31);
-        if (key < cnt && ko >= 0)
-          as_copy16(dst_rows + key * D + ((pc & ~swz) | ((pc ^ key) & swz)) * VEC,
-                    pool + ko + extra + pc * VEC);
-        key += dkey;
-        pc += dpc;
-        if (pc >= pieces) { pc -= pieces; ++key; }
+  for (int grp = 0; grp < n_groups; ++grp) {
+    const int t0 = t_first + grp * n_q;
+    const int r = tok_req[t0];
+    const int p0 = tok_pos[t0];
+    const int p_last = p0 + n_q - 1;
+    if (grp > 0) __syncthreads();                      // the group before is done with shared memory
+    if (r < 0 || p0 < 0 || p_last / g.page_size >= g.max_pages) {   // the same for the whole CTA
+      for (int i = 0; i < n_q; ++i) {
+        T* orow = out + (size_t)(t0 + i) * g.n_heads * D + (size_t)h * D;
+        for (int d = threadIdx.x; d < D; d += blockDim.x) orow[d] = from_f<T>(0.f);
       }
-    };
-    stage(sk, 0);
-    if (both) stage(sv, v_off);
-    as_copies_done();
-    __syncwarp();
-    float s = -INFINITY;
-    if (koff >= 0) {
-      float dot = 0.f;
-      const uint4* krow = (const uint4*)(sk + (size_t)lane * D);
-      for (int pc = 0; pc < pieces; ++pc)
-        dot = as_dot_piece(sq + pc * VEC, krow[(pc & ~swz) | ((pc ^ lane) & swz)], dot, T());
-      s = dot * scale;
+      continue;
     }
-    if (!both) {                                       // the values take the keys' place
-      __syncwarp();
-      stage(sv, v_off);
+    for (int i = 0; i < n_q; ++i) {
+      const T* qrow = qkv + (size_t)(t0 + i) * g.qkv_stride + g.q_off + (size_t)h * D;
+      for (int d = lane; d < D; d += 32) sq[i * D + d] = to_f(qrow[d]);
+    }
+    const int* trow = table + (size_t)r * g.max_pages;
+    const int lo = (g.window > 0 && p0 - g.window + 1 > 0) ? p0 - g.window + 1 : 0;   // n_q == 1
+
+    float m[G], l[G];
+    float acc[G][AS_MAX_D / 32];
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+      m[i] = -INFINITY;
+      l[i] = 0.f;
+#pragma unroll
+      for (int c = 0; c < AS_MAX_D / 32; ++c) acc[i][c] = 0.f;
+    }
+
+    for (int j0 = lo + warp * AS_CHUNK; j0 <= p_last; j0 += AS_STREAMS * AS_CHUNK) {
+      const int j = j0 + lane;
+      long long koff = -1;                               // this lane's key row in the pool
+      if (j <= p_last) {
+        const int page = trow[j / g.page_size];
+        if (page < 0 || page >= g.num_pages)
+          atomicOr(status, HS_STATUS_BAD_PAGE);
+        else
+          koff = (long long)((size_t)page * page_stride + (size_t)hk * tile +
+                             (size_t)(j % g.page_size) * D);
+      }
+      const int cnt = (p_last - j0 + 1) < AS_CHUNK ? (p_last - j0 + 1) : AS_CHUNK;
+      const unsigned live = __ballot_sync(0xffffffffu, koff >= 0);
+      __syncwarp();                                      // the step before is done with sk / sv
+      auto stage = [&](T* dst_rows, long long extra) {
+        int key = key0, pc = pc0;
+        for (int i0 = 0; i0 < cnt * pieces; i0 += 32) {  // the same trips for every lane
+          const long long ko = __shfl_sync(0xffffffffu, koff, key & 31);
+          if (key < cnt && ko >= 0)
+            as_copy16(dst_rows + key * D + ((pc & ~swz) | ((pc ^ key) & swz)) * VEC,
+                      pool + ko + extra + pc * VEC);
+          key += dkey;
+          pc += dpc;
+          if (pc >= pieces) { pc -= pieces; ++key; }
+        }
+      };
+      stage(sk, 0);
+      if (both) stage(sv, v_off);
       as_copies_done();
       __syncwarp();
-    }
-    const float cm = warp_max(s);
-    const float m_new = fmaxf(m, cm);
-    // a chunk whose pages were all refused leaves m_new at -inf: skip it
-    if (m_new == -INFINITY) continue;
-    const float pj = (s == -INFINITY) ? 0.f : expf(s - m_new);
-    const float corr = expf(m - m_new);
-    l = l * corr + warp_sum(pj);
+      if constexpr (G == 1) {
+        // one query: score, running softmax, values (the loops of the grouped form below cost
+        // a lone query half as much again)
+        float s1 = -INFINITY;
+        if (koff >= 0) {
+          float dot = 0.f;
+          const uint4* krow = (const uint4*)(sk + (size_t)lane * D);
+          for (int pc = 0; pc < pieces; ++pc)
+            dot = as_dot_piece(sq + pc * VEC, krow[(pc & ~swz) | ((pc ^ lane) & swz)], dot, T());
+          s1 = dot * scale;
+        }
+        if (!both) {                                     // the values take the keys' place
+          __syncwarp();
+          stage(sv, v_off);
+          as_copies_done();
+          __syncwarp();
+        }
+        const float cm = warp_max(s1);
+        const float m_new = fmaxf(m[0], cm);
+        // a chunk whose pages were all refused leaves m_new at -inf: skip it
+        if (m_new == -INFINITY) continue;
+        const float pj1 = (s1 == -INFINITY) ? 0.f : expf(s1 - m_new);
+        const float corr = expf(m[0] - m_new);
+        l[0] = l[0] * corr + warp_sum(pj1);
 #pragma unroll
-    for (int i = 0; i < AS_MAX_D / 32; ++i) acc[i] *= corr;
-    for (int jj = 0; jj < cnt; ++jj) {
-      const float pv = __shfl_sync(0xffffffffu, pj, jj);
-      if (!((live >> jj) & 1u)) continue;
-      const T* vrow = sv + (size_t)jj * D;
+        for (int c = 0; c < AS_MAX_D / 32; ++c) acc[0][c] *= corr;
+        for (int jj = 0; jj < cnt; ++jj) {
+          const float pv = __shfl_sync(0xffffffffu, pj1, jj);
+          if (!((live >> jj) & 1u)) continue;
+          const T* vrow = sv + (size_t)jj * D;
 #pragma unroll
-      for (int i = 0; i < AS_MAX_D / 32; ++i) {
-        const int d = lane + 32 * i;
-        if (d < D) {
-          const int pc = d / VEC;
-          acc[i] = fmaf(pv, to_f(vrow[((pc & ~swz) | ((pc ^ jj) & swz)) * VEC + (d - pc * VEC)]),
-                        acc[i]);
+          for (int c = 0; c < AS_MAX_D / 32; ++c) {
+            const int d = lane + 32 * c;
+            if (d < D) {
+              const int pc = d / VEC;
+              acc[0][c] = fmaf(pv, to_f(vrow[((pc & ~swz) | ((pc ^ jj) & swz)) * VEC + (d - pc * VEC)]),
+                               acc[0][c]);
+            }
+          }
+        }
+        m[0] = m_new;
+      } else {
+      // scores of the chunk's key `lane` for every query of the group: the queries' chains of
+      // fused multiply-adds run side by side on one read of the key's pieces
+      float s[G];
+      bool sees[G];
+#pragma unroll
+      for (int i = 0; i < G; ++i) {
+        sees[i] = i < n_q && koff >= 0 && j <= p0 + i;     // key j is visible to query i
+        s[i] = 0.f;
+      }
+      if (koff >= 0) {
+        const uint4* krow = (const uint4*)(sk + (size_t)lane * D);
+        for (int pc = 0; pc < pieces; ++pc) {
+          const uint4 kp = krow[(pc & ~swz) | ((pc ^ lane) & swz)];
+#pragma unroll
+          for (int i = 0; i < G; ++i)
+            if (i < n_q) s[i] = as_dot_piece(sq + i * D + pc * VEC, kp, s[i], T());
         }
       }
+#pragma unroll
+      for (int i = 0; i < G; ++i) s[i] = sees[i] ? s[i] * scale : -INFINITY;
+      if (!both) {                                       // the values take the keys' place
+        __syncwarp();
+        stage(sv, v_off);
+        as_copies_done();
+        __syncwarp();
+      }
+      // each query's running softmax takes the chunk in; then the values, read once per key,
+      // go into every query that sees the key
+      float pj[G];
+      int cnt_q[G];
+#pragma unroll
+      for (int i = 0; i < G; ++i) {
+        pj[i] = 0.f;
+        cnt_q[i] = 0;
+        if (i >= n_q || j0 > p0 + i) continue;           // (the same for the whole warp)
+        const float cm = warp_max(s[i]);
+        const float m_new = fmaxf(m[i], cm);
+        // a chunk whose pages were all refused leaves m_new at -inf: skip it
+        if (m_new == -INFINITY) continue;
+        pj[i] = (s[i] == -INFINITY) ? 0.f : expf(s[i] - m_new);
+        const float corr = expf(m[i] - m_new);
+        l[i] = l[i] * corr + warp_sum(pj[i]);
+#pragma unroll
+        for (int c = 0; c < AS_MAX_D / 32; ++c) acc[i][c] *= corr;
+        cnt_q[i] = (p0 + i - j0 + 1) < AS_CHUNK ? (p0 + i - j0 + 1) : AS_CHUNK;
+        m[i] = m_new;
+      }
+      for (int jj = 0; jj < cnt; ++jj) {
+        float pv[G];
+#pragma unroll
+        for (int i = 0; i < G; ++i) pv[i] = __shfl_sync(0xffffffffu, pj[i], jj);
+        if (!((live >> jj) & 1u)) continue;
+        const T* vrow = sv + (size_t)jj * D;
+#pragma unroll
+        for (int c = 0; c < AS_MAX_D / 32; ++c) {
+          const int d = lane + 32 * c;
+          if (d < D) {
+            const int pc = d / VEC;
+            const float v = to_f(vrow[((pc & ~swz) | ((pc ^ jj) & swz)) * VEC + (d - pc * VEC)]);
+#pragma unroll
+            for (int i = 0; i < G; ++i)
+              if (jj < cnt_q[i]) acc[i][c] = fmaf(pv[i], v, acc[i][c]);
+          }
+        }
+      }
+      }
     }
-    m = m_new;
-  }
 
-  // fold the streams in stream order: each warp leaves (m, l, acc) in its own shared memory
-  __syncwarp();
-  float* st = (float*)(base + (size_t)D * sizeof(float));   // the key rows' place: >= 2 + D floats
-  if (lane == 0) { st[0] = m; st[1] = l; }
+    // fold the streams in stream order: each warp leaves (m, l, acc) of every query in its own
+    // shared memory (the key rows' place: 32 rows of D against G x (2 + D) floats)
+    __syncwarp();
+    float* st = (float*)(base + q_bytes);
 #pragma unroll
-  for (int i = 0; i < AS_MAX_D / 32; ++i) {
-    const int d = lane + 32 * i;
-    if (d < D) st[2 + d] = acc[i];
-  }
-  __syncthreads();
-  if (warp != 0) return;
-  float M = -INFINITY, L = 0.f;
+    for (int i = 0; i < G; ++i) {
+      if (i >= n_q) continue;
+      float* sti = st + (size_t)i * (2 + D);
+      if (lane == 0) { sti[0] = m[i]; sti[1] = l[i]; }
 #pragma unroll
-  for (int i = 0; i < AS_MAX_D / 32; ++i) acc[i] = 0.f;
-  for (int sidx = 0; sidx < AS_STREAMS; ++sidx) {
-    const float* ss = (const float*)(as_smem + (size_t)sidx * per_warp + (size_t)D * sizeof(float));
-    const float ms = ss[0];
-    if (ms == -INFINITY) continue;                     // a stream without keys
-    const float m_new = fmaxf(M, ms);
-    const float c0 = expf(M - m_new), c1 = expf(ms - m_new);
-    L = L * c0 + ss[1] * c1;
-#pragma unroll
-    for (int i = 0; i < AS_MAX_D / 32; ++i) {
-      const int d = lane + 32 * i;
-      if (d < D) acc[i] = fmaf(ss[2 + d], c1, acc[i] * c0);
+      for (int c = 0; c < AS_MAX_D / 32; ++c) {
+        const int d = lane + 32 * c;
+        if (d < D) sti[2 + d] = acc[i][c];
+      }
     }
-    M = m_new;
-  }
-  const float inv = L > 0.f ? 1.0f / L : 0.f;
+    __syncthreads();
+    // warp w folds query w, w + 4, ...
+    for (int i = warp; i < n_q; i += AS_STREAMS) {
+      float M = -INFINITY, L = 0.f;
+      float o[AS_MAX_D / 32];
 #pragma unroll
-  for (int i = 0; i < AS_MAX_D / 32; ++i) {
-    const int d = lane + 32 * i;
-    if (d < D) orow[d] = from_f<T>(acc[i] * inv);
+      for (int c = 0; c < AS_MAX_D / 32; ++c) o[c] = 0.f;
+      for (int sidx = 0; sidx < AS_STREAMS; ++sidx) {
+        const float* ss = (const float*)(as_smem + (size_t)sidx * per_warp + q_bytes) +
+                          (size_t)i * (2 + D);
+        const float ms = ss[0];
+        if (ms == -INFINITY) continue;                   // a stream without keys
+        const float m_new = fmaxf(M, ms);
+        const float c0 = expf(M - m_new), c1 = expf(ms - m_new);
+        L = L * c0 + ss[1] * c1;
+#pragma unroll
+        for (int c = 0; c < AS_MAX_D / 32; ++c) {
+          const int d = lane + 32 * c;
+          if (d < D) o[c] = fmaf(ss[2 + d], c1, o[c] * c0);
+        }
+        M = m_new;
+      }
+      const float inv = L > 0.f ? 1.0f / L : 0.f;
+      T* orow = out + (size_t)(t0 + i) * g.n_heads * D + (size_t)h * D;
+#pragma unroll
+      for (int c = 0; c < AS_MAX_D / 32; ++c) {
+        const int d = lane + 32 * c;
+        if (d < D) orow[d] = from_f<T>(o[c] * inv);
+      }
+    }
   }
 }
 
@@ -302,11 +416,37 @@ HS_EXPORT int hs_kv_append(void* pool, const void* qkv, const int* table, const 
   return HS_OK;
 }
 
-HS_EXPORT int hs_attention_simt(void* out, const void* qkv, const void* pool, const int* table,
-                                const int* tok_pos, const int* tok_req, int n_tokens, int n_heads,
-                                int n_kv_heads, int head_dim, int page_size, int num_pages,
-                                int max_pages, int q_off, int k_off, int v_off, int qkv_stride,
-                                int window, float scale, int dtype, int* status, void* stream) {
+// group: tokens per CTA (1, or 4 for steps of prompt portions, where neighbours in the batch
+// are consecutive positions of one request and share the staged keys).
+template <typename T, int G>
+static int launch_attention_simt(void* out, const void* qkv, const void* pool, const int* table,
+                                 const int* tok_pos, const int* tok_req, int n_tokens,
+                                 const hs::AttnGeom& g, float scale, size_t esz, int* status,
+                                 cudaStream_t st) {
+  // keys and values side by side in shared memory while four warps of them fit in 160 KB
+  const size_t rows_bytes = (size_t)hs::AS_CHUNK * g.head_dim * esz;
+  const size_t q_bytes = (size_t)G * g.head_dim * 4;
+  const int both = hs::AS_STREAMS * (q_bytes + 2 * rows_bytes) <= 160 * 1024 ? 1 : 0;
+  const size_t smem = hs::AS_STREAMS * (q_bytes + (both ? 2 : 1) * rows_bytes);
+  dim3 grid((n_tokens + G - 1) / G, g.n_heads);
+  auto* k = hs::attention_simt_kernel<T, G>;
+  static cudaError_t state = cudaErrorUnknown;
+  if (state != cudaSuccess)
+    state = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 164 * 1024);
+  if (state != cudaSuccess) return (int)state;
+  k<<<grid, hs::AS_STREAMS * 32, smem, st>>>((T*)out, (const T*)qkv, (const T*)pool, table,
+                                              tok_pos, tok_req, n_tokens, g, scale, both, status);
+  HS_LAUNCH_CHECK();
+  return HS_OK;
+}
+
+HS_EXPORT int hs_attention_simt_grouped(void* out, const void* qkv, const void* pool,
+                                        const int* table, const int* tok_pos, const int* tok_req,
+                                        int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                        int page_size, int num_pages, int max_pages, int q_off,
+                                        int k_off, int v_off, int qkv_stride, int window,
+                                        float scale, int dtype, int group, int* status,
+                                        void* stream) {
   if (!out || !pool || !qkv || !table || !tok_pos || !tok_req || !status) return HS_ERR_ARGUMENT;
   hs::AttnGeom g{n_heads, n_kv_heads, head_dim, page_size, num_pages, max_pages,
                  q_off,   k_off,      v_off,    qkv_stride, window};
@@ -315,33 +455,28 @@ HS_EXPORT int hs_attention_simt(void* out, const void* qkv, const void* pool, co
   cudaStream_t st = (cudaStream_t)stream;
   if ((uintptr_t)pool & 15) return HS_ERR_UNSUPPORTED;   // rows are copied 16 bytes at a time
   if (n_heads > 65535) return HS_ERR_UNSUPPORTED;
-  // keys and values side by side in shared memory while four warps of them fit in 160 KB
-  const size_t esz = dtype == HS_DT_F32 ? 4 : 2;
-  const size_t rows_bytes = (size_t)hs::AS_CHUNK * head_dim * esz;
-  const int both = hs::AS_STREAMS * ((size_t)head_dim * 4 + 2 * rows_bytes) <= 160 * 1024 ? 1 : 0;
-  const size_t smem = hs::AS_STREAMS * ((size_t)head_dim * 4 + (both ? 2 : 1) * rows_bytes);
-  dim3 grid(n_tokens, n_heads);
-  if (dtype == HS_DT_F32) {
-    auto* k = hs::attention_simt_kernel<float>;
-    static cudaError_t state = cudaErrorUnknown;
-    if (state != cudaSuccess)
-      state = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 164 * 1024);
-    if (state != cudaSuccess) return (int)state;
-    k<<<grid, hs::AS_STREAMS * 32, smem, st>>>((float*)out, (const float*)qkv,
-                                                (const float*)pool, table, tok_pos, tok_req, g,
-                                                scale, both, status);
-  } else if (dtype == HS_DT_BF16) {
-    auto* k = hs::attention_simt_kernel<__nv_bfloat16>;
-    static cudaError_t state = cudaErrorUnknown;
-    if (state != cudaSuccess)
-      state = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 164 * 1024);
-    if (state != cudaSuccess) return (int)state;
-    k<<<grid, hs::AS_STREAMS * 32, smem, st>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)qkv,
-                                                (const __nv_bfloat16*)pool, table, tok_pos,
-                                                tok_req, g, scale, both, status);
-  }
-  else
-    return HS_ERR_UNSUPPORTED;
-  HS_LAUNCH_CHECK();
-  return HS_OK;
+  if (group != 1 && group != 4) return HS_ERR_ARGUMENT;
+  using bf16 = __nv_bfloat16;
+  if (dtype == HS_DT_F32)
+    return group == 4 ? launch_attention_simt<float, 4>(out, qkv, pool, table, tok_pos, tok_req,
+                                                         n_tokens, g, scale, 4, status, st)
+                      : launch_attention_simt<float, 1>(out, qkv, pool, table, tok_pos, tok_req,
+                                                         n_tokens, g, scale, 4, status, st);
+  if (dtype == HS_DT_BF16)
+    return group == 4 ? launch_attention_simt<bf16, 4>(out, qkv, pool, table, tok_pos, tok_req,
+                                                        n_tokens, g, scale, 2, status, st)
+                      : launch_attention_simt<bf16, 1>(out, qkv, pool, table, tok_pos, tok_req,
+                                                        n_tokens, g, scale, 2, status, st);
+  return HS_ERR_UNSUPPORTED;
+}
+
+HS_EXPORT int hs_attention_simt(void* out, const void* qkv, const void* pool, const int* table,
+                                const int* tok_pos, const int* tok_req, int n_tokens, int n_heads,
+                                int n_kv_heads, int head_dim, int page_size, int num_pages,
+                                int max_pages, int q_off, int k_off, int v_off, int qkv_stride,
+                                int window, float scale, int dtype, int* status, void* stream) {
+  return hs_attention_simt_grouped(out, qkv, pool, table, tok_pos, tok_req, n_tokens, n_heads,
+                                   n_kv_heads, head_dim, page_size, num_pages, max_pages, q_off,
+                                   k_off, v_off, qkv_stride, window, scale, dtype, 1, status,
+                                   stream);
 }

@@ -174,6 +174,8 @@ def _declare(lib) -> None:
         "hs_linear_skinny_argmax_scratch": [I, I, I, P],
         "hs_kv_append": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "hs_attention_simt": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P],
+        "hs_attention_simt_grouped": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, I, I,
+                                      P, P],
         "hs_attention_decode_append": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I,
                                        F, I, I, I, I, P, P, P, P, P],
         "hs_attention_decode_mma": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, I, I,
@@ -714,10 +716,14 @@ class CudaOps:
                                  fuse)
             return
         self.launches += 1
-        _check(self.lib.hs_attention_simt(
+        # steps of prompt portions (four tokens a request or more on average): a CTA serves four
+        # neighbours of the batch, which share the staged keys when they are one request's
+        # (with a work list: the step has prompt portions; the counts may be padded ones)
+        group = 4 if (plan.tile_cap > 0 if plan is not None else n >= 4 * table.shape[0]) else 1
+        _check(self.lib.hs_attention_simt_grouped(
             _ptr(out), _ptr(qkv), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req), n,
             g.n_heads, g.n_kv_heads, g.head_dim, g.page_size, g.num_pages, g.max_pages, g.q_off,
-            g.k_off, g.v_off, g.qkv_stride, g.window, scale, _DT[qkv.dtype], _ptr(status),
+            g.k_off, g.v_off, g.qkv_stride, g.window, scale, _DT[qkv.dtype], group, _ptr(status),
             self._stream()), f"attention(head_dim={g.head_dim}, heads={g.n_heads})")
 
     def _attention_fast(self, out, qkv, pool, table, tok_pos, tok_req, g, scale, status, plan,
