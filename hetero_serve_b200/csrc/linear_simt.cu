@@ -17,7 +17,21 @@ namespace hs {
 
 constexpr int LS_BM = 64, LS_BN = 64, LS_BK = 16, LS_THREADS = 256;
 
-template <typename TI, typename TO>
+// four consecutive elements of a row in one load (the rows are 16-byte / 8-byte aligned there)
+__device__ __forceinline__ void lb_load4(const float* p, float (&v)[4]) {
+  const float4 x = *(const float4*)p;
+  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+__device__ __forceinline__ void lb_load4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 x = *(const uint2*)p;
+  v[0] = __uint_as_float(x.x << 16); v[1] = __uint_as_float(x.x & 0xffff0000u);
+  v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
+}
+
+
+// VEC: K is a multiple of 4 and both matrices start on a 16-byte boundary: a thread's four k
+// of a row come in one load.
+template <typename TI, typename TO, bool VEC>
 __global__ void __launch_bounds__(LS_THREADS)
 linear_simt_kernel(TO* out, const TI* __restrict__ a, const TI* __restrict__ w,
                    const float* __restrict__ bias, const float* residual, int M, int N, int K,
@@ -38,11 +52,23 @@ linear_simt_kernel(TO* out, const TI* __restrict__ a, const TI* __restrict__ w,
   for (int k0 = 0; k0 < K; k0 += LS_BK) {
     {
       const int gm = m0 + lr, gn = n0 + lr;
+      if (VEC) {
+        float ra[4] = {0.f, 0.f, 0.f, 0.f}, rw[4] = {0.f, 0.f, 0.f, 0.f};
+        const int gk = k0 + lk;                           // K % 4 == 0: all four or none
+        if (gm < M && gk < K) lb_load4(a + (size_t)gm * K + gk, ra);
+        if (gn < N && gk < K) lb_load4(w + (size_t)gn * K + gk, rw);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int gk = k0 + lk + j;
-        As[lk + j][lr] = (gm < M && gk < K) ? to_f(a[(size_t)gm * K + gk]) : 0.f;
-        Ws[lk + j][lr] = (gn < N && gk < K) ? to_f(w[(size_t)gn * K + gk]) : 0.f;
+        for (int j = 0; j < 4; ++j) {
+          As[lk + j][lr] = ra[j];
+          Ws[lk + j][lr] = rw[j];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int gk = k0 + lk + j;
+          As[lk + j][lr] = (gm < M && gk < K) ? to_f(a[(size_t)gm * K + gk]) : 0.f;
+          Ws[lk + j][lr] = (gn < N && gk < K) ? to_f(w[(size_t)gn * K + gk]) : 0.f;
+        }
       }
     }
     __syncthreads();
@@ -83,17 +109,6 @@ linear_simt_kernel(TO* out, const TI* __restrict__ a, const TI* __restrict__ w,
 // Tiles of both operands arrive k-major ([k][row]) through registers, two buffers.
 constexpr int LB_BM = 128, LB_BN = 128, LB_BK = 8, LB_THREADS = 256;
 
-// four consecutive elements of a row in one load (the rows are 16-byte / 8-byte aligned there)
-__device__ __forceinline__ void lb_load4(const float* p, float (&v)[4]) {
-  const float4 x = *(const float4*)p;
-  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
-}
-__device__ __forceinline__ void lb_load4(const __nv_bfloat16* p, float (&v)[4]) {
-  const uint2 x = *(const uint2*)p;
-  v[0] = __uint_as_float(x.x << 16); v[1] = __uint_as_float(x.x & 0xffff0000u);
-  v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
-}
-
 // VEC: K is a multiple of 4 and both matrices start on a 16-byte boundary, so a thread's four
 // k of a row come in one load (with one 4-byte load per element the load pipe, 16 sectors an
 // instruction, took as long as the products).
@@ -123,13 +138,13 @@ linear_simt_big_kernel(TO* out, const TI* __restrict__ a, const TI* __restrict__
       for (int j = 0; j < 4; ++j) ra[j] = rw[j] = 0.f;
       if (gm < M && gk < K) lb_load4(a + (size_t)gm * K + gk, ra);
       if (gn < N && gk < K) lb_load4(w + (size_t)gn * K + gk, rw);
-      return;
-    }
+    } else {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int gk = k0 + lk + j;
-      ra[j] = (gm < M && gk < K) ? to_f(a[(size_t)gm * K + gk]) : 0.f;
-      rw[j] = (gn < N && gk < K) ? to_f(w[(size_t)gn * K + gk]) : 0.f;
+      for (int j = 0; j < 4; ++j) {
+        const int gk = k0 + lk + j;
+        ra[j] = (gm < M && gk < K) ? to_f(a[(size_t)gm * K + gk]) : 0.f;
+        rw[j] = (gn < N && gk < K) ? to_f(w[(size_t)gn * K + gk]) : 0.f;
+      }
     }
   };
   auto stash = [&](int buf) {
@@ -190,14 +205,16 @@ linear_simt_big_kernel(TO* out, const TI* __restrict__ a, const TI* __restrict__
 // rows; thread (feature f, row group g) runs the chains of rows g and g + 8 for feature f over
 // k = 0..K-1 in index order - the same chain of fused multiply-adds, so the same bits, as the
 // tile kernel gives that element.  The weight rows and the activation rows arrive through a
-// ring of four 128-column stages of 16-byte cp.async copies.
-constexpr int LF_BN = 16, LF_BK = 128, LF_THREADS = 128, LF_STAGES = 4, LF_MAX_M = 16;
+// ring of four 128-column stages of 16-byte cp.async copies.  RPT rows per thread: 2 for up to
+// 16 rows, 8 for up to 64 (rows g, g + 8, ..., g + 56).
+constexpr int LF_BN = 16, LF_BK = 128, LF_THREADS = 128, LF_STAGES = 4;
 
-template <typename TI>
+template <typename TI, int RPT>
 struct LfShape {
+  static constexpr int MAX_M = 8 * RPT;
   static constexpr int VEC = 16 / (int)sizeof(TI);           // elements per 16-byte copy
   static constexpr int WS = LF_BK + VEC;                     // weight row stride: no bank conflicts
-  static constexpr int STAGE = LF_BN * WS + LF_MAX_M * LF_BK;  // elements per stage
+  static constexpr int STAGE = LF_BN * WS + MAX_M * LF_BK;   // elements per stage
   static constexpr size_t SMEM = (size_t)LF_STAGES * STAGE * sizeof(TI);
 };
 
@@ -217,16 +234,16 @@ __device__ __forceinline__ void lf_load4(const __nv_bfloat16* p, float (&v)[4]) 
   v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
 }
 
-template <typename TI, typename TO>
+template <typename TI, typename TO, int RPT>
 __global__ void __launch_bounds__(LF_THREADS)
 linear_simt_few_rows_kernel(TO* out, const TI* __restrict__ a, const TI* __restrict__ w,
                             const float* __restrict__ bias, const float* residual, int M, int N,
                             int K, int act) {
-  using S = LfShape<TI>;
+  using S = LfShape<TI, RPT>;
   extern __shared__ __align__(16) uint8_t lf_smem[];
   TI* ring = (TI*)lf_smem;
   const int tid = threadIdx.x;
-  const int f = tid & 15, grp = tid >> 4;                    // rows grp and grp + 8
+  const int f = tid & 15, grp = tid >> 4;                    // rows grp, grp + 8, ...
   const int n0 = blockIdx.x * LF_BN;
   const int num_kt = (K + LF_BK - 1) / LF_BK;
   constexpr int CPR = LF_BK / S::VEC;                        // copies per row of a stage
@@ -241,7 +258,7 @@ linear_simt_few_rows_kernel(TO* out, const TI* __restrict__ a, const TI* __restr
         const bool ok = gn < N && gk < K;
         lf_copy16(sw + row * S::WS + kc, ok ? w + (size_t)gn * K + gk : w, ok);
       }
-      for (int c = tid; c < LF_MAX_M * CPR; c += LF_THREADS) {
+      for (int c = tid; c < S::MAX_M * CPR; c += LF_THREADS) {
         const int row = c / CPR, kc = (c - row * CPR) * S::VEC;
         const int gk = kt * LF_BK + kc;
         const bool ok = row < M && gk < K;
@@ -252,25 +269,26 @@ linear_simt_few_rows_kernel(TO* out, const TI* __restrict__ a, const TI* __restr
   };
 
   for (int s = 0; s < LF_STAGES - 1; ++s) issue(s);
-  float acc0 = 0.f, acc1 = 0.f;
+  float acc[RPT];
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) acc[r] = 0.f;
   for (int kt = 0; kt < num_kt; ++kt) {
     asm volatile("cp.async.wait_group %0;" ::"n"(LF_STAGES - 2) : "memory");
     __syncthreads();                 // stage kt has landed; stage kt - 1 is free for every thread
     issue(kt + LF_STAGES - 1);
     const TI* sw = ring + (size_t)(kt % LF_STAGES) * S::STAGE + f * S::WS;
-    const TI* sa0 = ring + (size_t)(kt % LF_STAGES) * S::STAGE + LF_BN * S::WS + grp * LF_BK;
-    const TI* sa1 = sa0 + 8 * LF_BK;
+    const TI* sa = ring + (size_t)(kt % LF_STAGES) * S::STAGE + LF_BN * S::WS + grp * LF_BK;
     const int kmax = min(LF_BK, K - kt * LF_BK);             // a multiple of 4
 #pragma unroll 4
     for (int k = 0; k < kmax; k += 4) {
-      float wv[4], x0[4], x1[4];
+      float wv[4];
       lf_load4(sw + k, wv);
-      lf_load4(sa0 + k, x0);
-      lf_load4(sa1 + k, x1);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        acc0 = fmaf(x0[i], wv[i], acc0);
-        acc1 = fmaf(x1[i], wv[i], acc1);
+      for (int r = 0; r < RPT; ++r) {
+        float x[4];
+        lf_load4(sa + r * 8 * LF_BK + k, x);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[r] = fmaf(x[i], wv[i], acc[r]);
       }
     }
   }
@@ -278,10 +296,10 @@ linear_simt_few_rows_kernel(TO* out, const TI* __restrict__ a, const TI* __restr
   const int gn = n0 + f;
   if (gn >= N) return;
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int gm = grp + 8 * half;
+  for (int r = 0; r < RPT; ++r) {
+    const int gm = grp + 8 * r;
     if (gm >= M) continue;
-    float v = half ? acc1 : acc0;
+    float v = acc[r];
     if (bias) v += bias[gn];
     v = apply_act(v, act);
     if (residual) v += residual[(size_t)gm * N + gn];
@@ -289,18 +307,26 @@ linear_simt_few_rows_kernel(TO* out, const TI* __restrict__ a, const TI* __restr
   }
 }
 
-template <typename TI, typename TO>
-static int launch_few_rows(void* out, const void* a, const void* w, const float* bias,
-                           const float* residual, int M, int N, int K, int act, cudaStream_t st) {
-  auto* k = linear_simt_few_rows_kernel<TI, TO>;
+template <typename TI, typename TO, int RPT>
+static int launch_few_rows_as(void* out, const void* a, const void* w, const float* bias,
+                              const float* residual, int M, int N, int K, int act,
+                              cudaStream_t st) {
+  auto* k = linear_simt_few_rows_kernel<TI, TO, RPT>;
   static cudaError_t state = cudaErrorUnknown;
   if (state != cudaSuccess)
     state = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)LfShape<TI>::SMEM);
+                                 (int)LfShape<TI, RPT>::SMEM);
   if (state != cudaSuccess) return (int)state;
-  k<<<(N + LF_BN - 1) / LF_BN, LF_THREADS, LfShape<TI>::SMEM, st>>>(
+  k<<<(N + LF_BN - 1) / LF_BN, LF_THREADS, LfShape<TI, RPT>::SMEM, st>>>(
       (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act);
   return HS_OK;
+}
+
+template <typename TI, typename TO>
+static int launch_few_rows(void* out, const void* a, const void* w, const float* bias,
+                           const float* residual, int M, int N, int K, int act, cudaStream_t st) {
+  if (M <= 16) return launch_few_rows_as<TI, TO, 2>(out, a, w, bias, residual, M, N, K, act, st);
+  return launch_few_rows_as<TI, TO, 8>(out, a, w, bias, residual, M, N, K, act, st);
 }
 
 }  // namespace hs
@@ -318,7 +344,10 @@ HS_EXPORT int hs_linear_simt(void* out, const void* a, const void* w, const floa
   using bf16 = __nv_bfloat16;
   // few rows: the weight-stream kernel (rows and pointers that 16-byte copies can take)
   const int vec = in_dtype == HS_DT_F32 ? 4 : 8;
-  if (M <= hs::LF_MAX_M && K % vec == 0 && !((uintptr_t)a & 15) && !((uintptr_t)w & 15)) {
+  // (17-64 rows: while the layer's feature blocks are a few per SM; a wide layer such as the
+  // vocabulary head keeps more in flight with the tile kernel: 233 us against 599 at 64 rows)
+  const bool few = M <= 16 || (M <= 64 && (N + hs::LF_BN - 1) / hs::LF_BN <= 4 * hs_sm_count());
+  if (few && K % vec == 0 && !((uintptr_t)a & 15) && !((uintptr_t)w & 15)) {
     int rc = HS_ERR_UNSUPPORTED;
     if (in_dtype == HS_DT_F32 && out_dtype == HS_DT_F32)
       rc = hs::launch_few_rows<float, float>(out, a, w, bias, residual, M, N, K, act, st);
@@ -351,9 +380,16 @@ HS_EXPORT int hs_linear_simt(void* out, const void* a, const void* w, const floa
     HS_LAUNCH_CHECK();
     return HS_OK;
   }
+  const bool ls_vec = K % 4 == 0 && !((uintptr_t)a & 15) && !((uintptr_t)w & 15);
 #define HS_LS_LAUNCH(TI, TO)                                                                  \
-  hs::linear_simt_kernel<TI, TO><<<grid, hs::LS_THREADS, 0, st>>>(                             \
-      (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act)
+  do {                                                                                        \
+    if (ls_vec)                                                                               \
+      hs::linear_simt_kernel<TI, TO, true><<<grid, hs::LS_THREADS, 0, st>>>(                  \
+          (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act);                \
+    else                                                                                      \
+      hs::linear_simt_kernel<TI, TO, false><<<grid, hs::LS_THREADS, 0, st>>>(                 \
+          (TO*)out, (const TI*)a, (const TI*)w, bias, residual, M, N, K, act);                \
+  } while (0)
   if (in_dtype == HS_DT_F32 && out_dtype == HS_DT_F32) HS_LS_LAUNCH(float, float);
   else if (in_dtype == HS_DT_BF16 && out_dtype == HS_DT_BF16) HS_LS_LAUNCH(bf16, bf16);
   else if (in_dtype == HS_DT_BF16 && out_dtype == HS_DT_F32) HS_LS_LAUNCH(bf16, float);
