@@ -584,6 +584,21 @@ def run_kernels(args):
     return 0
 
 
+def run_phase_marks(args):
+    """`HETERO_SERVE_PHASE_MARKS=1 python bench.py --phase-marks [--batch B]`: one JSON line per
+    launch of the later layers of the chain (see kernels/microbench.py:phase_marks)."""
+    from hetero_serve_b200.kernels import microbench
+    cfg, _ = model_config(args)
+    rows = microbench.phase_marks(cfg, rows=args.batch)
+    if not rows:
+        print(json.dumps({"phase_marks": "unavailable: build the library with "
+                                         "HETERO_SERVE_PHASE_MARKS=1"}))
+        return 0
+    for r in rows:
+        print(json.dumps(r))
+    return 0
+
+
 def run_one_step(args):
     """For profilers: build the model, warm up, then run ONE step (eager, no CUDA graph)
     between cudaProfilerStart and cudaProfilerStop, so that
@@ -759,6 +774,9 @@ def main() -> int:
                     help="with --one-step decode: sample with this temperature (0: greedy)")
     ap.add_argument("--top-k", dest="top_k", type=int, default=0,
                     help="with --one-step decode: restrict sampling to the k largest")
+    ap.add_argument("--phase-marks", dest="phase_marks", action="store_true",
+                    help="print the few-row linears' own time marks inside a CUDA graph (needs a "
+                         "library built with HETERO_SERVE_PHASE_MARKS=1) and exit")
     ap.add_argument("--one-step", dest="one_step", default="", choices=["", "decode", "prefill"],
                     help="for profilers: run a single eager step between cudaProfilerStart/Stop")
     args = ap.parse_args()
@@ -771,6 +789,8 @@ def main() -> int:
         return run_reference(args)
     if args.kernels:
         return run_kernels(args)
+    if args.phase_marks:
+        return run_phase_marks(args)
     if args.one_step:
         return run_one_step(args)
     return run_ours(args)

@@ -32,7 +32,9 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 if os.environ.get("HETERO_SERVE_PHASE_MARKS") == "1":      # a tuning build (see common.cuh)
     NVCC_FLAGS = NVCC_FLAGS + ["-DHS_PHASE_MARKS"]
-LIB_STEM = "libhetero_serve_b200"
+    LIB_STEM = "libhetero_serve_b200_marks"                # kept beside the product library
+else:
+    LIB_STEM = "libhetero_serve_b200"
 
 
 class BuildError(RuntimeError):

@@ -285,3 +285,74 @@ def fractions(model, cfg, peaks, dtype="bfloat16", device="cuda:0") -> dict:
     prefill step (a kernel that failed its comparison carries ``None``)."""
     return {f"{r['step']}.{r['kernel']}": r.get("frac") for r in
             table(model, cfg, peaks, dtype, batches=(8,), device=device)}
+
+
+def phase_marks(cfg, rows: int = 8, layers: int = 8, device: str = "cuda:0") -> list[dict]:
+    """The four few-row linears of a decode layer (LayerNorm + QKV, attention out + residual,
+    LayerNorm + fc + GELU, MLP out + residual) chained ``layers`` times in one CUDA graph with
+    programmatic dependent launch, weights rotating through DRAM, and the kernel's own time
+    marks read back: for every launch of the later layers, when its LAST CTA passed the
+    dependency wait, had its activations staged, had issued its MMAs and had finished, in ns
+    after the last CTA of the launch before.  Needs a library built with phase marks
+    (``HETERO_SERVE_PHASE_MARKS=1``); the product build has none and returns an empty list."""
+    import ctypes
+
+    from .ops import CudaOps
+    ops = CudaOps(device)
+    if not hasattr(ops.lib, "hs_set_timing_buffer"):
+        return []
+    ops.lib.hs_set_timing_buffer.argtypes = [ctypes.c_void_p]
+    E = cfg["n_embd"]
+    inner = cfg.get("n_inner") or 4 * E
+    slots = 512
+    bufs = torch.zeros(layers * 4, slots * 8, dtype=torch.int64, device=device)
+    ws = [dict(qkv=torch.randn(3 * E, E, device=device).bfloat16(),
+               o=torch.randn(E, E, device=device).bfloat16(),
+               fc=torch.randn(inner, E, device=device).bfloat16(),
+               p2=torch.randn(E, inner, device=device).bfloat16()) for _ in range(layers)]
+    x = torch.randn(rows, E, device=device)
+    g, b = torch.randn(E, device=device), torch.randn(E, device=device)
+    h = torch.empty(rows, E, device=device, dtype=torch.bfloat16)
+    qkv = torch.empty(rows, 3 * E, device=device, dtype=torch.bfloat16)
+    att = torch.randn(rows, E, device=device).bfloat16()
+    mid = torch.empty(rows, inner, device=device, dtype=torch.bfloat16)
+    bq, bo, bf = (torch.randn(n, device=device) for n in (3 * E, E, inner))
+
+    def layer(i, armed):
+        w = ws[i]
+
+        def arm(k):
+            ops.lib.hs_set_timing_buffer(bufs[i * 4 + k].data_ptr() if armed else None)
+        arm(0); ops.norm_linear(qkv, h, x, g, b, 1e-5, w["qkv"], bq)
+        arm(1); ops.linear(x, att, w["o"], bo, residual=x)
+        arm(2); ops.norm_linear(mid, h, x, g, b, 1e-5, w["fc"], bf, act="gelu_tanh")
+        arm(3); ops.linear(x, mid, w["p2"], bo, residual=x)
+
+    for i in range(layers):
+        layer(i, False)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(layers):
+            layer(i, True)
+    ops.lib.hs_set_timing_buffer(None)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    marks = bufs.view(layers * 4, slots, 8).cpu()
+    names = ["layernorm + qkv", "attention out + residual", "layernorm + fc + gelu",
+             "mlp out + residual"]
+    out, prev_end = [], None
+    for j in range(layers * 4):
+        t = marks[j]
+        t = t[t[:, 0] > 0]
+        if t.shape[0] == 0:
+            return []                                   # built without marks
+        first = int(t[:, 0].min())                      # the first CTA to start (may be negative:
+        wait, staged, mma, end = (int(t[:, k].max()) for k in (1, 2, 3, 4))   # it overlaps)
+        if prev_end is not None and j >= 8:             # the first two layers warm up
+            out.append({"kernel": names[j % 4], "ctas": int(t.shape[0]),
+                        "first_start_ns": first - prev_end, "wait_over_ns": wait - prev_end, "staged_ns": staged - wait,
+                        "mma_ns": mma - staged, "end_ns": end - mma, "total_ns": end - prev_end})
+        prev_end = end
+    return out
