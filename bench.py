@@ -255,25 +255,37 @@ def time_decode(runner, torch, batch, windows, warmup, vocab, seed, tag):
     return total_ms, launches, per_window
 
 
-def time_prefill(runner, torch, n_seqs, seq_len, vocab, seed, reps=5, warmup=3):
+def time_prefill(runner, torch, n_seqs, seq_len, vocab, seed, reps=5, warmup=3, chain=4):
+    """Milliseconds of one prefill step of n_seqs whole prompts: `chain` such steps (other
+    requests, other pages) launched back to back between two events, divided by `chain`, so
+    that the host's preparation of a step runs while the device works on the one before, as
+    it does in serving and in the decode windows; the median of `reps` such chains.  Also
+    returned: the same for a single step launched on an idle device (host preparation
+    included)."""
     from hetero_serve_b200.engine import StepEntry
     g = torch.Generator().manual_seed(seed)
     prompts = torch.randint(0, vocab, (n_seqs, seq_len), generator=g).tolist()
-    times = []
-    for it in range(warmup + reps):
-        entries = [StepEntry(f"p{it}_{i}", p, want=[seq_len - 1]) for i, p in enumerate(prompts)]
-        torch.cuda.synchronize()
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        runner.step(entries, sample=True, check_status=False)
-        e.record()
-        torch.cuda.synchronize()
-        if it >= warmup:
-            times.append(s.elapsed_time(e))
-        for en in entries:
-            runner.close(en.req_id)
+    out = {}
+    for n in (chain, 1):
+        times = []
+        for it in range(warmup + reps):
+            steps = [[StepEntry(f"p{n}_{it}_{c}_{i}", p, want=[seq_len - 1])
+                      for i, p in enumerate(prompts)] for c in range(n)]
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for entries in steps:
+                runner.step(entries, sample=True, check_status=False)
+            e.record()
+            torch.cuda.synchronize()
+            if it >= warmup:
+                times.append(s.elapsed_time(e) / n)
+            for entries in steps:
+                for en in entries:
+                    runner.close(en.req_id)
+        out[n] = statistics.median(times)
     runner.check_status()
-    return statistics.median(times)
+    return out[chain], out[1]
 
 
 def time_e2e(model_dir, torch, batch, windows, warmup, vocab, seed, num_blocks, dtype,
@@ -506,7 +518,7 @@ def run_ours(args):
             nb = decode_bytes(model, b_, mean_ctx, itemsize)
             points[f"decode_b{b_}_hbm_frac"] = round(nb / (ms_b / steps / 1e3) / 1e9 / pk["hbm_gbs"], 4)
 
-        pre_ms = time_prefill(runner, torch, 2, 1024, vocab, 5)
+        pre_ms, pre_single_ms = time_prefill(runner, torch, 2, 1024, vocab, 5)
         flops = prefill_flops(cfg, 2, 1024, 2)
         pre_frac = flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12)
         del runner
@@ -552,7 +564,8 @@ def run_ours(args):
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
         "prefill": {"value": round(2048 / (pre_ms / 1e3), 1), "tokens": 2048,
-                    "ms": round(pre_ms, 3), "frac": round(pre_frac, 4)},
+                    "ms": round(pre_ms, 3), "frac": round(pre_frac, 4),
+                    "steps_back_to_back": 4, "single_step_ms": round(pre_single_ms, 3)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
@@ -596,6 +609,9 @@ def run_phase_marks(args):
         return 0
     for r in rows:
         print(json.dumps(r))
+    shares = microbench.attention_phase_marks(cfg)
+    if shares:
+        print(json.dumps(shares))
     return 0
 
 

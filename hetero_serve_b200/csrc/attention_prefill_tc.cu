@@ -57,9 +57,10 @@ struct PrefillTcParams {
   int* work_counter;
   int n_heads, n_kv_heads, page_size, num_pages, max_pages, q_off, ps_log2;
   float scale;
-  unsigned long long* timing;   // null, or 8 x uint64 per CTA: cycles per softmax phase (0 wait
-                                // for S, 1 maximum, 2 exponentials, 3 wait for P V and add O,
-                                // 4 write P, 5 loop, 6 last O, 7 wait for an item's first S)
+  unsigned long long* timing;   // tuning builds (-DHS_PHASE_MARKS) only: null, or 8 x uint64 per
+                                // CTA, cycles of one softmax thread per phase (0 wait for S,
+                                // 1 maximum, 2 exponentials, 3 wait for P V and add O, 4 write P,
+                                // 5 loop, 6 last O, 7 wait for an item's first S)
 };
 
 // barriers, in this order in shared memory
@@ -262,6 +263,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
       const float sl2 = p.scale * 1.4426950408889634f;
       float m = -INFINITY, l = 0.f, corr_pending = 1.f;
+#ifdef HS_PHASE_MARKS
       long long t_mark = clock64();
       auto lap = [&](int phase) {
         if (p.timing != nullptr && threadIdx.x == 64) {
@@ -270,6 +272,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
           t_mark = now;
         }
       };
+#else
+      auto lap = [](int) {};
+#endif
       constexpr int OC = TA_D / 2;                          // output columns of this thread
       float o[OC];
 #pragma unroll

@@ -113,10 +113,13 @@ __device__ __forceinline__ void mark_time(unsigned long long* buf, int cta, int 
 // anything an earlier kernel of the step writes (weights, block tables and work lists are safe).
 // The decode attention kernels also fetch cache pages of EARLIER positions before the wait.
 // Those were written by a kernel of an earlier step, and that is safe only because steps are
-// separated on the stream by an operation that is not a kernel (the upload of the step's
-// metadata): a programmatic launch overlaps its predecessor kernel, never a copy.  A caller
-// that chains steps without such an operation between them must launch these kernels without
-// the attribute (`pdl` = 0).
+// separated on the stream by something that is not a programmatic edge between kernels: the
+// upload of the step's metadata (a copy; a programmatic launch overlaps its predecessor
+// kernel, never a copy) when steps are launched kernel by kernel, the boundary between two
+// graph launches when a step is a CUDA graph (its first kernel node has no kernel before it
+// in the graph, and a graph starts after all earlier work of its stream).  A caller that
+// chains steps inside ONE graph or stream of kernels without such a boundary must launch
+// these kernels without the attribute (`pdl` = 0).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

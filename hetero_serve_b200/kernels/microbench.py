@@ -356,3 +356,40 @@ def phase_marks(cfg, rows: int = 8, layers: int = 8, device: str = "cuda:0") -> 
                         "mma_ns": mma - staged, "end_ns": end - mma, "total_ns": end - prev_end})
         prev_end = end
     return out
+
+
+def attention_phase_marks(cfg, n_seqs: int = 2, seq_len: int = 1024, device: str = "cuda:0") -> dict:
+    """The prompt attention on tcgen05 over `n_seqs` whole prompts of `seq_len` tokens with the
+    kernel's own cycle counters on (a library built with ``HETERO_SERVE_PHASE_MARKS=1``): what
+    one softmax thread of every CTA spends in each phase of its loop, as mean cycles per CTA and
+    as shares.  Empty when the library has no counters or the head size is not the kernel's."""
+    import ctypes
+
+    b = _Bench(cfg, {"hbm_gbs": 1.0, "bf16_tflops": 1.0}, "bfloat16", device)
+    ops = b.ops
+    if not hasattr(ops.lib, "hs_set_timing_buffer") or b.D != 64:
+        return {}
+    ops.lib.hs_set_timing_buffer.argtypes = [ctypes.c_void_p]
+    lens = [seq_len] * n_seqs
+    geom, qkv, pool, table, pos, req, host = b._cache(lens, lens, 1)
+    T = qkv.shape[0]
+    plan = ops.make_plan(host, T, 16)
+    out = torch.zeros(T, b.E, device=b.dev, dtype=b.dt)
+    scale = 1.0 / math.sqrt(b.D)
+    for _ in range(3):
+        ops.attention_append(out, qkv, pool[0], table, pos, req, geom, scale, b.status, plan, True)
+    torch.cuda.synchronize()
+    sms = torch.cuda.get_device_properties(b.dev).multi_processor_count
+    buf = torch.zeros(sms * 8, dtype=torch.int64, device=b.dev)
+    ops.lib.hs_set_timing_buffer(buf.data_ptr())
+    ops.attention(out, qkv, pool[0], table, pos, req, geom, scale, b.status, plan)
+    torch.cuda.synchronize()
+    ops.lib.hs_set_timing_buffer(None)
+    t = buf.view(sms, 8).cpu().double()
+    total = float(t.sum(1).mean())
+    if total <= 0:
+        return {}
+    names = ["wait for S", "row maximum", "exponentials", "wait for P V, add O_tile", "write P",
+             "loop", "last O_tile and output", "wait for an item's first S"]
+    return {"kernel": "attention_prefill_tc", "tokens": T, "cycles_per_cta": round(total),
+            "shares": {n: round(float(t[:, i].mean()) / total, 4) for i, n in enumerate(names)}}
