@@ -93,11 +93,14 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed.  The
+    reported clock is the median of the samples taken while the GPU was busy (utilisation above
+    zero); a program that leaves the GPU idle between small kernels, as the reference arm does,
+    shows the idle clock in the others."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_power_cap,utilization.gpu")
 
     def __init__(self, index=0):
         self.proc, self.index = None, index
@@ -121,7 +124,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
+        sm, mx, busy, reasons = [], [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for line in out.splitlines():
             parts = [x.strip() for x in line.split(",")]
@@ -131,12 +134,18 @@ class ClockSampler:
                 sm.append(float(parts[0])); mx.append(float(parts[1]))
             except ValueError:
                 continue
+            try:
+                if len(parts) > 7 and float(parts[7]) > 0:
+                    busy.append(sm[-1])
+            except ValueError:
+                pass
             for nm, val in zip(names, parts[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(nm)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
+        under_load = busy or sm
+        return {"sm_mhz": statistics.median(under_load) if under_load else None,
                 "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
-                "reasons": sorted(reasons)}
+                "samples_busy": len(busy), "reasons": sorted(reasons)}
 
 
 def decode_windows(prompt_len: int, context: int, steps: int, n_windows: int = N_WINDOWS):
