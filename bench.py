@@ -529,7 +529,14 @@ def run_ours(args):
 
         pre_ms, pre_single_ms = time_prefill(runner, torch, 2, 1024, vocab, 5)
         flops = prefill_flops(cfg, 2, 1024, 2)
-        pre_frac = flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12)
+        if dtype == "bfloat16":
+            pre_peak, pre_peak_of = pk["bf16_tflops"], "bf16 tensor, " + pk_src
+        else:
+            # the 32-bit path runs on the CUDA cores: 128 FMA lanes an SM at the highest clock
+            props = torch.cuda.get_device_properties(0)
+            pre_peak = props.multi_processor_count * 128 * 2 * props.clock_rate * 1e3 / 1e12
+            pre_peak_of = "fp32 CUDA cores, nominal"
+        pre_frac = flops / (pre_ms / 1e3) / (pre_peak * 1e12)
         del runner
         torch.cuda.empty_cache()
         e2e_val, h2d, d2h = time_e2e(d, torch, batch, windows, warmup, vocab, 1,
@@ -574,7 +581,8 @@ def run_ours(args):
         "gpu_launches": launches,
         "prefill": {"value": round(2048 / (pre_ms / 1e3), 1), "tokens": 2048,
                     "ms": round(pre_ms, 3), "frac": round(pre_frac, 4),
-                    "steps_back_to_back": 4, "single_step_ms": round(pre_single_ms, 3)},
+                    "steps_back_to_back": 4, "single_step_ms": round(pre_single_ms, 3),
+                    "peak_tflops": round(pre_peak, 1), "peak_of": pre_peak_of},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
